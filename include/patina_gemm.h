@@ -1,0 +1,153 @@
+/*
+ * patina_gemm.h -- C ABI of the B200 (sm_100a) tcgen05 GEMM library.
+ *
+ * This is the boundary that replaces, for the GEMM hot path, what the reference
+ * (neoming/Patina) exposes only as a generated PTX entry plus host runners:
+ *   - the kernel ABI `tcgen05_gemm_v2(tma_a, tma_b, c, k_tiles)`
+ *     (crates/patina/tests/golden/v2_gemm_pipelined.ptx:25-31),
+ *   - the Rust runner `run_gemm(ptx, kernel, k, a, b)` (crates/patina/src/run.rs:462-529),
+ *   - the C++ harness `gemm_check <ptx> <kernel> <K>` (harness/gemm_check.cpp:186-351).
+ * Ownership and error conventions follow the reference's compiler C ABI
+ * (mlir/include/patina-c/PatinaCAPI.h:3-39): opaque caller-owned contexts,
+ * heap strings released by a *_string_free that accepts NULL, null arguments
+ * produce a diagnostic and never a crash.
+ *
+ * All matrices are "TN": C[M,N] = alpha * A[M,K] * B[N,K]^T with A and B both
+ * K-contiguous (row-major A, K-major B) and C row-major. Leading dimensions
+ * are in ELEMENTS. Unless a function says otherwise, pointers are DEVICE
+ * pointers owned by the caller, the call only enqueues work on `stream`
+ * (a cudaStream_t passed as void*; NULL = the default stream) and does not
+ * synchronise. There is no CPU fallback: without an sm_100 device every
+ * compute entry point returns PATINA_GEMM_ERR_UNSUPPORTED_ARCH.
+ *
+ * Alignment rules (TMA): A, B, C base addresses 16-byte aligned;
+ * lda, ldb, ldc times the element size a multiple of 16 bytes; lda,ldb >= K,
+ * ldc >= N. M, N, K are otherwise free (ragged edges are zero-filled on load
+ * and clipped on store). M == 0 or N == 0 is a no-op; K == 0 stores zeros.
+ */
+#ifndef PATINA_GEMM_H
+#define PATINA_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct PatinaGemmContext PatinaGemmContext;
+
+enum {
+  PATINA_GEMM_OK = 0,
+  PATINA_GEMM_ERR_INVALID_ARG = 1,
+  PATINA_GEMM_ERR_UNSUPPORTED_ARCH = 2, /* harness exit code 3 (gemm_check.cpp:233-238) */
+  PATINA_GEMM_ERR_CUDA = 3,             /* harness exit code 2 (gemm_check.cpp:43-56) */
+  PATINA_GEMM_ERR_TIMEOUT = 4           /* a bounded device-side wait expired */
+};
+
+enum { PATINA_IN_F16 = 0, PATINA_IN_BF16 = 1, PATINA_IN_E4M3 = 2 };
+enum { PATINA_OUT_BF16 = 0, PATINA_OUT_F32 = 1 };
+
+/* Tile configuration. Zero in any field means "choose for me". */
+typedef struct PatinaGemmConfig {
+  int32_t cta_group; /* 1 = one CTA per tile (128 x block_n); 2 = CTA pair (256 x block_n) */
+  int32_t block_n;   /* 128 or 256 */
+  int32_t stages;    /* shared-memory ring depth */
+  int32_t group_m;   /* scheduler band height in tiles */
+  int32_t max_ctas;  /* cap on persistent CTAs (0 = number of SMs) */
+} PatinaGemmConfig;
+
+/* What a call would launch; computed on the host without touching a device. */
+typedef struct PatinaGemmPlan {
+  int32_t cta_group, block_n, stages, group_m;
+  uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
+  uint32_t grid, block, cluster, smem_bytes, tmem_cols;
+  uint32_t stage_bytes, expect_tx_bytes;
+  uint32_t idesc;
+} PatinaGemmPlan;
+
+/* ---- context (replaces run.rs `Cuda::init` / `Drop`, run.rs:256-394) ----- */
+/* One context per device. Calls on one context are not thread-safe; different
+ * contexts are independent. Returns PATINA_GEMM_ERR_UNSUPPORTED_ARCH when the
+ * device is not compute capability 10.x (run.rs:476-481, gemm_check.cpp:233). */
+int patina_gemm_context_create(int device, PatinaGemmContext** out);
+void patina_gemm_context_destroy(PatinaGemmContext* ctx);
+
+/* Last diagnostic of this context as a heap string (NULL if none). Mirrors
+ * patina_verify's "NULL means success" (PatinaCAPI.h:25-28). */
+char* patina_gemm_last_error(PatinaGemmContext* ctx);
+/* Mirrors patina_string_free (PatinaCAPI.h:38-39). NULL-safe. */
+void patina_gemm_string_free(char* s);
+
+/* Bound, in nanoseconds, on every barrier wait inside the kernels
+ * (the reference's waits are unbounded spins, v2_gemm_pipelined.ptx:111-113). */
+int patina_gemm_set_wait_limit_ns(PatinaGemmContext* ctx, uint64_t ns);
+
+/* Synchronise `stream` and report whether any kernel enqueued through this
+ * context since the last call gave up on a wait (PATINA_GEMM_ERR_TIMEOUT).
+ * Replaces the cuStreamSynchronize in gemm_check.cpp:297 / run.rs:375. */
+int patina_gemm_status(PatinaGemmContext* ctx, void* stream);
+
+/* Kernels this context has launched so far. */
+uint64_t patina_gemm_launch_count(PatinaGemmContext* ctx);
+
+/* ---- the GEMM entry points ------------------------------------------------ */
+/* bf16 in, fp32 accumulate (TMEM), bf16 out. Replaces the cuLaunchKernel of the
+ * generated kernel (gemm_check.cpp:286-296, run.rs:502-524) for bf16 problems. */
+int patina_gemm_bf16_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                        int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                        float alpha, void* stream);
+
+/* fp8 e4m3 in, fp32 accumulate, bf16 out scaled by scale_a * scale_b. */
+int patina_gemm_fp8e4m3_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                           int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                           float scale_a, float scale_b, void* stream);
+
+/* f16 in, fp32 out: the reference kernel's own types (gemm_check.cpp:9-10);
+ * with M = N = 128 and K % 32 == 0 it computes exactly what tcgen05_gemm_v2 does. */
+int patina_gemm_f16_tn_f32out(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                              int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                              float alpha, void* stream);
+
+/* Any supported (in_type, out_type) pair with an explicit tile configuration
+ * (cfg may be NULL). */
+int patina_gemm_ex(PatinaGemmContext* ctx, int in_type, int out_type, const void* A, int64_t lda,
+                   const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N,
+                   int64_t K, float alpha, const PatinaGemmConfig* cfg, void* stream);
+
+/* End-to-end form with HOST buffers, the shape of run.rs `run_gemm`
+ * (alloc + memcpy_htod + launch + memcpy_dtoh, run.rs:484-528): copies A and B
+ * to context-owned device buffers, runs the GEMM, copies C back, all on
+ * `stream`, and returns without synchronising. Host buffers should be pinned. */
+int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const void* hostA,
+                     int64_t lda, const void* hostB, int64_t ldb, void* hostC, int64_t ldc,
+                     int64_t M, int64_t N, int64_t K, float alpha, const PatinaGemmConfig* cfg,
+                     void* stream);
+
+/* ---- host-only helpers (no device needed) ---------------------------------- */
+/* Argument check used by every entry point; on failure returns
+ * PATINA_GEMM_ERR_INVALID_ARG and, if err_out != NULL, a heap diagnostic. */
+int patina_gemm_validate(int in_type, int out_type, const void* A, int64_t lda, const void* B,
+                         int64_t ldb, const void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                         char** err_out);
+
+/* Launch plan for a problem on a device with `num_sms` SMs. */
+int patina_gemm_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
+                     const PatinaGemmConfig* cfg, int num_sms, PatinaGemmPlan* out);
+
+/* Derived encodings, exported so tests can pin them against the reference's
+ * constants (crates/patina/tests/layout.rs:33-68; v2_gemm_pipelined.ptx:192,197). */
+uint64_t patina_gemm_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                               int swizzle_code);
+uint32_t patina_gemm_idesc(int in_type, uint32_t umma_m, uint32_t umma_n);
+uint32_t patina_gemm_k_advance_units(uint32_t k_elems, int in_type);
+uint32_t patina_gemm_tmem_lane_offset(uint32_t warp_quarter);
+void patina_gemm_tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m,
+                            uint32_t* m_block, uint32_t* n_block);
+
+const char* patina_gemm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PATINA_GEMM_H */

@@ -1,0 +1,134 @@
+// patina_desc.h -- every derived encoding the GEMM depends on, as plain
+// host+device constexpr functions so that host unit tests can pin them:
+// the 64-bit UMMA shared-memory descriptor, the 32-bit instruction descriptor,
+// the K-advance inside a swizzle atom, TMEM addressing, and the persistent
+// tile scheduler's index map.
+//
+// Reference counterparts: crates/patina/src/layout.rs:162-228 (SWIZZLE_NONE,
+// f16 only: LBO 128, SBO 256, idesc_f16, tmem_lane_offset) and the constants
+// its PTX printer bakes in (mlir/lib/LowerToPTX.cpp:40-42). This header
+// generalises them to 128-byte swizzle, bf16 / f16 / e4m3 operands,
+// M in {128, 256} and N up to 256; the reference's own constants fall out as
+// special cases and are checked in the tests.
+#pragma once
+
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define PATINA_HD __host__ __device__ __forceinline__
+#else
+#define PATINA_HD inline
+#endif
+
+namespace patina {
+
+enum InputType : int { kF16 = 0, kBF16 = 1, kE4M3 = 2 };
+enum OutputType : int { kOutBF16 = 0, kOutF32 = 1 };
+enum SwizzleMode : int { kSwizzleNone = 0, kSwizzle128B = 2 };  // descriptor layout-type codes
+
+PATINA_HD constexpr uint32_t input_bytes(int t) { return t == kE4M3 ? 1u : 2u; }
+PATINA_HD constexpr uint32_t output_bytes(int t) { return t == kOutF32 ? 4u : 2u; }
+
+// ---- shared-memory matrix descriptor (tcgen05, "version 1") --------------
+//   [ 0,14) start address  >> 4      [16,30) leading-dim byte offset >> 4
+//   [32,46) stride-dim byte offset >> 4   [46,48) version = 1
+//   [61,64) layout type: 0 none, 2 = 128-byte swizzle
+PATINA_HD constexpr uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                       int swizzle) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)swizzle << 61);
+}
+
+// K-major operand tile whose rows are exactly one 128-byte swizzle span:
+// 8-row groups are 1024 bytes apart; the leading-dim offset is unused.
+PATINA_HD constexpr uint64_t smem_desc_sw128_kmajor(uint32_t smem_addr) {
+  return smem_desc(smem_addr, 0, 1024, kSwizzle128B);
+}
+
+// Descriptor units (16 bytes) to advance by `k_elems` along K inside the
+// 128-byte span: +2 per K16 of bf16/f16, +2 per K32 of e4m3.
+PATINA_HD constexpr uint32_t k_advance_units_sw128(uint32_t k_elems, int input_type) {
+  return (k_elems * input_bytes(input_type)) >> 4;
+}
+
+// The reference's no-swizzle layout: K-adjacent core matrices 128 B apart,
+// K advance = core matrices * LBO (layout.rs:176-179).
+PATINA_HD constexpr uint32_t k_advance_units_noswizzle(uint32_t k_elems, uint32_t elt_bytes,
+                                                       uint32_t lbo_bytes) {
+  return ((k_elems * elt_bytes / 16) * lbo_bytes) >> 4;
+}
+
+// ---- instruction descriptor (kind::f16 and kind::f8f6f4, dense) -----------
+//   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format
+//   [15] A major, [16] B major (0 = K-major)   [17,23) N >> 3   [24,29) M >> 4
+// kind::f16: 0 = f16, 1 = bf16.   kind::f8f6f4: 0 = e4m3.
+PATINA_HD constexpr uint32_t idesc(int input_type, uint32_t umma_m, uint32_t umma_n) {
+  uint32_t fmt = (input_type == kBF16) ? 1u : 0u;  // f16 -> 0, e4m3 -> 0 (in its own kind)
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
+}
+
+// Elements of K one MMA instruction consumes: 32 bytes of a K-major row.
+PATINA_HD constexpr uint32_t umma_k(int input_type) { return 32u / input_bytes(input_type); }
+
+// Legal (M, N) for one instruction: M=128 (one CTA) or 256 (CTA pair), N % 16 == 0, 16..256.
+PATINA_HD constexpr bool umma_shape_ok(uint32_t m, uint32_t n) {
+  return (m == 128 || m == 256) && n >= 16 && n <= 256 && (n % 16) == 0;
+}
+
+// ---- tensor memory ---------------------------------------------------------
+// Address = lane << 16 | column. A warp may only touch the 32-lane quarter
+// (warp_id % 4); lane quarter q starts at q << 21.
+PATINA_HD constexpr uint32_t tmem_lane_offset(uint32_t quarter) { return quarter << 21; }
+PATINA_HD constexpr uint32_t tmem_addr(uint32_t base, uint32_t lane, uint32_t col) {
+  return base + (lane << 16) + col;
+}
+
+// ---- persistent tile scheduler ---------------------------------------------
+// Linear tile index -> (m_block, n_block). Tiles are walked in bands of
+// `group_m` M-blocks; inside a band M runs fastest, so the CTAs that are
+// resident at the same time share a few A row-panels and B column-panels in L2.
+struct TileCoord {
+  uint32_t m, n;
+};
+
+PATINA_HD TileCoord tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m) {
+  if (group_m == 0) group_m = 1;
+  const uint32_t per_band = group_m * tiles_n;
+  const uint32_t band = t / per_band;
+  const uint32_t first_m = band * group_m;
+  const uint32_t rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+  const uint32_t in_band = t - band * per_band;
+  TileCoord c;
+  c.m = first_m + in_band % rows;
+  c.n = in_band / rows;
+  return c;
+}
+
+// ---- shared-memory plan ------------------------------------------------------
+struct SmemPlan {
+  uint32_t a_bytes, b_bytes, stage_bytes, stages, staging_bytes, barrier_bytes, total_bytes;
+};
+
+constexpr uint32_t kBlockKBytes = 128;      // one swizzle span of K per stage
+constexpr uint32_t kCtaRows = 128;          // accumulator rows (TMEM lanes) per CTA
+constexpr uint32_t kEpiWarps = 4;
+constexpr uint32_t kStoreBoxRows = 32;      // one epilogue warp's rows
+constexpr uint32_t kStagingBufBytes = kStoreBoxRows * 128;  // 32 rows x 128 B
+constexpr uint32_t kStagingBufs = 2;        // per epilogue warp
+constexpr uint32_t kBarrierRegionBytes = 256;
+constexpr uint32_t kMaxDynSmem = 232448;    // 227 KB
+
+PATINA_HD constexpr SmemPlan smem_plan(uint32_t cta_group, uint32_t block_n, uint32_t stages) {
+  SmemPlan p{};
+  p.a_bytes = kCtaRows * kBlockKBytes;
+  p.b_bytes = (block_n / cta_group) * kBlockKBytes;
+  p.stage_bytes = p.a_bytes + p.b_bytes;
+  p.stages = stages;
+  p.staging_bytes = kEpiWarps * kStagingBufs * kStagingBufBytes;
+  p.barrier_bytes = kBarrierRegionBytes;
+  // +1024: the ring is placed on the next 1024-byte boundary (swizzle atom).
+  p.total_bytes = 1024 + stages * p.stage_bytes + p.staging_bytes + p.barrier_bytes;
+  return p;
+}
+
+}  // namespace patina

@@ -1,0 +1,622 @@
+// patina_gemm.cu -- C ABI (include/patina_gemm.h) over the tcgen05 GEMM kernels:
+// argument validation, launch planning, TMA tensor-map construction and caching,
+// kernel dispatch. Host side of what the reference does in
+// harness/gemm_check.cpp:240-300 and crates/patina/src/run.rs:462-529, minus
+// the allocation and copies (device pointers belong to the caller here).
+#include "../../include/patina_gemm.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "patina_desc.h"
+#include "patina_gemm_kernel.cuh"
+
+using namespace patina;
+
+namespace {
+
+char* dup_cstr(const std::string& s) {
+  char* p = static_cast<char*>(std::malloc(s.size() + 1));
+  if (p) std::memcpy(p, s.c_str(), s.size() + 1);
+  return p;
+}
+
+std::string fmt(const char* f, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, f);
+  std::vsnprintf(buf, sizeof(buf), f, ap);
+  va_end(ap);
+  return std::string(buf);
+}
+
+// ------------------------------------------------------------------ kernels
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+
+struct KernelEntry {
+  int cta_group, block_n, stages, in_type, out_type;
+  KernelFn fn;
+  uint32_t smem_bytes;
+};
+
+#define PATINA_KERNEL(G, BN, S, IN, OUT) \
+  { G, BN, S, IN, OUT, gemm_tn_kernel<G, BN, S, IN, OUT>, GemmTraits<G, BN, S, IN, OUT>::kSmemBytes }
+
+const KernelEntry kKernels[] = {
+    // bf16 -> bf16
+    PATINA_KERNEL(2, 256, 6, kBF16, kOutBF16),
+    PATINA_KERNEL(1, 256, 4, kBF16, kOutBF16),
+    PATINA_KERNEL(2, 128, 8, kBF16, kOutBF16),
+    PATINA_KERNEL(1, 128, 6, kBF16, kOutBF16),
+    // e4m3 -> bf16
+    PATINA_KERNEL(2, 256, 6, kE4M3, kOutBF16),
+    PATINA_KERNEL(1, 256, 4, kE4M3, kOutBF16),
+    PATINA_KERNEL(1, 128, 6, kE4M3, kOutBF16),
+    // f16 -> f32 (the reference kernel's types)
+    PATINA_KERNEL(2, 256, 6, kF16, kOutF32),
+    PATINA_KERNEL(1, 256, 4, kF16, kOutF32),
+    PATINA_KERNEL(1, 128, 6, kF16, kOutF32),
+};
+constexpr int kNumKernels = sizeof(kKernels) / sizeof(kKernels[0]);
+
+bool type_pair_supported(int in_type, int out_type) {
+  for (int i = 0; i < kNumKernels; ++i)
+    if (kKernels[i].in_type == in_type && kKernels[i].out_type == out_type) return true;
+  return false;
+}
+
+// ------------------------------------------------------------------ planning
+uint32_t ceil_div(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
+
+// Fraction of the persistent slots that do useful work, times a speed factor of
+// the tile shape (bigger tiles move fewer operand bytes per flop).
+double config_score(const KernelEntry& k, int64_t M, int64_t N, int num_sms) {
+  const uint64_t tiles = (uint64_t)ceil_div(M, 128 * k.cta_group) * ceil_div(N, k.block_n);
+  const uint64_t slots = (uint64_t)(num_sms / k.cta_group);
+  if (slots == 0 || tiles == 0) return 0.0;
+  const uint64_t waves = (tiles + slots - 1) / slots;
+  // useful fraction of the padded tile area
+  const double area = (double)M * (double)N /
+                      ((double)ceil_div(M, 128 * k.cta_group) * 128 * k.cta_group *
+                       (double)ceil_div(N, k.block_n) * k.block_n);
+  const double eff = (double)tiles / (double)(waves * slots) * area;
+  double speed = 1.0;
+  if (k.cta_group == 1 && k.block_n == 256) speed = 0.92;
+  if (k.cta_group == 2 && k.block_n == 128) speed = 0.85;
+  if (k.cta_group == 1 && k.block_n == 128) speed = 0.75;
+  return eff * speed;
+}
+
+int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
+              const PatinaGemmConfig* cfg, int num_sms, PatinaGemmPlan* out,
+              const KernelEntry** entry_out, std::string* err) {
+  if (!type_pair_supported(in_type, out_type)) {
+    if (err) *err = fmt("unsupported type pair in=%d out=%d", in_type, out_type);
+    return PATINA_GEMM_ERR_INVALID_ARG;
+  }
+  if (num_sms <= 0) {
+    if (err) *err = "num_sms must be positive";
+    return PATINA_GEMM_ERR_INVALID_ARG;
+  }
+  PatinaGemmConfig c{};
+  if (cfg) c = *cfg;
+  const KernelEntry* best = nullptr;
+  if (c.cta_group != 0 || c.block_n != 0) {
+    // explicit request: fill in whatever was left open with the first match
+    for (int i = 0; i < kNumKernels && !best; ++i) {
+      const KernelEntry& k = kKernels[i];
+      if (k.in_type != in_type || k.out_type != out_type) continue;
+      if (c.cta_group != 0 && k.cta_group != c.cta_group) continue;
+      if (c.block_n != 0 && k.block_n != c.block_n) continue;
+      if (c.stages != 0 && k.stages != c.stages) continue;
+      best = &k;
+    }
+    if (!best) {
+      if (err)
+        *err = fmt("no kernel for cta_group=%d block_n=%d stages=%d with these types", c.cta_group,
+                   c.block_n, c.stages);
+      return PATINA_GEMM_ERR_INVALID_ARG;
+    }
+  } else {
+    double best_score = -1.0;
+    for (int i = 0; i < kNumKernels; ++i) {
+      const KernelEntry& k = kKernels[i];
+      if (k.in_type != in_type || k.out_type != out_type) continue;
+      if (c.stages != 0 && k.stages != c.stages) continue;
+      if (k.cta_group == 2 && num_sms < 2) continue;
+      const double s = config_score(k, M, N, num_sms);
+      if (s > best_score) {
+        best_score = s;
+        best = &k;
+      }
+    }
+    if (!best) {
+      if (err) *err = "no kernel matches the requested stage count";
+      return PATINA_GEMM_ERR_INVALID_ARG;
+    }
+  }
+  PatinaGemmPlan p{};
+  p.cta_group = best->cta_group;
+  p.block_n = best->block_n;
+  p.stages = best->stages;
+  p.tiles_m = ceil_div(M, 128 * best->cta_group);
+  p.tiles_n = ceil_div(N, best->block_n);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t kelems = kBlockKBytes / input_bytes(in_type);
+  p.k_blocks = ceil_div(K, kelems);
+  p.group_m = c.group_m > 0 ? c.group_m : 8;
+  uint32_t slots = (uint32_t)(num_sms / best->cta_group);
+  if (c.max_ctas > 0 && (uint32_t)(c.max_ctas / best->cta_group) < slots)
+    slots = (uint32_t)(c.max_ctas / best->cta_group);
+  if (slots == 0) slots = 1;
+  const uint32_t clusters = p.num_tiles < slots ? p.num_tiles : slots;
+  p.grid = clusters * best->cta_group;
+  p.block = 192;
+  p.cluster = best->cta_group;
+  p.smem_bytes = best->smem_bytes;
+  p.tmem_cols = 2 * best->block_n;
+  const SmemPlan sp = smem_plan(best->cta_group, best->block_n, best->stages);
+  p.stage_bytes = sp.stage_bytes;
+  p.expect_tx_bytes = sp.stage_bytes * best->cta_group;
+  p.idesc = idesc(in_type, 128 * best->cta_group, best->block_n);
+  if (out) *out = p;
+  if (entry_out) *entry_out = best;
+  return PATINA_GEMM_OK;
+}
+
+int validate_args(int in_type, int out_type, const void* A, int64_t lda, const void* B, int64_t ldb,
+                  const void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, std::string* err) {
+  auto fail = [&](const std::string& m) {
+    if (err) *err = m;
+    return (int)PATINA_GEMM_ERR_INVALID_ARG;
+  };
+  if (!type_pair_supported(in_type, out_type))
+    return fail(fmt("unsupported type pair in=%d out=%d", in_type, out_type));
+  if (M < 0 || N < 0 || K < 0) return fail(fmt("negative dimension M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K));
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL)
+    return fail("dimension exceeds 2^31-1");
+  if (M == 0 || N == 0) return PATINA_GEMM_OK;
+  if (!C) return fail("C is null");
+  const int64_t ib = input_bytes(in_type), ob = output_bytes(out_type);
+  if ((reinterpret_cast<uintptr_t>(C) & 15u) != 0) return fail("C is not 16-byte aligned");
+  if (ldc < N) return fail(fmt("ldc=%lld < N=%lld", (long long)ldc, (long long)N));
+  if ((ldc * ob) % 16 != 0) return fail(fmt("ldc=%lld: row pitch is not a multiple of 16 bytes", (long long)ldc));
+  if (K == 0) return PATINA_GEMM_OK;
+  if (!A) return fail("A is null");
+  if (!B) return fail("B is null");
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) != 0) return fail("A is not 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(B) & 15u) != 0) return fail("B is not 16-byte aligned");
+  if (lda < K) return fail(fmt("lda=%lld < K=%lld", (long long)lda, (long long)K));
+  if (ldb < K) return fail(fmt("ldb=%lld < K=%lld", (long long)ldb, (long long)K));
+  if ((lda * ib) % 16 != 0) return fail(fmt("lda=%lld: row pitch is not a multiple of 16 bytes", (long long)lda));
+  if ((ldb * ib) % 16 != 0) return fail(fmt("ldb=%lld: row pitch is not a multiple of 16 bytes", (long long)ldb));
+  return PATINA_GEMM_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------- context
+struct TensorMapKey {
+  const void* ptr;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows, box_cols;
+  int dtype;  // CUtensorMapDataType
+  bool operator==(const TensorMapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows && box_cols == o.box_cols && dtype == o.dtype;
+  }
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct PatinaGemmContext {
+  int device = 0;
+  int num_sms = 0;
+  int cc_major = 0, cc_minor = 0;
+  uint32_t* d_status = nullptr;  // 4 words
+  uint64_t wait_limit_ns = 2000000000ull;
+  uint64_t launches = 0;
+  std::string last_error;
+  EncodeTiledFn encode = nullptr;
+  std::vector<std::pair<TensorMapKey, CUtensorMap>> tmaps;  // small most-recent-first cache
+  bool smem_attr_set[kNumKernels] = {};
+  int max_clusters[kNumKernels] = {};  // co-resident clusters per kernel (pairs only)
+  // device staging for patina_gemm_host
+  void* d_a = nullptr;
+  void* d_b = nullptr;
+  void* d_c = nullptr;
+  size_t cap_a = 0, cap_b = 0, cap_c = 0;
+};
+
+namespace {
+
+int set_error(PatinaGemmContext* ctx, int code, const std::string& msg) {
+  if (ctx) ctx->last_error = msg;
+  return code;
+}
+
+int cuda_fail(PatinaGemmContext* ctx, cudaError_t e, const char* what) {
+  return set_error(ctx, PATINA_GEMM_ERR_CUDA,
+                   fmt("%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e)));
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+// A K-major matrix [rows, cols] with row pitch ld elements, tiled in boxes of
+// box_rows x box_cols where box_cols spans exactly 128 bytes, 128-byte swizzle.
+// (The reference's map is 4-D, unswizzled: harness/gemm_check.cpp:127-147.)
+int get_tensor_map(PatinaGemmContext* ctx, const void* ptr, CUtensorMapDataType dtype,
+                   uint32_t elt_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                   uint32_t box_rows, uint32_t box_cols, CUtensorMap* out) {
+  TensorMapKey key{ptr, rows, cols, ld, box_rows, box_cols, (int)dtype};
+  for (size_t i = 0; i < ctx->tmaps.size(); ++i) {
+    if (ctx->tmaps[i].first == key) {
+      *out = ctx->tmaps[i].second;
+      return PATINA_GEMM_OK;
+    }
+  }
+  if (box_cols * elt_bytes != 128 || box_rows == 0 || box_rows > 256)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "internal: illegal TMA box");
+  const cuuint64_t gdim[2] = {cols, rows};
+  const cuuint64_t gstride[1] = {ld * elt_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estride[2] = {1, 1};
+  CUtensorMap tm;
+  CUresult rc = ctx->encode(&tm, dtype, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return set_error(ctx, PATINA_GEMM_ERR_CUDA,
+                     fmt("cuTensorMapEncodeTiled failed (CUresult %d) for %llux%llu ld=%llu", (int)rc,
+                         (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld));
+  if (ctx->tmaps.size() >= 64) ctx->tmaps.pop_back();
+  ctx->tmaps.insert(ctx->tmaps.begin(), std::make_pair(key, tm));
+  *out = tm;
+  return PATINA_GEMM_OK;
+}
+
+CUtensorMapDataType tmap_in_type(int in_type) {
+  switch (in_type) {
+    case kF16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    case kBF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  }
+}
+
+int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A, int64_t lda,
+                const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  std::string err;
+  int rc = validate_args(in_type, out_type, A, lda, B, ldb, C, ldc, M, N, K, &err);
+  if (rc != PATINA_GEMM_OK) return set_error(ctx, rc, err);
+  if (M == 0 || N == 0) return PATINA_GEMM_OK;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok) return set_error(ctx, PATINA_GEMM_ERR_CUDA, "cudaSetDevice failed");
+  const uint32_t ob = output_bytes(out_type);
+  if (K == 0) {
+    cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * ob, 0, (size_t)N * ob, (size_t)M, stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemset2DAsync");
+    return PATINA_GEMM_OK;
+  }
+  PatinaGemmPlan plan;
+  const KernelEntry* k = nullptr;
+  rc = make_plan(in_type, out_type, M, N, K, cfg, ctx->num_sms, &plan, &k, &err);
+  if (rc != PATINA_GEMM_OK) return set_error(ctx, rc, err);
+
+  const uint32_t ib = input_bytes(in_type);
+  const uint32_t kelems = kBlockKBytes / ib;
+  CUtensorMap tm_a, tm_b, tm_c;
+  rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
+                      kCtaRows, kelems, &tm_a);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, B, tmap_in_type(in_type), ib, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
+                      (uint32_t)(k->block_n / k->cta_group), kelems, &tm_b);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, C,
+                      out_type == kOutF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                      ob, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kStoreBoxRows, 128 / ob, &tm_c);
+  if (rc != PATINA_GEMM_OK) return rc;
+
+  const int ki = (int)(k - kKernels);
+  if (!ctx->smem_attr_set[ki]) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k->fn),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)k->smem_bytes);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(smem)");
+    ctx->smem_attr_set[ki] = true;
+  }
+
+  if (k->cta_group > 1) {
+    // A persistent grid must not exceed what can be resident at once, or the
+    // late clusters would start their tile lists after the others finish.
+    if (ctx->max_clusters[ki] == 0) {
+      cudaLaunchConfig_t qc{};
+      qc.gridDim = dim3((unsigned)(ctx->num_sms / k->cta_group) * k->cta_group, 1, 1);
+      qc.blockDim = dim3(plan.block, 1, 1);
+      qc.dynamicSmemBytes = k->smem_bytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = (unsigned)k->cta_group;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      qc.attrs = qa;
+      qc.numAttrs = 1;
+      int n = 0;
+      cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(k->fn), &qc);
+      if (qe != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = ctx->num_sms / k->cta_group;
+      }
+      ctx->max_clusters[ki] = n;
+    }
+    const uint32_t cap = (uint32_t)ctx->max_clusters[ki] * k->cta_group;
+    if (plan.grid > cap) plan.grid = cap;
+  }
+
+  GemmParams p{};
+  p.M = (uint32_t)M;
+  p.N = (uint32_t)N;
+  p.K = (uint32_t)K;
+  p.tiles_m = plan.tiles_m;
+  p.tiles_n = plan.tiles_n;
+  p.num_tiles = plan.num_tiles;
+  p.k_blocks = plan.k_blocks;
+  p.group_m = (uint32_t)plan.group_m;
+  p.alpha = alpha;
+  p.status = ctx->d_status;
+  p.wait_limit_ns = ctx->wait_limit_ns;
+
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(plan.grid, 1, 1);
+  lc.blockDim = dim3(plan.block, 1, 1);
+  lc.dynamicSmemBytes = k->smem_bytes;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)k->cta_group;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = (k->cta_group > 1) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&lc, k->fn, tm_a, tm_b, tm_c, p);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaLaunchKernelEx");
+  ctx->launches += 1;
+  return PATINA_GEMM_OK;
+}
+
+int grow(PatinaGemmContext* ctx, void** p, size_t* cap, size_t need) {
+  if (*cap >= need) return PATINA_GEMM_OK;
+  if (*p) cudaFree(*p);
+  *p = nullptr;
+  *cap = 0;
+  cudaError_t e = cudaMalloc(p, need);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMalloc(staging)");
+  *cap = need;
+  return PATINA_GEMM_OK;
+}
+
+}  // namespace
+
+// =============================================================== C ABI ======
+extern "C" {
+
+const char* patina_gemm_version(void) { return "patina-b200-gemm 0.1 (sm_100a, tcgen05)"; }
+
+void patina_gemm_string_free(char* s) { std::free(s); }
+
+char* patina_gemm_last_error(PatinaGemmContext* ctx) {
+  if (!ctx || ctx->last_error.empty()) return nullptr;
+  return dup_cstr(ctx->last_error);
+}
+
+int patina_gemm_context_create(int device, PatinaGemmContext** out) {
+  if (!out) return PATINA_GEMM_ERR_INVALID_ARG;
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count <= 0) {
+    cudaGetLastError();
+    return PATINA_GEMM_ERR_UNSUPPORTED_ARCH;  // no CUDA device at all: nothing can run here
+  }
+  if (device < 0 || device >= count) return PATINA_GEMM_ERR_INVALID_ARG;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return PATINA_GEMM_ERR_CUDA;
+  if (prop.major != 10) return PATINA_GEMM_ERR_UNSUPPORTED_ARCH;  // tcgen05 needs sm_100a
+  PatinaGemmContext* ctx = new PatinaGemmContext();
+  ctx->device = device;
+  ctx->num_sms = prop.multiProcessorCount;
+  ctx->cc_major = prop.major;
+  ctx->cc_minor = prop.minor;
+  DeviceGuard guard(device);
+  if (!guard.ok) {
+    delete ctx;
+    return PATINA_GEMM_ERR_CUDA;
+  }
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+    delete ctx;
+    return PATINA_GEMM_ERR_CUDA;
+  }
+  ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  e = cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), 4 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 4 * sizeof(uint32_t));
+  if (e != cudaSuccess) {
+    delete ctx;
+    return PATINA_GEMM_ERR_CUDA;
+  }
+  *out = ctx;
+  return PATINA_GEMM_OK;
+}
+
+void patina_gemm_context_destroy(PatinaGemmContext* ctx) {
+  if (!ctx) return;
+  {
+    DeviceGuard guard(ctx->device);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_a) cudaFree(ctx->d_a);
+    if (ctx->d_b) cudaFree(ctx->d_b);
+    if (ctx->d_c) cudaFree(ctx->d_c);
+  }
+  delete ctx;
+}
+
+int patina_gemm_set_wait_limit_ns(PatinaGemmContext* ctx, uint64_t ns) {
+  if (!ctx || ns == 0) return PATINA_GEMM_ERR_INVALID_ARG;
+  ctx->wait_limit_ns = ns;
+  return PATINA_GEMM_OK;
+}
+
+uint64_t patina_gemm_launch_count(PatinaGemmContext* ctx) { return ctx ? ctx->launches : 0; }
+
+int patina_gemm_status(PatinaGemmContext* ctx, void* stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaStreamSynchronize");
+  uint32_t st[4] = {0, 0, 0, 0};
+  e = cudaMemcpy(st, ctx->d_status, sizeof(st), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy(status)");
+  if (st[0] == 0) return PATINA_GEMM_OK;
+  static const char* const names[] = {"ok",
+                                      "producer waiting for an empty stage",
+                                      "MMA issuer waiting for a full stage",
+                                      "MMA issuer waiting for a free accumulator",
+                                      "epilogue waiting for a finished accumulator",
+                                      "MMA issuer draining its last accumulator",
+                                      "split-K reducer"};
+  const char* what = st[0] < sizeof(names) / sizeof(names[0]) ? names[st[0]] : "unknown";
+  set_error(ctx, PATINA_GEMM_ERR_TIMEOUT,
+            fmt("device wait expired: %s (code %u, block %u, detail %u)", what, st[0], st[1], st[2]));
+  cudaMemset(ctx->d_status, 0, sizeof(st));
+  return PATINA_GEMM_ERR_TIMEOUT;
+}
+
+int patina_gemm_ex(PatinaGemmContext* ctx, int in_type, int out_type, const void* A, int64_t lda,
+                   const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N,
+                   int64_t K, float alpha, const PatinaGemmConfig* cfg, void* stream) {
+  return launch_gemm(ctx, in_type, out_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, cfg,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_bf16_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                        int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                        float alpha, void* stream) {
+  return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C, ldc, M, N, K, alpha, nullptr,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_fp8e4m3_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                           int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                           float scale_a, float scale_b, void* stream) {
+  return launch_gemm(ctx, kE4M3, kOutBF16, A, lda, B, ldb, C, ldc, M, N, K, scale_a * scale_b,
+                     nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_f16_tn_f32out(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                              int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                              float alpha, void* stream) {
+  return launch_gemm(ctx, kF16, kOutF32, A, lda, B, ldb, C, ldc, M, N, K, alpha, nullptr,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const void* hostA,
+                     int64_t lda, const void* hostB, int64_t ldb, void* hostC, int64_t ldc,
+                     int64_t M, int64_t N, int64_t K, float alpha, const PatinaGemmConfig* cfg,
+                     void* stream_v) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  if (!type_pair_supported(in_type, out_type))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "unsupported type pair");
+  if (M < 0 || N < 0 || K < 0 || lda < K || ldb < K || ldc < N)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "bad dimensions or leading dimensions");
+  if (M == 0 || N == 0) return PATINA_GEMM_OK;
+  if (!hostC || (K > 0 && (!hostA || !hostB)))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "null host pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  DeviceGuard guard(ctx->device);
+  const size_t ib = input_bytes(in_type), ob = output_bytes(out_type);
+  // Device copies are dense with the pitch rounded up to 16 bytes.
+  const int64_t dk = (int64_t)((((size_t)K * ib + 15) / 16) * 16 / ib);
+  const int64_t dn = (int64_t)((((size_t)N * ob + 15) / 16) * 16 / ob);
+  int rc;
+  if ((rc = grow(ctx, &ctx->d_a, &ctx->cap_a, (size_t)M * dk * ib + 16)) != 0) return rc;
+  if ((rc = grow(ctx, &ctx->d_b, &ctx->cap_b, (size_t)N * dk * ib + 16)) != 0) return rc;
+  if ((rc = grow(ctx, &ctx->d_c, &ctx->cap_c, (size_t)M * dn * ob + 16)) != 0) return rc;
+  cudaError_t e;
+  if (K > 0) {
+    e = cudaMemcpy2DAsync(ctx->d_a, (size_t)dk * ib, hostA, (size_t)lda * ib, (size_t)K * ib,
+                          (size_t)M, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(A)");
+    e = cudaMemcpy2DAsync(ctx->d_b, (size_t)dk * ib, hostB, (size_t)ldb * ib, (size_t)K * ib,
+                          (size_t)N, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(B)");
+  }
+  rc = launch_gemm(ctx, in_type, out_type, ctx->d_a, dk, ctx->d_b, dk, ctx->d_c, dn, M, N, K, alpha,
+                   cfg, stream);
+  if (rc != PATINA_GEMM_OK) return rc;
+  e = cudaMemcpy2DAsync(hostC, (size_t)ldc * ob, ctx->d_c, (size_t)dn * ob, (size_t)N * ob,
+                        (size_t)M, cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(C)");
+  return PATINA_GEMM_OK;
+}
+
+// ---- host-only helpers ------------------------------------------------------
+int patina_gemm_validate(int in_type, int out_type, const void* A, int64_t lda, const void* B,
+                         int64_t ldb, const void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                         char** err_out) {
+  std::string err;
+  if (err_out) *err_out = nullptr;
+  int rc = validate_args(in_type, out_type, A, lda, B, ldb, C, ldc, M, N, K, &err);
+  if (rc != PATINA_GEMM_OK && err_out) *err_out = dup_cstr(err);
+  return rc;
+}
+
+int patina_gemm_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
+                     const PatinaGemmConfig* cfg, int num_sms, PatinaGemmPlan* out) {
+  if (!out || M <= 0 || N <= 0 || K <= 0) return PATINA_GEMM_ERR_INVALID_ARG;
+  return make_plan(in_type, out_type, M, N, K, cfg, num_sms, out, nullptr, nullptr);
+}
+
+uint64_t patina_gemm_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                               int swizzle_code) {
+  return smem_desc(smem_addr, lbo_bytes, sbo_bytes, swizzle_code);
+}
+uint32_t patina_gemm_idesc(int in_type, uint32_t umma_m, uint32_t umma_n) {
+  return idesc(in_type, umma_m, umma_n);
+}
+uint32_t patina_gemm_k_advance_units(uint32_t k_elems, int in_type) {
+  return k_advance_units_sw128(k_elems, in_type);
+}
+uint32_t patina_gemm_tmem_lane_offset(uint32_t warp_quarter) { return tmem_lane_offset(warp_quarter); }
+void patina_gemm_tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m,
+                            uint32_t* m_block, uint32_t* n_block) {
+  const TileCoord c = tile_coord(t, tiles_m, tiles_n, group_m);
+  if (m_block) *m_block = c.m;
+  if (n_block) *n_block = c.n;
+}
+
+}  // extern "C"

@@ -1,0 +1,355 @@
+// patina_gemm_kernel.cuh -- the persistent, warp-specialised tcgen05 GEMM.
+//
+//   C[M,N] = alpha * A[M,K] * B[N,K]^T      (both operands K-major, "TN")
+//
+// One CTA = 6 warps with fixed roles, the same split the reference's generated
+// kernel uses (crates/patina/tests/golden/v2_gemm_pipelined.ptx:89-94):
+//   warp 0      TMA producer   (one elected lane)
+//   warp 1      MMA issuer     (one elected lane; the whole warp owns TMEM alloc/dealloc)
+//   warps 2..5  epilogue       (TMEM -> registers -> swizzled SMEM -> TMA store)
+//
+// What is different from that kernel (which runs one 128x128 tile in one CTA):
+//   * persistent: each CTA (or CTA pair) walks a list of output tiles
+//     (patina::tile_coord), so prologue cost is paid once per SM;
+//   * 128-byte-swizzled K-major stages of 128 bytes of K, kStages deep;
+//   * two accumulators in TMEM (2 x BN columns) so the epilogue of tile i
+//     overlaps the mainloop of tile i+1;
+//   * optional CTA pair (kCtaGroup == 2): tcgen05.mma.cta_group::2 computes a
+//     256 x BN tile; each CTA loads its own 128 rows of A and its own BN/2 rows
+//     of B; the pair leader issues the MMAs. No TMA multicast is used: each
+//     CTA's loads land in its own shared memory and count on the leader's
+//     barrier;
+//   * every wait is bounded (WaitCtx): on expiry the CTA records a status code,
+//     raises an abort flag that all roles poll, drains and returns.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "patina_desc.h"
+#include "patina_ptx.cuh"
+
+namespace patina {
+
+struct GemmParams {
+  uint32_t M, N, K;
+  uint32_t tiles_m, tiles_n, num_tiles;  // in units of the cluster tile
+  uint32_t k_blocks;                     // ceil(K / elements per 128 bytes)
+  uint32_t group_m;                      // scheduler band height (tiles)
+  float alpha;
+  uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
+  uint64_t wait_limit_ns;  // bound for every barrier wait
+};
+
+enum StatusCode : uint32_t {
+  kStatusOk = 0,
+  kTimeoutProducerEmpty = 1,
+  kTimeoutMmaFull = 2,
+  kTimeoutMmaTmemEmpty = 3,
+  kTimeoutEpilogueTmemFull = 4,
+  kTimeoutMmaDrain = 5,
+};
+
+struct WaitCtx {
+  volatile uint32_t* abort_flag;  // this CTA's flag (shared memory)
+  uint32_t peer_abort_addr;       // shared::cluster address of the partner's flag (pair only)
+  uint32_t* status;
+  uint64_t limit_ns;
+  bool has_peer;
+};
+
+__device__ __noinline__ void raise_abort(const WaitCtx& w, uint32_t code, uint32_t detail) {
+  *w.abort_flag = 1u;
+  if (w.has_peer) ptx::st_cluster_u32(w.peer_abort_addr, 1u);
+  if (atomicCAS(w.status, 0u, code) == 0u) {
+    w.status[1] = blockIdx.x;
+    w.status[2] = detail;
+  }
+  __threadfence();
+}
+
+// Returns false when the wait was abandoned (limit reached here, or another
+// role raised the abort flag).
+template <bool kClusterScope>
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx& w,
+                                             uint32_t code, uint32_t detail) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  for (;;) {
+    const bool done = kClusterScope ? ptx::mbar_try_wait_cluster(bar, parity)
+                                    : ptx::mbar_try_wait(bar, parity);
+    if (done) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*w.abort_flag) return false;
+      const uint64_t now = ptx::globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > w.limit_ns) {
+        raise_abort(w, code, detail);
+        return false;
+      }
+    }
+  }
+}
+
+template <int kCtaGroup, int BN, int kStages, int kIn, int kOut>
+struct GemmTraits {
+  static constexpr uint32_t kThreads = 192;
+  static constexpr uint32_t kBlockKElems = kBlockKBytes / input_bytes(kIn);
+  static constexpr uint32_t kUmmaK = umma_k(kIn);
+  static constexpr uint32_t kUmmaPerStage = kBlockKElems / kUmmaK;  // 4
+  static constexpr uint32_t kBRows = BN / kCtaGroup;                // B rows this CTA loads
+  static constexpr uint32_t kABytes = kCtaRows * kBlockKBytes;
+  static constexpr uint32_t kBBytes = kBRows * kBlockKBytes;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kTmemCols = 2 * BN;
+  static constexpr uint32_t kChunkCols = 128 / output_bytes(kOut);  // one 128-byte row segment
+  static constexpr uint32_t kChunks = BN / kChunkCols;
+  static constexpr uint32_t kSmemBytes = smem_plan(kCtaGroup, BN, kStages).total_bytes;
+  static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
+  static_assert(kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
+                "TMEM allocations are powers of two");
+  static_assert((kBBytes % 1024) == 0, "swizzle atoms must stay 1024-byte aligned");
+  static_assert(kSmemBytes <= kMaxDynSmem, "shared-memory plan exceeds 227 KB");
+  static_assert((2 * kStages + 4) * 8 + 8 <= kBarrierRegionBytes, "barrier region too small");
+};
+
+template <int kCtaGroup, int BN, int kStages, int kIn, int kOut>
+__global__ void __launch_bounds__(192, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+  using T = GemmTraits<kCtaGroup, BN, kStages, kIn, kOut>;
+  constexpr bool kPair = (kCtaGroup == 2);
+  constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t ring = smem_base;
+  const uint32_t staging = ring + kStages * T::kStageBytes;
+  const uint32_t bars = staging + kEpiWarps * kStagingBufs * kStagingBufBytes;
+  const uint32_t full_bar = bars;                      // [kStages]
+  const uint32_t empty_bar = bars + 8u * kStages;      // [kStages]
+  const uint32_t tfull_bar = bars + 16u * kStages;     // [2]
+  const uint32_t tempty_bar = tfull_bar + 16u;         // [2]
+  const uint32_t tmem_slot = tempty_bar + 16u;         // u32
+  const uint32_t abort_slot = tmem_slot + 4u;          // u32
+  uint8_t* const smem_generic = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  volatile uint32_t* const tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      smem_generic + (tmem_slot - smem_base));
+  volatile uint32_t* const abort_ptr = reinterpret_cast<volatile uint32_t*>(
+      smem_generic + (abort_slot - smem_base));
+
+  const uint32_t warp_idx = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;
+  const uint32_t peer_rank = cta_rank ^ 1u;
+  const uint32_t cluster_id = blockIdx.x / kCtaGroup;
+  const uint32_t num_clusters = gridDim.x / kCtaGroup;
+
+  WaitCtx w;
+  w.abort_flag = abort_ptr;
+  w.peer_abort_addr = kPair ? ptx::mapa(abort_slot, peer_rank) : 0u;
+  w.status = p.status;
+  w.limit_ns = p.wait_limit_ns;
+  w.has_peer = kPair;
+
+  // ---------------------------------------------------------------- prologue
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tm_a);
+    ptx::prefetch_tensormap(&tm_b);
+    ptx::prefetch_tensormap(&tm_c);
+    for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+      ptx::mbar_init(full_bar + 8u * s, 1);
+      ptx::mbar_init(empty_bar + 8u * s, 1);
+    }
+    for (uint32_t b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar + 8u * b, 1);
+      ptx::mbar_init(tempty_bar + 8u * b, kEpiWarps * kCtaGroup);
+    }
+    *abort_ptr = 0u;
+    ptx::fence_mbar_init();
+  }
+  if (warp_idx == 1) {
+    ptx::tmem_alloc<kCtaGroup>(tmem_slot, T::kTmemCols);
+    ptx::tmem_relinquish<kCtaGroup>();
+  }
+  ptx::tc_fence_before_sync();
+  if constexpr (kPair) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // ------------------------------------------------------------ TMA producer
+  if (warp_idx == 0) {
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
+      for (uint32_t t = cluster_id; t < p.num_tiles; t += num_clusters) {
+        const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+        const int32_t a_row = (int32_t)((c.m * kCtaGroup + cta_rank) * kCtaRows);
+        const int32_t b_row = (int32_t)(c.n * BN + cta_rank * T::kBRows);
+        bool ok = true;
+        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+          ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
+          if (!ok) break;
+          const uint32_t sa = ring + s * T::kStageBytes;
+          const uint32_t sb = sa + T::kABytes;
+          const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
+          if constexpr (kPair) {
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, 2u * T::kStageBytes);
+            ptx::tma_load_2d_pair(sa, &tm_a, leader_full + 8u * s, k0, a_row);
+            ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
+          } else {
+            ptx::mbar_arrive_expect_tx(full_bar + 8u * s, T::kStageBytes);
+            ptx::tma_load_2d(sa, &tm_a, full_bar + 8u * s, k0, a_row);
+            ptx::tma_load_2d(sb, &tm_b, full_bar + 8u * s, k0, b_row);
+          }
+          if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+      }
+    }
+  }
+  // -------------------------------------------------------------- MMA issuer
+  else if (warp_idx == 1) {
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc_v = idesc(kIn, kCtaRows * kCtaGroup, BN);
+      const uint32_t peer_empty = kPair ? ptx::mapa(empty_bar, 1) : 0u;
+      const uint32_t peer_tfull = kPair ? ptx::mapa(tfull_bar, 1) : 0u;
+      uint32_t s = 0, ph = 0, it = 0;
+      bool ok = true;
+      for (uint32_t t = cluster_id; t < p.num_tiles && ok; t += num_clusters, ++it) {
+        const uint32_t buf = it & 1u, acc_ph = (it >> 1) & 1u;
+        ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+          ok = bounded_wait<kPair>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = ring + s * T::kStageBytes;
+          const uint64_t da = smem_desc_sw128_kmajor(sa);
+          const uint64_t db = smem_desc_sw128_kmajor(sa + T::kABytes);
+#pragma unroll
+          for (uint32_t k = 0; k < T::kUmmaPerStage; ++k) {
+            const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
+            ptx::umma<kCtaGroup, kKind>(tmem_d, da + adv, db + adv, idesc_v, (kb | k) != 0u);
+          }
+          ptx::umma_commit<kCtaGroup>(empty_bar + 8u * s);
+          if constexpr (kPair) ptx::umma_commit<kCtaGroup>(peer_empty + 8u * s);
+          if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit<kCtaGroup>(tfull_bar + 8u * buf);
+        if constexpr (kPair) ptx::umma_commit<kCtaGroup>(peer_tfull + 8u * buf);
+      }
+      // Every MMA must have retired before shared memory or TMEM is released:
+      // wait for the last accumulator's completion here as well.
+      if (ok && it > 0) {
+        const uint32_t last = it - 1;
+        bounded_wait<kPair>(tfull_bar + 8u * (last & 1u), (last >> 1) & 1u, w, kTimeoutMmaDrain, it);
+      }
+    }
+  }
+  // ---------------------------------------------------------------- epilogue
+  else {
+    const uint32_t q = warp_idx & 3u;          // TMEM lane quarter this warp may touch
+    const uint32_t e = warp_idx - 2u;          // staging-buffer owner index
+    const uint32_t stg0 = staging + e * (kStagingBufs * kStagingBufBytes);
+    const uint32_t leader_tempty = kPair ? ptx::mapa(tempty_bar, 0) : tempty_bar;
+    const uint32_t row_sw = lane & 7u;
+    uint32_t it = 0, sbuf = 0;
+    bool ok = true;
+    for (uint32_t t = cluster_id; t < p.num_tiles && ok; t += num_clusters, ++it) {
+      const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+      const uint32_t buf = it & 1u, acc_ph = (it >> 1) & 1u;
+      ok = bounded_wait<kPair>(tfull_bar + 8u * buf, acc_ph, w, kTimeoutEpilogueTmemFull, t);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t row0 = (c.m * kCtaGroup + cta_rank) * kCtaRows + q * kStoreBoxRows;
+      const uint32_t col0 = c.n * BN;
+      const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * BN;
+#pragma unroll 1
+      for (uint32_t ch = 0; ch < T::kChunks; ++ch) {
+        uint32_t v[kOut == kOutBF16 ? 64 : 32];
+        ptx::tmem_ld_32x32b_x32(taddr + ch * T::kChunkCols, &v[0]);
+        if constexpr (kOut == kOutBF16)
+          ptx::tmem_ld_32x32b_x32(taddr + ch * T::kChunkCols + 32u, &v[32]);
+        ptx::tmem_ld_wait();
+        if (ch == T::kChunks - 1) {
+          // Accumulator fully read: hand the TMEM buffer back to the MMA issuer.
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kPair) ptx::mbar_arrive_cluster(leader_tempty + 8u * buf);
+            else ptx::mbar_arrive(tempty_bar + 8u * buf);
+          }
+        }
+        // The staging buffer written two chunks ago must have been read by its store.
+        if (lane == 0) ptx::tma_store_wait_read<kStagingBufs - 1>();
+        __syncwarp();
+        const uint32_t row_addr = stg0 + sbuf * kStagingBufBytes + lane * 128u;
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) {
+          uint32_t w0, w1, w2, w3;
+          if constexpr (kOut == kOutBF16) {
+            auto pack = [&](uint32_t a, uint32_t b) -> uint32_t {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a) * p.alpha,
+                                                       __uint_as_float(b) * p.alpha);
+              return *reinterpret_cast<uint32_t*>(&h);
+            };
+            w0 = pack(v[8 * j + 0], v[8 * j + 1]);
+            w1 = pack(v[8 * j + 2], v[8 * j + 3]);
+            w2 = pack(v[8 * j + 4], v[8 * j + 5]);
+            w3 = pack(v[8 * j + 6], v[8 * j + 7]);
+          } else {
+            w0 = __float_as_uint(__uint_as_float(v[4 * j + 0]) * p.alpha);
+            w1 = __float_as_uint(__uint_as_float(v[4 * j + 1]) * p.alpha);
+            w2 = __float_as_uint(__uint_as_float(v[4 * j + 2]) * p.alpha);
+            w3 = __float_as_uint(__uint_as_float(v[4 * j + 3]) * p.alpha);
+          }
+          const uint32_t dst = row_addr + ((j ^ row_sw) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1),
+                       "r"(w2), "r"(w3)
+                       : "memory");
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t cc = col0 + ch * T::kChunkCols;
+          if (row0 < p.M && cc < p.N)
+            ptx::tma_store_2d(&tm_c, stg0 + sbuf * kStagingBufBytes, (int32_t)cc, (int32_t)row0);
+          ptx::tma_store_commit();
+        }
+        sbuf ^= 1u;
+      }
+    }
+    if (lane == 0) ptx::tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  if (*abort_ptr) {
+    // Give copies and MMAs that are still in flight time to land before the
+    // shared memory and TMEM they target are released.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  __syncwarp();
+  ptx::tc_fence_before_sync();
+  if constexpr (kPair) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  ptx::tc_fence_after_sync();
+  if (warp_idx == 1) ptx::tmem_dealloc<kCtaGroup>(tmem_base, T::kTmemCols);
+}
+
+}  // namespace patina

@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME]
+
+One "step" is one GEMM over one batch of synthetic operands. At N = 1 the
+workload is the bf16 TN GEMM M = N = K = 8192 (fp32 accumulate, bf16 out). At
+N > 1 (one process per GPU, launched by torch.distributed.run) every rank owns
+an 8192-column shard of an 8192 x (8192 N) x 8192 problem: A is replicated, B
+and C are split by N columns, no collective is on the data path ("weak"
+scaling: per-GPU work is fixed).
+
+Prints ONE JSON line (rank 0). `value` times the kernel with operands resident
+in HBM; `e2e` times the public host-buffer call (H2D + GEMM + D2H every step).
+`--impl reference` times the reference's own CPU GEMM (harness/gemm_check.cpp
+reference_gemm, compiled into oracle/_ref; the oracle port if that is absent)
+on the host cores, on bounded samples of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "GEMM TFLOP/s per GPU and % of tcgen05 peak (bf16 8192³) at 1/2/4/8 B200"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+WORKLOADS = {
+    # name: (M, N per GPU, K, distribution, description)
+    "bf16_tn_8192": (8192, 8192, 8192, "normal_0p1",
+                     "bf16 TN GEMM M=N=K=8192, N(0,1)*0.1, fp32 accumulate, bf16 out"),
+    "bf16_tn_4096": (4096, 4096, 4096, "normal_0p1",
+                     "bf16 TN GEMM M=N=K=4096, N(0,1)*0.1, fp32 accumulate, bf16 out"),
+}
+
+# DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture;
+# see profiles/. None until a capture of that workload exists.
+NCU_DRAM_TRAFFIC_BYTES = {}
+
+
+def dist_env():
+    return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
+            int(os.environ.get("WORLD_SIZE", 1)))
+
+
+# ---------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------ CPU reference leg
+def cpu_reference_sample(K: int, budget_s: float, steps: int | None = None, warmup: int = 0):
+    """Times the reference's CPU GEMM on 128x128xK blocks of the workload, one block per
+    host thread at a time. Returns (tflops, cores, kind, sample_description, ms_per_step).
+
+    steps=None: run rounds until about `budget_s` seconds are spent (cpu_baseline leg);
+    steps=k: run exactly k timed rounds after `warmup` (the --impl reference arm); if that
+    would take too long the K extent of each block is shortened and the sample says so.
+    """
+    import numpy as np
+    import oracle
+    threads = oracle.host_threads()
+    use_ref = oracle.have_ref()
+    kind = "reference" if use_ref else "port"
+    rng = np.random.default_rng(0x5EED)
+
+    def make_block(kk):
+        a = (rng.standard_normal((128, kk)) * 0.1).astype(np.float32)
+        b = (rng.standard_normal((128, kk)) * 0.1).astype(np.float32)
+        return oracle.f32_to_f16_bits(a), oracle.f32_to_f16_bits(b)
+
+    def run_block(blk, out):
+        a, b = blk
+        if use_ref:
+            oracle.ref().patina_ref_reference_gemm(a.ctypes.data, b.ctypes.data, a.shape[1],
+                                                   out.ctypes.data)
+        else:
+            out[:] = oracle.ref_gemm_tn(oracle.f16_bits_to_f32(a), oracle.f16_bits_to_f32(b),
+                                        threads=1)
+
+    def run_round(blocks, outs):
+        ts = [threading.Thread(target=run_block, args=(blocks[i], outs[i])) for i in range(threads)]
+        t0 = time.perf_counter()
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        return time.perf_counter() - t0
+
+    # calibrate on a short block
+    cal = make_block(512)
+    out0 = np.empty((128, 128), np.float64)
+    t0 = time.perf_counter()
+    run_block(cal, out0)
+    per_k = (time.perf_counter() - t0) / 512  # seconds per unit of K for one block, one thread
+    kk = K
+    if steps is not None:
+        rounds_total = steps + warmup
+        while kk > 256 and per_k * kk * rounds_total > budget_s:
+            kk //= 2
+    blocks = [make_block(kk) for _ in range(threads)]
+    outs = [np.empty((128, 128), np.float64) for _ in range(threads)]
+    for _ in range(warmup):
+        run_round(blocks, outs)
+    times = []
+    if steps is None:
+        spent = 0.0
+        while spent < budget_s and len(times) < 64:
+            dt = run_round(blocks, outs)
+            times.append(dt)
+            spent += dt
+    else:
+        for _ in range(steps):
+            times.append(run_round(blocks, outs))
+    flops_round = 2.0 * 128 * 128 * kk * threads
+    total = sum(times)
+    tflops = flops_round * len(times) / total / 1e12
+    what = ("the reference's reference_gemm (harness/gemm_check.cpp:165-178, compiled from the "
+            "reference source)" if use_ref else "the oracle port of the reference's reference_gemm")
+    sample = (f"{len(times)} rounds x {threads} threads x one 128x128x{kk} f16 block each "
+              f"(blocks of the {K}-deep workload" + ("" if kk == K else f", K shortened to {kk}") +
+              f"), {what}, {total:.1f} s of wall time")
+    return tflops, threads, kind, sample, 1e3 * total / len(times)
+
+
+# ------------------------------------------------------------------ our arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    rank, local_rank, world = dist_env()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run "
+                             "--nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench.py --gpus N")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import patina_b200
+    from patina_b200 import inputs
+
+    M, N, K, distn, desc = WORKLOADS[args.workload]
+    ctx = patina_b200.GemmContext(local_rank)
+    # Column shard of this rank: its own seed, so shards differ like real weight shards do.
+    A_h, B_h = inputs.make_operands(distn, M, N, K, seed=inputs.DEFAULT_SEED + rank, pin=True)
+    if world > 1:
+        # A is replicated: every rank uses rank 0's activations.
+        A_h0, _ = inputs.make_operands(distn, M, 1, K, seed=inputs.DEFAULT_SEED)
+        A_h.copy_(A_h0)
+    C_h = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    dA, dB = A_h.cuda(non_blocking=True), B_h.cuda(non_blocking=True)
+    dC = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        evs[0].record()
+        for i in range(steps):
+            fn()
+            evs[i + 1].record()
+        barrier()
+        total_ms = evs[0].elapsed_time(evs[-1])
+        per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+        if world > 1:
+            t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total_ms = float(t.item())
+        return total_ms, per
+
+    flops_per_gpu = 2.0 * M * N * K
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = ctx.launch_count
+    total_ms, per = timed(lambda: ctx.gemm_tn(dA, dB, out=dC), args.steps, args.warmup)
+    launches = ctx.launch_count - launches0 - args.warmup
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.status()
+    ms_per_step = total_ms / args.steps
+    value = world * flops_per_gpu / (ms_per_step * 1e-3) / 1e12
+
+    # end to end: host buffers in, host buffer out, every step
+    e2e_steps = args.steps
+    if args.no_e2e:
+        e2e_total_ms = float("nan")
+    else:
+        e2e_total_ms, _ = timed(lambda: ctx.gemm_host(A_h, B_h, C_h), e2e_steps, min(args.warmup, 3))
+        ctx.status()
+    e2e_value = world * flops_per_gpu / (e2e_total_ms / e2e_steps * 1e-3) / 1e12
+    h2d = (M * K + N * K) * 2
+    d2h = M * N * 2
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(peaks_path):
+        peak = float(json.load(open(peaks_path))["bf16_tflops"])
+        peak_src = "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    else:
+        peak, peak_src = FALLBACK_BF16_TFLOPS, "fallback"
+    kernel_ms = statistics.mean(per)
+    achieved = flops_per_gpu / (kernel_ms * 1e-3) / 1e12
+    traffic = NCU_DRAM_TRAFFIC_BYTES.get(args.workload)
+
+    out = {
+        "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}" +
+                               (f"; N-column shards, one {N}-column shard per GPU, A replicated"
+                                if world > 1 else ""),
+                   "M": M, "N_per_gpu": N, "K": K, "layout": "TN (A row-major MxK, B K-major NxK)",
+                   "l2": "inputs (268 MB) larger than L2 (126 MB); no flush between steps",
+                   "kernel": "persistent tcgen05 GEMM, auto tile config"},
+        "per_gpu_tflops": round(value / world, 2),
+        "pct_of_nominal_bf16_peak": round(100.0 * value / world / NOMINAL_BF16_TFLOPS, 2),
+        "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_total_ms / e2e_steps, 4)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak,
+                     "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": traffic,
+                     "peak_source": peak_src, "kernel_ms_mean": round(kernel_ms, 5),
+                     "kernel_ms_min": round(min(per), 5)},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        tf, cores, kind, sample, _ = cpu_reference_sample(K, budget_s=12.0)
+        out["cpu_baseline"] = {"value": round(tf, 6), "unit": "TFLOP/s", "cores": cores,
+                               "kind": kind, "sample": sample}
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------ reference arm
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    M, N, K, distn, desc = WORKLOADS[args.workload]
+    tf, cores, kind, sample, ms = cpu_reference_sample(K, budget_s=150.0, steps=args.steps,
+                                                       warmup=args.warmup)
+    out = {
+        "impl": "reference", "metric": METRIC, "value": round(tf, 6), "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}", "M": M, "N_per_gpu": N, "K": K,
+                   "note": "CPU arm: each step is a bounded sample of the workload (see cpu_baseline.sample)"},
+        "cpu_baseline": {"value": round(tf, 6), "unit": "TFLOP/s", "cores": cores, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": round(tf, 6), "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bf16_tn_8192")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

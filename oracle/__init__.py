@@ -131,7 +131,11 @@ def ref_gemm_tn(A: np.ndarray, B: np.ndarray, rows=None, threads: int = 0) -> np
     values; rows (optional int64 indices) restricts the output to those rows.
     """
     assert A.dtype == np.float32 and B.dtype == np.float32
-    assert A.strides[1] == 4 and B.strides[1] == 4 and A.shape[1] == B.shape[1]
+    assert A.shape[1] == B.shape[1]
+    if A.size == 0 or B.size == 0:
+        n_out = A.shape[0] if rows is None else len(rows)
+        return np.zeros((n_out, B.shape[0]), np.float64)
+    assert A.strides[1] == 4 and B.strides[1] == 4
     lda, ldb = A.strides[0] // 4, B.strides[0] // 4
     N, K = B.shape
     if rows is None:

@@ -59,7 +59,9 @@ def build_harness(force: bool = False) -> str:
         subprocess.check_call([
             cxx, "-O2", "-std=c++17", "-I", os.path.join(_PKG, "..", "include"),
             "-I", "/usr/local/cuda/include", src, "-o", HARNESS_PATH,
-            "-L", LIB_DIR, "-lpatina_gemm", "-Wl,-rpath,$ORIGIN", "-lpthread", "-ldl", "-lm",
+            "-L", LIB_DIR, "-lpatina_gemm", "-Wl,-rpath,$ORIGIN",
+            "-L", "/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,/usr/local/cuda/lib64",
+            "-lpthread", "-ldl", "-lm",
         ])
     return HARNESS_PATH
 

@@ -1,0 +1,55 @@
+"""The C++ harness keeps the reference CLI's contract (harness/gemm_check.cpp:24-31,186-218):
+positional form, usage errors -> exit 2, no Blackwell device -> exit 3, PASS -> 0."""
+import subprocess
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def harness():
+    from patina_b200 import build
+    path = build.build_harness()
+    assert path
+    return path
+
+
+def run(harness, *args):
+    return subprocess.run([harness, *args], capture_output=True, text=True, timeout=600)
+
+
+def test_usage_errors_exit_2(harness):
+    assert run(harness).returncode == 2
+    assert run(harness, "a.ptx", "tcgen05_gemm_v1", "64").returncode == 2      # v1 needs K=32
+    assert run(harness, "a.ptx", "tcgen05_gemm_v2", "48").returncode == 2      # v2 needs K%32==0
+    r = run(harness, "a.ptx", "some_other_kernel", "32")
+    assert r.returncode == 2 and "unknown kernel" in r.stderr
+    assert run(harness, "--m", "128", "--dtype", "int4").returncode == 2
+
+
+def test_without_a_blackwell_device_exit_3(harness):
+    import torch
+    if torch.cuda.is_available() and torch.cuda.get_device_capability(0)[0] == 10:
+        pytest.skip("a Blackwell GPU is present")
+    r = run(harness, "a.ptx", "tcgen05_gemm_v2", "128")
+    assert r.returncode == 3 and "sm_100a" in r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernel,K", [("tcgen05_gemm_v1", "32"), ("tcgen05_gemm_v2", "32"), ("tcgen05_gemm_v2", "128")])
+def test_reference_cases_pass_on_hardware(harness, kernel, K):
+    """The reference's three hardware cases (docs/HARDWARE_TESTING.md:77-87)."""
+    r = run(harness, "unused.ptx", kernel, K)
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = r.stdout.splitlines()
+    assert lines[0].startswith("device: ") and lines[-1] == "PASS"
+    assert any(l.startswith(f"kernel: {kernel}  K={K}  k_tiles={int(K) // 32}  block=192") for l in lines)
+    assert any(l.startswith("mismatches:  0 / 16384") for l in lines)
+    assert any(l.startswith("max abs err:") for l in lines) and any(l.startswith("sum(C):") for l in lines)
+
+
+@pytest.mark.gpu
+def test_flag_form_bf16_and_fp8(harness):
+    r = run(harness, "--m", "512", "--n", "776", "--k", "264", "--dtype", "bf16", "--dist", "llm", "--cta", "2")
+    assert r.returncode == 0 and r.stdout.strip().endswith("PASS"), r.stdout + r.stderr
+    r = run(harness, "--m", "256", "--n", "512", "--k", "512", "--dtype", "fp8", "--dist", "normal01", "--iters", "3")
+    assert r.returncode == 0 and "tflops:" in r.stdout, r.stdout + r.stderr

@@ -1,0 +1,146 @@
+"""Host-side logic of the library, no GPU: the shared object loads and exports the
+whole C ABI, every derived encoding matches the reference's pinned constants,
+the tile scheduler is a bijection, plans and argument checks behave."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from patina_b200 import lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    header = open(os.path.join(ROOT, "include", "patina_gemm.h")).read()
+    declared = set(re.findall(r"\b(patina_gemm_\w+)\s*\(", header))
+    assert declared == set(L.SYMBOLS)
+    for name in declared:
+        assert hasattr(built_lib, name), name
+
+
+def test_reference_constants(built_lib):
+    # crates/patina/tests/golden/v2_gemm_pipelined.ptx:192,197; crates/patina/tests/layout.rs:33-68
+    assert built_lib.patina_gemm_smem_desc(0, 128, 256, 0) == 70437464178688
+    d = built_lib.patina_gemm_smem_desc(0x4000, 128, 256, 0)
+    assert d & 0x3FFF == 0x4000 >> 4
+    assert (d >> 16) & 0x3FFF == 128 >> 4 and (d >> 32) & 0x3FFF == 256 >> 4
+    assert (d >> 46) & 3 == 1 and (d >> 61) == 0
+    assert built_lib.patina_gemm_idesc(L.IN_F16, 128, 128) == 136314896
+    assert built_lib.patina_gemm_idesc(L.IN_F16, 64, 256) == (1 << 4) | ((256 >> 3) << 17) | ((64 >> 4) << 24)
+    assert built_lib.patina_gemm_tmem_lane_offset(0) == 0
+    assert built_lib.patina_gemm_tmem_lane_offset(3) == 3 << 21
+
+
+def test_generalised_encodings(built_lib):
+    # 128-byte swizzle, K-major: SBO 1024, layout code 2, version 1
+    d = built_lib.patina_gemm_smem_desc(0x8400, 0, 1024, 2)
+    assert d & 0x3FFF == 0x8400 >> 4 and (d >> 32) & 0x3FFF == 64 and d >> 61 == 2 and (d >> 46) & 3 == 1
+    bf = built_lib.patina_gemm_idesc(L.IN_BF16, 256, 256)
+    assert (bf >> 4) & 3 == 1 and (bf >> 7) & 7 == 1 and (bf >> 10) & 7 == 1
+    assert (bf >> 17) & 0x3F == 32 and (bf >> 24) & 0x1F == 16 and (bf >> 15) & 3 == 0
+    f8 = built_lib.patina_gemm_idesc(L.IN_E4M3, 128, 256)
+    assert (f8 >> 7) & 7 == 0 and (f8 >> 10) & 7 == 0 and (f8 >> 24) & 0x1F == 8
+    # one MMA consumes 32 bytes of K: +2 descriptor units for K16 (16-bit) and K32 (8-bit)
+    assert built_lib.patina_gemm_k_advance_units(16, L.IN_BF16) == 2
+    assert built_lib.patina_gemm_k_advance_units(48, L.IN_F16) == 6
+    assert built_lib.patina_gemm_k_advance_units(32, L.IN_E4M3) == 2
+
+
+@pytest.mark.parametrize("tiles_m,tiles_n,group", [(1, 1, 8), (32, 32, 8), (5, 7, 3), (7, 3, 16), (64, 2, 8), (3, 112, 1)])
+def test_tile_scheduler_is_a_bijection(built_lib, tiles_m, tiles_n, group):
+    seen = set()
+    m, n = C.c_uint32(), C.c_uint32()
+    for t in range(tiles_m * tiles_n):
+        built_lib.patina_gemm_tile_coord(t, tiles_m, tiles_n, group, C.byref(m), C.byref(n))
+        assert m.value < tiles_m and n.value < tiles_n
+        seen.add((m.value, n.value))
+    assert len(seen) == tiles_m * tiles_n
+    # within a band M runs fastest
+    if tiles_m >= 2 and group >= 2:
+        built_lib.patina_gemm_tile_coord(1, tiles_m, tiles_n, group, C.byref(m), C.byref(n))
+        assert (m.value, n.value) == (1, 0)
+
+
+def test_plan_headline_shape():
+    p = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192)
+    assert (p.cta_group, p.block_n, p.cluster) == (2, 256, 2)
+    assert (p.tiles_m, p.tiles_n, p.num_tiles, p.k_blocks) == (32, 32, 1024, 128)
+    assert p.grid == 148 and p.block == 192 and p.tmem_cols == 512
+    assert p.smem_bytes <= 232448
+    # bytes the full barrier expects == bytes of the TMA boxes that land on it
+    # (the invariant the reference's verifier enforces, mlir/lib/PatinaOps.cpp:587-614)
+    assert p.stage_bytes == 128 * 128 + 128 * 128 and p.expect_tx_bytes == 2 * p.stage_bytes
+
+
+def test_plan_variants():
+    cfg = L.GemmConfig(1, 256, 0, 0, 0)
+    p = L.plan(L.IN_BF16, L.OUT_BF16, 1000, 776, 520, cfg)
+    assert (p.cta_group, p.block_n, p.tiles_m, p.tiles_n, p.k_blocks) == (1, 256, 8, 4, 9)
+    assert p.grid == 32 and p.expect_tx_bytes == 128 * 128 + 256 * 128
+    p = L.plan(L.IN_E4M3, L.OUT_BF16, 8192, 8192, 8192)
+    assert p.k_blocks == 64
+    p = L.plan(L.IN_F16, L.OUT_F32, 128, 128, 4096)
+    assert p.num_tiles == 1 and p.grid == p.cluster
+    cfg = L.GemmConfig(2, 256, 0, 0, 20)
+    assert L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 64, cfg).grid == 20
+    with pytest.raises(ValueError):
+        L.plan(L.IN_BF16, L.OUT_F32, 128, 128, 128)          # unsupported type pair
+    with pytest.raises(ValueError):
+        L.plan(L.IN_BF16, L.OUT_BF16, 128, 128, 128, L.GemmConfig(4, 256, 0, 0, 0))
+
+
+def test_argument_validation(built_lib):
+    ok = dict(in_type=L.IN_BF16, out_type=L.OUT_BF16, A=0x1000, lda=64, B=0x2000, ldb=64, Cp=0x3000,
+              ldc=64, M=32, N=64, K=64)
+    assert L.validate(**ok) is None
+    bad = [({"A": 0}, "A is null"), ({"B": 0}, "B is null"), ({"Cp": 0}, "C is null"),
+           ({"A": 0x1008}, "A is not 16-byte aligned"), ({"Cp": 0x3004}, "C is not 16-byte aligned"),
+           ({"lda": 60}, "lda=60 < K=64"), ({"lda": 68}, "multiple of 16 bytes"),
+           ({"ldc": 32}, "ldc=32 < N=64"), ({"ldc": 66}, "multiple of 16 bytes"),
+           ({"M": -1}, "negative dimension"), ({"K": 2 ** 31}, "exceeds"),
+           ({"out_type": L.OUT_F32}, "unsupported type pair")]
+    for change, needle in bad:
+        msg = L.validate(**{**ok, **change})
+        assert msg is not None and needle in msg, (change, msg)
+    # empty problems never dereference anything
+    assert L.validate(**{**ok, "M": 0, "A": 0, "Cp": 0}) is None
+    assert L.validate(**{**ok, "K": 0, "A": 0, "B": 0}) is None
+    # fp8 rows are bytes: K=48 is a legal pitch, K=40 is not
+    assert L.validate(L.IN_E4M3, L.OUT_BF16, 0x1000, 48, 0x2000, 48, 0x3000, 64, 32, 64, 48) is None
+    assert "16 bytes" in L.validate(L.IN_E4M3, L.OUT_BF16, 0x1000, 40, 0x2000, 40, 0x3000, 64, 32, 64, 40)
+
+
+def test_string_free_is_null_safe(built_lib):
+    built_lib.patina_gemm_string_free(None)
+    assert built_lib.patina_gemm_last_error(None) is None
+    assert built_lib.patina_gemm_version().startswith(b"patina-b200-gemm")
+
+
+def test_no_device_means_unsupported_not_fallback(built_lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    h = C.c_void_p()
+    assert built_lib.patina_gemm_context_create(0, C.byref(h)) == L.ERR_UNSUPPORTED_ARCH
+    assert not h.value
+    import patina_b200
+    with pytest.raises(patina_b200.PatinaGemmError):
+        patina_b200.GemmContext(0)
+    with pytest.raises(patina_b200.PatinaGemmError):
+        patina_b200.compute_capability()
+
+
+def test_inputs_are_deterministic():
+    import torch
+    from patina_b200 import inputs
+    A1, B1 = inputs.make_operands("llm", 64, 48, 32)
+    A2, B2 = inputs.make_operands("llm", 64, 48, 32)
+    assert torch.equal(A1, A2) and torch.equal(B1, B2) and A1.dtype == torch.bfloat16
+    assert 0.5 < float(A1.float().std()) < 1.5 and 0.01 < float(B1.float().std()) < 0.03
+    U, _ = inputs.make_operands("uniform", 256, 8, 64)
+    assert float(U.float().min()) >= -1 and float(U.float().max()) <= 1
+    Aq, sa, Bq, sb = inputs.make_fp8_operands(32, 16, 64)
+    assert Aq.dtype == torch.float8_e4m3fn and abs(float(Aq.float().abs().max()) - 448.0) < 1e-3
+    assert sa > 0 and sb > 0

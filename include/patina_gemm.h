@@ -50,16 +50,19 @@ enum { PATINA_OUT_BF16 = 0, PATINA_OUT_F32 = 1 };
 
 /* Tile configuration. Zero in any field means "choose for me". */
 typedef struct PatinaGemmConfig {
-  int32_t cta_group; /* 1 = one CTA per tile (128 x block_n); 2 = CTA pair (256 x block_n) */
-  int32_t block_n;   /* 128 or 256 */
+  int32_t cta_group; /* 1 = one CTA per tile; 2 = CTA pair (tcgen05 cta_group::2) */
+  int32_t block_n;   /* tile width: 128 or 256 */
   int32_t stages;    /* shared-memory ring depth */
   int32_t group_m;   /* scheduler band height in tiles */
   int32_t max_ctas;  /* cap on persistent CTAs (0 = number of SMs) */
+  int32_t m_sub;     /* 128-row accumulator sub-tiles per CTA: 1 or 2;
+                        tile height = 128 * cta_group * m_sub */
 } PatinaGemmConfig;
 
 /* What a call would launch; computed on the host without touching a device. */
 typedef struct PatinaGemmPlan {
-  int32_t cta_group, block_n, stages, group_m;
+  int32_t cta_group, block_n, stages, group_m, m_sub;
+  uint32_t tile_m;
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
   uint32_t grid, block, cluster, smem_bytes, tmem_cols;
   uint32_t stage_bytes, expect_tx_bytes;

@@ -41,28 +41,37 @@ std::string fmt(const char* f, ...) {
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
 
 struct KernelEntry {
-  int cta_group, block_n, stages, in_type, out_type;
+  int cta_group, m_sub, block_n, stages, in_type, out_type;
   KernelFn fn;
   uint32_t smem_bytes;
 };
 
-#define PATINA_KERNEL(G, BN, S, IN, OUT) \
-  { G, BN, S, IN, OUT, gemm_tn_kernel<G, BN, S, IN, OUT>, GemmTraits<G, BN, S, IN, OUT>::kSmemBytes }
+#define PATINA_KERNEL(G, MS, BN, S, IN, OUT)                  \
+  { G, MS, BN, S, IN, OUT, gemm_tn_kernel<G, MS, BN, S, IN, OUT>, \
+    GemmTraits<G, MS, BN, S, IN, OUT>::kSmemBytes }
 
+// Listed best-first per type pair: an explicit request takes the first match.
 const KernelEntry kKernels[] = {
     // bf16 -> bf16
-    PATINA_KERNEL(2, 256, 6, kBF16, kOutBF16),
-    PATINA_KERNEL(1, 256, 4, kBF16, kOutBF16),
-    PATINA_KERNEL(2, 128, 8, kBF16, kOutBF16),
-    PATINA_KERNEL(1, 128, 6, kBF16, kOutBF16),
+    PATINA_KERNEL(2, 2, 256, 4, kBF16, kOutBF16),  // 512 x 256 per pair, accumulators fill TMEM
+    PATINA_KERNEL(2, 1, 256, 6, kBF16, kOutBF16),  // 256 x 256 per pair, double-buffered TMEM
+    PATINA_KERNEL(2, 1, 256, 5, kBF16, kOutBF16),
+    PATINA_KERNEL(2, 1, 256, 4, kBF16, kOutBF16),
+    PATINA_KERNEL(2, 1, 256, 3, kBF16, kOutBF16),
+    PATINA_KERNEL(1, 1, 256, 4, kBF16, kOutBF16),
+    PATINA_KERNEL(1, 1, 256, 3, kBF16, kOutBF16),
+    PATINA_KERNEL(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
+    PATINA_KERNEL(2, 1, 128, 8, kBF16, kOutBF16),
+    PATINA_KERNEL(1, 1, 128, 6, kBF16, kOutBF16),
     // e4m3 -> bf16
-    PATINA_KERNEL(2, 256, 6, kE4M3, kOutBF16),
-    PATINA_KERNEL(1, 256, 4, kE4M3, kOutBF16),
-    PATINA_KERNEL(1, 128, 6, kE4M3, kOutBF16),
+    PATINA_KERNEL(2, 2, 256, 4, kE4M3, kOutBF16),
+    PATINA_KERNEL(2, 1, 256, 6, kE4M3, kOutBF16),
+    PATINA_KERNEL(1, 1, 256, 4, kE4M3, kOutBF16),
+    PATINA_KERNEL(1, 1, 128, 6, kE4M3, kOutBF16),
     // f16 -> f32 (the reference kernel's types)
-    PATINA_KERNEL(2, 256, 6, kF16, kOutF32),
-    PATINA_KERNEL(1, 256, 4, kF16, kOutF32),
-    PATINA_KERNEL(1, 128, 6, kF16, kOutF32),
+    PATINA_KERNEL(2, 1, 256, 6, kF16, kOutF32),
+    PATINA_KERNEL(1, 1, 256, 4, kF16, kOutF32),
+    PATINA_KERNEL(1, 1, 128, 6, kF16, kOutF32),
 };
 constexpr int kNumKernels = sizeof(kKernels) / sizeof(kKernels[0]);
 
@@ -78,19 +87,20 @@ uint32_t ceil_div(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); 
 // Fraction of the persistent slots that do useful work, times a speed factor of
 // the tile shape (bigger tiles move fewer operand bytes per flop).
 double config_score(const KernelEntry& k, int64_t M, int64_t N, int num_sms) {
-  const uint64_t tiles = (uint64_t)ceil_div(M, 128 * k.cta_group) * ceil_div(N, k.block_n);
+  const int64_t tile_m = 128 * k.cta_group * k.m_sub;
+  const uint64_t tiles = (uint64_t)ceil_div(M, tile_m) * ceil_div(N, k.block_n);
   const uint64_t slots = (uint64_t)(num_sms / k.cta_group);
   if (slots == 0 || tiles == 0) return 0.0;
   const uint64_t waves = (tiles + slots - 1) / slots;
   // useful fraction of the padded tile area
   const double area = (double)M * (double)N /
-                      ((double)ceil_div(M, 128 * k.cta_group) * 128 * k.cta_group *
-                       (double)ceil_div(N, k.block_n) * k.block_n);
+                      ((double)ceil_div(M, tile_m) * tile_m * (double)ceil_div(N, k.block_n) * k.block_n);
   const double eff = (double)tiles / (double)(waves * slots) * area;
-  double speed = 1.0;
-  if (k.cta_group == 1 && k.block_n == 256) speed = 0.92;
-  if (k.cta_group == 2 && k.block_n == 128) speed = 0.85;
-  if (k.cta_group == 1 && k.block_n == 128) speed = 0.75;
+  // operand bytes fetched per output element, relative to the largest tile
+  const double per_out = (double)(tile_m + k.block_n) / ((double)tile_m * k.block_n);
+  const double best = (512.0 + 256.0) / (512.0 * 256.0);
+  double speed = 1.0 / (1.0 + 0.35 * (per_out / best - 1.0));
+  if (k.cta_group == 1) speed *= 0.97;  // a pair halves its B traffic from shared memory
   return eff * speed;
 }
 
@@ -108,7 +118,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   PatinaGemmConfig c{};
   if (cfg) c = *cfg;
   const KernelEntry* best = nullptr;
-  if (c.cta_group != 0 || c.block_n != 0) {
+  if (c.cta_group != 0 || c.block_n != 0 || c.m_sub != 0) {
     // explicit request: fill in whatever was left open with the first match
     for (int i = 0; i < kNumKernels && !best; ++i) {
       const KernelEntry& k = kKernels[i];
@@ -116,12 +126,13 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (c.cta_group != 0 && k.cta_group != c.cta_group) continue;
       if (c.block_n != 0 && k.block_n != c.block_n) continue;
       if (c.stages != 0 && k.stages != c.stages) continue;
+      if (k.m_sub != (c.m_sub != 0 ? c.m_sub : 1)) continue;  // explicit requests default to m_sub = 1
       best = &k;
     }
     if (!best) {
       if (err)
-        *err = fmt("no kernel for cta_group=%d block_n=%d stages=%d with these types", c.cta_group,
-                   c.block_n, c.stages);
+        *err = fmt("no kernel for cta_group=%d m_sub=%d block_n=%d stages=%d with these types",
+                   c.cta_group, c.m_sub, c.block_n, c.stages);
       return PATINA_GEMM_ERR_INVALID_ARG;
     }
   } else {
@@ -146,7 +157,9 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   p.cta_group = best->cta_group;
   p.block_n = best->block_n;
   p.stages = best->stages;
-  p.tiles_m = ceil_div(M, 128 * best->cta_group);
+  p.m_sub = best->m_sub;
+  p.tile_m = 128u * best->cta_group * best->m_sub;
+  p.tiles_m = ceil_div(M, p.tile_m);
   p.tiles_n = ceil_div(N, best->block_n);
   p.num_tiles = p.tiles_m * p.tiles_n;
   const uint32_t kelems = kBlockKBytes / input_bytes(in_type);
@@ -158,11 +171,11 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   if (slots == 0) slots = 1;
   const uint32_t clusters = p.num_tiles < slots ? p.num_tiles : slots;
   p.grid = clusters * best->cta_group;
-  p.block = 192;
+  p.block = 64 + 128 * best->m_sub;
   p.cluster = best->cta_group;
   p.smem_bytes = best->smem_bytes;
-  p.tmem_cols = 2 * best->block_n;
-  const SmemPlan sp = smem_plan(best->cta_group, best->block_n, best->stages);
+  p.tmem_cols = (2 * best->m_sub * best->block_n <= 512 ? 2 : 1) * best->m_sub * best->block_n;
+  const SmemPlan sp = smem_plan(best->cta_group, best->m_sub, best->block_n, best->stages);
   p.stage_bytes = sp.stage_bytes;
   p.expect_tx_bytes = sp.stage_bytes * best->cta_group;
   p.idesc = idesc(in_type, 128 * best->cta_group, best->block_n);

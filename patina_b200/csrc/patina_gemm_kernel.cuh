@@ -6,14 +6,20 @@
 // kernel uses (crates/patina/tests/golden/v2_gemm_pipelined.ptx:89-94):
 //   warp 0      TMA producer   (one elected lane)
 //   warp 1      MMA issuer     (one elected lane; the whole warp owns TMEM alloc/dealloc)
-//   warps 2..5  epilogue       (TMEM -> registers -> swizzled SMEM -> TMA store)
+//   warps 2..   epilogue       (TMEM -> registers -> swizzled SMEM -> TMA store),
+//               four warps per accumulator sub-tile, one per TMEM lane quarter
 //
 // What is different from that kernel (which runs one 128x128 tile in one CTA):
 //   * persistent: each CTA (or CTA pair) walks a list of output tiles
 //     (patina::tile_coord), so prologue cost is paid once per SM;
 //   * 128-byte-swizzled K-major stages of 128 bytes of K, kStages deep;
-//   * two accumulators in TMEM (2 x BN columns) so the epilogue of tile i
-//     overlaps the mainloop of tile i+1;
+//   * kMSub == 1: two accumulators in TMEM (2 x BN columns) so the epilogue of
+//     tile i overlaps the mainloop of tile i+1;
+//     kMSub == 2: each CTA owns two 128-row sub-tiles that share every B stage
+//     (a 256 x BN tile per CTA, 512 x BN per pair), which cuts operand traffic
+//     from L2 by a quarter; the accumulators then fill TMEM, so the epilogue
+//     (eight warps) is not overlapped with the next mainloop, only with its
+//     operand prefetch;
 //   * optional CTA pair (kCtaGroup == 2): tcgen05.mma.cta_group::2 computes a
 //     256 x BN tile; each CTA loads its own 128 rows of A and its own BN/2 rows
 //     of B; the pair leader issues the MMAs. No TMA multicast is used: each
@@ -78,7 +84,9 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
     const bool done = kClusterScope ? ptx::mbar_try_wait_cluster(bar, parity)
                                     : ptx::mbar_try_wait(bar, parity);
     if (done) return true;
-    if ((++spins & 63u) == 0u) {
+    // try_wait itself blocks for a hardware-defined slice, so a few failed polls
+    // already mean microseconds; look at the clock every fourth one.
+    if ((++spins & 3u) == 0u) {
       if (*w.abort_flag) return false;
       const uint64_t now = ptx::globaltimer_ns();
       if (t0 == 0) {
@@ -91,41 +99,49 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
   }
 }
 
-template <int kCtaGroup, int BN, int kStages, int kIn, int kOut>
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut>
 struct GemmTraits {
-  static constexpr uint32_t kThreads = 192;
+  static constexpr uint32_t kEpiWarps = 4 * kMSub;            // one warp per (sub-tile, lane quarter)
+  static constexpr uint32_t kThreads = 64 + 32 * kEpiWarps;   // producer + MMA + epilogue warps
   static constexpr uint32_t kBlockKElems = kBlockKBytes / input_bytes(kIn);
   static constexpr uint32_t kUmmaK = umma_k(kIn);
   static constexpr uint32_t kUmmaPerStage = kBlockKElems / kUmmaK;  // 4
+  static constexpr uint32_t kTileM = kCtaRows * kCtaGroup * kMSub;  // rows of one cluster tile
   static constexpr uint32_t kBRows = BN / kCtaGroup;                // B rows this CTA loads
-  static constexpr uint32_t kABytes = kCtaRows * kBlockKBytes;
+  static constexpr uint32_t kASubBytes = kCtaRows * kBlockKBytes;   // one 128-row slab of A
+  static constexpr uint32_t kABytes = kMSub * kASubBytes;
   static constexpr uint32_t kBBytes = kBRows * kBlockKBytes;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr uint32_t kTmemCols = 2 * BN;
+  static constexpr uint32_t kAccCols = kMSub * BN;                  // TMEM columns of one tile
+  static constexpr uint32_t kAccBufs = (2 * kAccCols <= 512) ? 2 : 1;
+  static constexpr uint32_t kTmemCols = kAccBufs * kAccCols;
+  static constexpr uint32_t kStageBufs = staging_bufs(kMSub);       // per epilogue warp
   static constexpr uint32_t kChunkCols = 128 / output_bytes(kOut);  // one 128-byte row segment
   static constexpr uint32_t kChunks = BN / kChunkCols;
-  static constexpr uint32_t kSmemBytes = smem_plan(kCtaGroup, BN, kStages).total_bytes;
+  static constexpr uint32_t kSmemBytes = smem_plan(kCtaGroup, kMSub, BN, kStages).total_bytes;
+  static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
   static_assert(kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
-                "TMEM allocations are powers of two");
+                "TMEM allocations are powers of two up to 512 columns");
   static_assert((kBBytes % 1024) == 0, "swizzle atoms must stay 1024-byte aligned");
   static_assert(kSmemBytes <= kMaxDynSmem, "shared-memory plan exceeds 227 KB");
   static_assert((2 * kStages + 4) * 8 + 8 <= kBarrierRegionBytes, "barrier region too small");
 };
 
-template <int kCtaGroup, int BN, int kStages, int kIn, int kOut>
-__global__ void __launch_bounds__(192, 1)
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut>
+__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
-  using T = GemmTraits<kCtaGroup, BN, kStages, kIn, kOut>;
+  using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut>;
   constexpr bool kPair = (kCtaGroup == 2);
   constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
+  constexpr uint32_t kEpiWarps = T::kEpiWarps;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = smem_base;
   const uint32_t staging = ring + kStages * T::kStageBytes;
-  const uint32_t bars = staging + kEpiWarps * kStagingBufs * kStagingBufBytes;
+  const uint32_t bars = staging + kEpiWarps * T::kStageBufs * kStagingBufBytes;
   const uint32_t full_bar = bars;                      // [kStages]
   const uint32_t empty_bar = bars + 8u * kStages;      // [kStages]
   const uint32_t tfull_bar = bars + 16u * kStages;     // [2]
@@ -189,7 +205,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
       for (uint32_t t = cluster_id; t < p.num_tiles; t += num_clusters) {
         const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
-        const int32_t a_row = (int32_t)((c.m * kCtaGroup + cta_rank) * kCtaRows);
+        // Sub-tile s of this CTA covers rows a_row + s * (128 * kCtaGroup).
+        const int32_t a_row = (int32_t)(c.m * T::kTileM + cta_rank * kCtaRows);
         const int32_t b_row = (int32_t)(c.n * BN + cta_rank * T::kBRows);
         bool ok = true;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
@@ -200,11 +217,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
           if constexpr (kPair) {
             if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, 2u * T::kStageBytes);
-            ptx::tma_load_2d_pair(sa, &tm_a, leader_full + 8u * s, k0, a_row);
+#pragma unroll
+            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
+              ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
+                                    a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
           } else {
             ptx::mbar_arrive_expect_tx(full_bar + 8u * s, T::kStageBytes);
-            ptx::tma_load_2d(sa, &tm_a, full_bar + 8u * s, k0, a_row);
+#pragma unroll
+            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
+              ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * s, k0,
+                               a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d(sb, &tm_b, full_bar + 8u * s, k0, b_row);
           }
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
@@ -222,22 +245,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
       for (uint32_t t = cluster_id; t < p.num_tiles && ok; t += num_clusters, ++it) {
-        const uint32_t buf = it & 1u, acc_ph = (it >> 1) & 1u;
+        const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
         ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
         if (!ok) break;
         ptx::tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t tmem_d = tmem_base + buf * T::kAccCols;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t sa = ring + s * T::kStageBytes;
-          const uint64_t da = smem_desc_sw128_kmajor(sa);
           const uint64_t db = smem_desc_sw128_kmajor(sa + T::kABytes);
 #pragma unroll
           for (uint32_t k = 0; k < T::kUmmaPerStage; ++k) {
             const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
-            ptx::umma<kCtaGroup, kKind>(tmem_d, da + adv, db + adv, idesc_v, (kb | k) != 0u);
+#pragma unroll
+            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
+              const uint64_t da = smem_desc_sw128_kmajor(sa + ms * T::kASubBytes);
+              ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db + adv, idesc_v,
+                                          (kb | k) != 0u);
+            }
           }
           ptx::umma_commit<kCtaGroup>(empty_bar + 8u * s);
           if constexpr (kPair) ptx::umma_commit<kCtaGroup>(peer_empty + 8u * s);
@@ -251,29 +278,32 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       // wait for the last accumulator's completion here as well.
       if (ok && it > 0) {
         const uint32_t last = it - 1;
-        bounded_wait<kPair>(tfull_bar + 8u * (last & 1u), (last >> 1) & 1u, w, kTimeoutMmaDrain, it);
+        bounded_wait<kPair>(tfull_bar + 8u * (last % T::kAccBufs), (last / T::kAccBufs) & 1u, w,
+                            kTimeoutMmaDrain, it);
       }
     }
   }
   // ---------------------------------------------------------------- epilogue
   else {
     const uint32_t q = warp_idx & 3u;          // TMEM lane quarter this warp may touch
-    const uint32_t e = warp_idx - 2u;          // staging-buffer owner index
-    const uint32_t stg0 = staging + e * (kStagingBufs * kStagingBufBytes);
+    const uint32_t e = warp_idx - 2u;          // epilogue warp index
+    const uint32_t ms = e >> 2;                // accumulator sub-tile this warp drains
+    const uint32_t stg0 = staging + e * (T::kStageBufs * kStagingBufBytes);
     const uint32_t leader_tempty = kPair ? ptx::mapa(tempty_bar, 0) : tempty_bar;
     const uint32_t row_sw = lane & 7u;
     uint32_t it = 0, sbuf = 0;
     bool ok = true;
     for (uint32_t t = cluster_id; t < p.num_tiles && ok; t += num_clusters, ++it) {
       const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
-      const uint32_t buf = it & 1u, acc_ph = (it >> 1) & 1u;
+      const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
       ok = bounded_wait<kPair>(tfull_bar + 8u * buf, acc_ph, w, kTimeoutEpilogueTmemFull, t);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const uint32_t row0 = (c.m * kCtaGroup + cta_rank) * kCtaRows + q * kStoreBoxRows;
+      const uint32_t row0 = c.m * T::kTileM + ms * (kCtaRows * kCtaGroup) + cta_rank * kCtaRows +
+                            q * kStoreBoxRows;
       const uint32_t col0 = c.n * BN;
-      const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * BN;
+      const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * T::kAccCols + ms * BN;
 #pragma unroll 1
       for (uint32_t ch = 0; ch < T::kChunks; ++ch) {
         uint32_t v[kOut == kOutBF16 ? 64 : 32];
@@ -290,8 +320,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             else ptx::mbar_arrive(tempty_bar + 8u * buf);
           }
         }
-        // The staging buffer written two chunks ago must have been read by its store.
-        if (lane == 0) ptx::tma_store_wait_read<kStagingBufs - 1>();
+        // The staging buffer about to be rewritten must have been read by its store.
+        if (lane == 0) ptx::tma_store_wait_read<T::kStageBufs - 1>();
         __syncwarp();
         const uint32_t row_addr = stg0 + sbuf * kStagingBufBytes + lane * 128u;
 #pragma unroll
@@ -326,7 +356,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             ptx::tma_store_2d(&tm_c, stg0 + sbuf * kStagingBufBytes, (int32_t)cc, (int32_t)row0);
           ptx::tma_store_commit();
         }
-        sbuf ^= 1u;
+        if constexpr (T::kStageBufs > 1) sbuf ^= 1u;
       }
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();

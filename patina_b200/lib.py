@@ -27,12 +27,13 @@ SYMBOLS = (
 
 class GemmConfig(C.Structure):
     _fields_ = [("cta_group", C.c_int32), ("block_n", C.c_int32), ("stages", C.c_int32),
-                ("group_m", C.c_int32), ("max_ctas", C.c_int32)]
+                ("group_m", C.c_int32), ("max_ctas", C.c_int32), ("m_sub", C.c_int32)]
 
 
 class GemmPlan(C.Structure):
     _fields_ = [("cta_group", C.c_int32), ("block_n", C.c_int32), ("stages", C.c_int32),
-                ("group_m", C.c_int32), ("tiles_m", C.c_uint32), ("tiles_n", C.c_uint32),
+                ("group_m", C.c_int32), ("m_sub", C.c_int32), ("tile_m", C.c_uint32),
+                ("tiles_m", C.c_uint32), ("tiles_n", C.c_uint32),
                 ("num_tiles", C.c_uint32), ("k_blocks", C.c_uint32), ("grid", C.c_uint32),
                 ("block", C.c_uint32), ("cluster", C.c_uint32), ("smem_bytes", C.c_uint32),
                 ("tmem_cols", C.c_uint32), ("stage_bytes", C.c_uint32),

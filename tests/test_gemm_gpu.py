@@ -50,7 +50,8 @@ def check_norm(oracle_mod, got: torch.Tensor, want: np.ndarray, what=""):
 def cfgs():
     from patina_b200 import GemmConfig
     return {"auto": None, "1cta_n256": GemmConfig(1, 256, 0, 0, 0), "1cta_n128": GemmConfig(1, 128, 0, 0, 0),
-            "pair_n256": GemmConfig(2, 256, 0, 0, 0), "pair_n128": GemmConfig(2, 128, 0, 0, 0)}
+            "pair_n256": GemmConfig(2, 256, 0, 0, 0), "pair_n128": GemmConfig(2, 128, 0, 0, 0),
+            "pair_2sub_n256": GemmConfig(2, 256, 0, 0, 0, 2), "pair_2sub_n128": GemmConfig(2, 128, 0, 0, 0, 2)}
 
 
 # ------------------------------------------------------------ reference shape
@@ -107,7 +108,8 @@ def test_bf16_ragged_shapes(ctx, oracle_mod, M, N, K):
     A, B = inputs.make_operands("llm", M, N, K, seed=M * 7 + N)
     want = expect_bf16(oracle_mod, A, B, alpha=0.75)
     for name, cfg in cfgs().items():
-        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ldc = (N + 7) // 8 * 8  # row pitch must be a multiple of 16 bytes
+        out = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :N]
         ctx.gemm_tn(A.cuda(), B.cuda(), out=out, alpha=0.75, config=cfg)
         ctx.status()
         check_norm(oracle_mod, out, want, f"{name} {M}x{N}x{K}")
@@ -179,8 +181,8 @@ def test_fp8_e4m3(ctx, oracle_mod, M, N, K):
     ctx.status()
     check_norm(oracle_mod, out, want, "fp8 auto")
     for name, cfg in cfgs().items():
-        if name == "pair_n128":
-            continue  # no such fp8 kernel
+        if name in ("pair_n128", "pair_2sub_n128"):
+            continue  # no such fp8 kernels
         out = ctx.gemm_tn(Aq.cuda(), Bq.cuda(), alpha=sa * sb, config=cfg)
         ctx.status()
         check_norm(oracle_mod, out, want, f"fp8 {name}")
@@ -232,7 +234,7 @@ def test_wait_expiry_is_reported_and_context_survives(ctx, oracle_mod):
     healthy; afterwards the same context must compute correctly again."""
     import patina_b200
     from patina_b200 import inputs, lib as L
-    A, B = inputs.make_operands("uniform", 128, 128, 32768, seed=3)
+    A, B = inputs.make_operands("uniform", 128, 128, 131072, seed=3)
     dA, dB = A.cuda(), B.cuda()
     ctx.set_wait_limit_ns(1)
     try:

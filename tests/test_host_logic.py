@@ -65,13 +65,17 @@ def test_tile_scheduler_is_a_bijection(built_lib, tiles_m, tiles_n, group):
 
 def test_plan_headline_shape():
     p = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192)
-    assert (p.cta_group, p.block_n, p.cluster) == (2, 256, 2)
-    assert (p.tiles_m, p.tiles_n, p.num_tiles, p.k_blocks) == (32, 32, 1024, 128)
-    assert p.grid == 148 and p.block == 192 and p.tmem_cols == 512
+    assert (p.cta_group, p.m_sub, p.block_n, p.cluster, p.tile_m) == (2, 2, 256, 2, 512)
+    assert (p.tiles_m, p.tiles_n, p.num_tiles, p.k_blocks) == (16, 32, 512, 128)
+    assert p.grid == 148 and p.block == 320 and p.tmem_cols == 512
     assert p.smem_bytes <= 232448
     # bytes the full barrier expects == bytes of the TMA boxes that land on it
-    # (the invariant the reference's verifier enforces, mlir/lib/PatinaOps.cpp:587-614)
-    assert p.stage_bytes == 128 * 128 + 128 * 128 and p.expect_tx_bytes == 2 * p.stage_bytes
+    # (the invariant the reference's verifier enforces, mlir/lib/PatinaOps.cpp:587-614):
+    # per CTA two 128-row A slabs and 128 rows of B, 128 bytes of K each, times two CTAs
+    assert p.stage_bytes == 2 * 128 * 128 + 128 * 128 and p.expect_tx_bytes == 2 * p.stage_bytes
+    q = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192, L.GemmConfig(2, 256, 0, 0, 0, 0))
+    assert (q.m_sub, q.tile_m, q.num_tiles, q.block, q.tmem_cols, q.stages) == (1, 256, 1024, 192, 512, 6)
+    assert q.stage_bytes == 128 * 128 + 128 * 128 and q.expect_tx_bytes == 2 * q.stage_bytes
 
 
 def test_plan_variants():
@@ -89,6 +93,10 @@ def test_plan_variants():
         L.plan(L.IN_BF16, L.OUT_F32, 128, 128, 128)          # unsupported type pair
     with pytest.raises(ValueError):
         L.plan(L.IN_BF16, L.OUT_BF16, 128, 128, 128, L.GemmConfig(4, 256, 0, 0, 0))
+    with pytest.raises(ValueError):
+        L.plan(L.IN_F16, L.OUT_F32, 128, 128, 128, L.GemmConfig(2, 256, 0, 0, 0, 2))  # no such f16 kernel
+    p = L.plan(L.IN_BF16, L.OUT_BF16, 4096, 4096, 4096, L.GemmConfig(2, 128, 0, 0, 0, 2))
+    assert (p.tile_m, p.tmem_cols, p.block) == (512, 512, 320)
 
 
 def test_argument_validation(built_lib):

@@ -45,7 +45,10 @@ WORKLOADS = {
 
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture;
 # see profiles/. None until a capture of that workload exists.
-NCU_DRAM_TRAFFIC_BYTES = {}
+NCU_DRAM_TRAFFIC_BYTES = {
+    # profiles/gemm_tn_kernel_bf16_8192_pair512x256.md: 821.4 MB read + 121.4 MB written
+    "bf16_tn_8192": 942_766_080,
+}
 
 
 def dist_env():

@@ -1,0 +1,74 @@
+"""Column sharding across ranks: shard arithmetic, and the all-gather assembly run as two
+gloo ranks on CPU (the per-rank GEMM itself is checked on the GPU, where column shards are
+required to reproduce the full result bit for bit)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from patina_b200 import sharded
+
+
+def test_column_shards_cover_exactly():
+    for n, world in [(8192, 1), (8192, 8), (4096, 8), (14336, 8), (28672, 4), (1000, 3), (100, 8), (0, 2)]:
+        spans = [sharded.column_shard(n, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+            assert a1 == b0 and a0 <= a1
+        assert sum(sharded.shard_sizes(n, world)) == n
+        # every shard but the last non-empty one is a whole number of 256-wide tiles
+        nonempty = [b - a for a, b in spans if b > a]
+        assert all(w % 256 == 0 for w in nonempty[:-1])
+    assert sharded.column_shard(14336, 8, 3) == (3 * 1792, 4 * 1792)
+    with pytest.raises(ValueError):
+        sharded.column_shard(10, 2, 2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, n_total, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        rng = np.random.default_rng(7)                  # same operands on every rank
+        A = rng.standard_normal((48, 64)).astype(np.float32)
+        B = rng.standard_normal((n_total, 64)).astype(np.float32)
+        n0, n1 = sharded.column_shard(n_total, world, rank)
+        shard = torch.from_numpy(oracle.ref_gemm_tn(A, B[n0:n1].copy()).astype(np.float32)) \
+            if n1 > n0 else torch.zeros((48, 0))
+        full = sharded.all_gather_columns(shard, n_total)
+        want = torch.from_numpy(oracle.ref_gemm_tn(A, B).astype(np.float32))
+        q.put((rank, bool(torch.equal(full, want)), tuple(full.shape)))
+    except Exception as exc:  # report instead of leaving the parent to time out
+        q.put((rank, False, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n_total", [512, 700, 256])
+def test_all_gather_assembles_full_c_two_gloo_ranks(n_total):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_total, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=90) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in results) == [0, 1]
+    assert all(ok and shape == (48, n_total) for _, ok, shape in results), results

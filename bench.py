@@ -261,12 +261,22 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
+    # Denominator: the measured library GEMM on this pool. A timed region of a second or more
+    # runs under the power cap like the "sustained" measurement; a shorter one is compared with
+    # the (higher) burst figure.
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    region_s = total_ms * 1e-3
     if os.path.isfile(peaks_path):
-        peak = float(json.load(open(peaks_path))["bf16_tflops"])
-        peak_src = "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+        peaks = json.load(open(peaks_path))
+        burst = float(peaks["bf16_tflops"])
+        sustained = float(peaks.get("bf16_tflops_sustained", burst))
+        if region_s >= 1.0:
+            peak, peak_src = sustained, "of measured (MEASURED_PEAKS.json bf16_tflops_sustained; timed region >= 1 s)"
+        else:
+            peak, peak_src = burst, "of measured (MEASURED_PEAKS.json bf16_tflops, burst; timed region < 1 s)"
     else:
-        peak, peak_src = FALLBACK_BF16_TFLOPS, "fallback"
+        burst = sustained = None
+        peak, peak_src = FALLBACK_BF16_TFLOPS, "of fallback"
     kernel_ms = statistics.mean(per)
     achieved = flops_per_gpu / (kernel_ms * 1e-3) / 1e12
     traffic = NCU_DRAM_TRAFFIC_BYTES.get(args.workload)
@@ -291,7 +301,11 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak,
                      "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": traffic,
                      "peak_source": peak_src, "kernel_ms_mean": round(kernel_ms, 5),
-                     "kernel_ms_min": round(min(per), 5)},
+                     "kernel_ms_min": round(min(per), 5), "timed_region_s": round(region_s, 4),
+                     "frac_of_burst_peak": round(achieved / burst, 4) if burst else None,
+                     "frac_of_sustained_peak": round(achieved / sustained, 4) if sustained else None,
+                     "algorithmic_flops_per_launch": flops_per_gpu,
+                     "algorithmic_bytes_per_launch": (M * K + N * K) * 2 + M * N * 2},
     }
     if world == 1 and not args.no_cpu_baseline:
         tf, cores, kind, sample, _ = cpu_reference_sample(K, budget_s=12.0)
@@ -316,6 +330,7 @@ def run_reference(args):
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {desc}", "M": M, "N_per_gpu": N, "K": K,
+                   "layout": "TN (A row-major MxK, B K-major NxK)",
                    "note": "CPU arm: each step is a bounded sample of the workload (see cpu_baseline.sample)"},
         "cpu_baseline": {"value": round(tf, 6), "unit": "TFLOP/s", "cores": cores, "kind": kind,
                          "sample": sample},

@@ -57,6 +57,8 @@ typedef struct PatinaGemmConfig {
   int32_t max_ctas;  /* cap on persistent CTAs (0 = number of SMs) */
   int32_t m_sub;     /* 128-row accumulator sub-tiles per CTA: 1 or 2;
                         tile height = 128 * cta_group * m_sub */
+  int32_t stream_k;  /* skinny path (M <= 128, bf16 out): 0 = library decides, 1 = force,
+                        -1 = never */
 } PatinaGemmConfig;
 
 /* What a call would launch; computed on the host without touching a device. */
@@ -137,6 +139,19 @@ int patina_gemm_validate(int in_type, int out_type, const void* A, int64_t lda, 
 /* Launch plan for a problem on a device with `num_sms` SMs. */
 int patina_gemm_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
                      const PatinaGemmConfig* cfg, int num_sms, PatinaGemmPlan* out);
+
+/* The skinny (stream-K) path: the flat list of (128-row tile of B, k-block) units is cut
+ * into one contiguous range per CTA; tiles shared by several CTAs are reduced through
+ * context-owned scratch memory. These helpers expose the partition for host tests. */
+typedef struct PatinaStreamKPlan {
+  uint32_t grid, tiles, k_blocks, m_pad, max_contrib, stages, smem_bytes;
+  uint64_t units, partial_bytes, counter_bytes;
+} PatinaStreamKPlan;
+int patina_gemm_streamk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms,
+                             PatinaStreamKPlan* out);
+void patina_gemm_streamk_range(uint64_t cta, uint64_t units, uint64_t parts, uint64_t* begin,
+                               uint64_t* end);
+uint32_t patina_gemm_streamk_owner(uint64_t unit, uint64_t units, uint64_t parts);
 
 /* Derived encodings, exported so tests can pin them against the reference's
  * constants (crates/patina/tests/layout.rs:33-68; v2_gemm_pipelined.ptx:192,197). */

@@ -17,6 +17,7 @@
 
 #include "patina_desc.h"
 #include "patina_gemm_kernel.cuh"
+#include "patina_gemm_streamk.cuh"
 
 using namespace patina;
 
@@ -244,6 +245,11 @@ struct PatinaGemmContext {
   std::vector<std::pair<TensorMapKey, CUtensorMap>> tmaps;  // small most-recent-first cache
   bool smem_attr_set[kNumKernels] = {};
   int max_clusters[kNumKernels] = {};  // co-resident clusters per kernel (pairs only)
+  // scratch of the stream-K path: fp32 partial tiles and per-tile arrival counters
+  float* d_sk_partials = nullptr;
+  uint32_t* d_sk_counters = nullptr;
+  size_t cap_sk_partials = 0, cap_sk_counters = 0;
+  bool sk_attr_set[2] = {false, false};
   // device staging for patina_gemm_host
   void* d_a = nullptr;
   void* d_b = nullptr;
@@ -317,6 +323,110 @@ CUtensorMapDataType tmap_in_type(int in_type) {
   }
 }
 
+
+// ------------------------------------------------------------ stream-K path
+constexpr int kSkStages = 6;
+
+struct SkPlan {
+  uint32_t grid, tiles, k_blocks, m_pad, max_contrib;
+  uint64_t units, partial_bytes, counter_bytes;
+};
+
+bool streamk_supported(int in_type, int out_type, int64_t M) {
+  return out_type == kOutBF16 && (in_type == kBF16 || in_type == kE4M3) && M >= 1 && M <= 128;
+}
+
+SkPlan make_sk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms) {
+  SkPlan s{};
+  s.m_pad = (uint32_t)((M + 15) / 16 * 16);
+  s.tiles = ceil_div(N, kSkTileRows);
+  s.k_blocks = ceil_div(K, kBlockKBytes / input_bytes(in_type));
+  s.units = (uint64_t)s.tiles * s.k_blocks;
+  s.grid = (uint32_t)((uint64_t)num_sms < s.units ? (uint64_t)num_sms : s.units);
+  s.max_contrib = streamk_max_contrib(s.units, s.grid, s.k_blocks);
+  s.partial_bytes = (uint64_t)s.tiles * s.max_contrib * s.m_pad * 128ull * sizeof(float);
+  s.counter_bytes = (uint64_t)s.tiles * sizeof(uint32_t);
+  return s;
+}
+
+// Heuristic for the automatic choice: skinny M, and enough (tile, k-block) units that cutting
+// K across CTAs pays (otherwise the large-tile kernel's 128-wide tiles already fill the GPU).
+bool streamk_preferred(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
+  if (!streamk_supported(in_type, out_type, M)) return false;
+  const SkPlan s = make_sk_plan(in_type, M, N, K, num_sms);
+  return s.units >= 4ull * (uint64_t)num_sms;
+}
+
+template <int kIn>
+cudaError_t launch_sk_kernel(const SkPlan& sp, cudaStream_t stream, const CUtensorMap& tm_w,
+                             const CUtensorMap& tm_x, const StreamKParams& p, bool* attr_set) {
+  auto fn = gemm_streamk_kernel<kSkStages, kIn>;
+  const uint32_t smem = streamk_smem_bytes(kSkStages);
+  if (!*attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    *attr_set = true;
+  }
+  fn<<<sp.grid, 192, smem, stream>>>(tm_w, tm_x, p);
+  return cudaGetLastError();
+}
+
+int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t lda, const void* B,
+                   int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha,
+                   cudaStream_t stream) {
+  const SkPlan sp = make_sk_plan(in_type, M, N, K, ctx->num_sms);
+  // scratch: grow-only; counters start (and are left) at zero
+  if (ctx->cap_sk_partials < sp.partial_bytes) {
+    if (ctx->d_sk_partials) cudaFree(ctx->d_sk_partials);
+    ctx->d_sk_partials = nullptr;
+    ctx->cap_sk_partials = 0;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ctx->d_sk_partials), sp.partial_bytes);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMalloc(stream-K partials)");
+    ctx->cap_sk_partials = sp.partial_bytes;
+  }
+  if (ctx->cap_sk_counters < sp.counter_bytes) {
+    if (ctx->d_sk_counters) cudaFree(ctx->d_sk_counters);
+    ctx->d_sk_counters = nullptr;
+    ctx->cap_sk_counters = 0;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ctx->d_sk_counters), sp.counter_bytes);
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_sk_counters, 0, sp.counter_bytes);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMalloc(stream-K counters)");
+    ctx->cap_sk_counters = sp.counter_bytes;
+  }
+  const uint32_t ib = input_bytes(in_type);
+  const uint32_t kelems = kBlockKBytes / ib;
+  CUtensorMap tm_w, tm_x;
+  int rc = get_tensor_map(ctx, B, tmap_in_type(in_type), ib, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
+                          kSkTileRows, kelems, &tm_w);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
+                      sp.m_pad, kelems, &tm_x);
+  if (rc != PATINA_GEMM_OK) return rc;
+  StreamKParams p{};
+  p.M = (uint32_t)M;
+  p.N = (uint32_t)N;
+  p.K = (uint32_t)K;
+  p.m_pad = sp.m_pad;
+  p.tiles = sp.tiles;
+  p.k_blocks = sp.k_blocks;
+  p.units = sp.units;
+  p.max_contrib = sp.max_contrib;
+  p.alpha = alpha;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.ldc = ldc;
+  p.partials = ctx->d_sk_partials;
+  p.counters = ctx->d_sk_counters;
+  p.status = ctx->d_status;
+  p.wait_limit_ns = ctx->wait_limit_ns;
+  cudaError_t e = (in_type == kBF16)
+                      ? launch_sk_kernel<kBF16>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[0])
+                      : launch_sk_kernel<kE4M3>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[1]);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "stream-K launch");
+  ctx->launches += 1;
+  return PATINA_GEMM_OK;
+}
+
 int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A, int64_t lda,
                 const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                 float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream) {
@@ -333,6 +443,14 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemset2DAsync");
     return PATINA_GEMM_OK;
   }
+  const int want_sk = cfg ? cfg->stream_k : 0;
+  if (want_sk > 0 && !streamk_supported(in_type, out_type, M))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
+                     "stream_k needs M <= 128, bf16 or e4m3 inputs and bf16 output");
+  const bool explicit_tile = cfg && (cfg->cta_group != 0 || cfg->block_n != 0 || cfg->m_sub != 0);
+  if (want_sk > 0 || (want_sk == 0 && !explicit_tile &&
+                      streamk_preferred(in_type, out_type, M, N, K, ctx->num_sms)))
+    return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream);
   PatinaGemmPlan plan;
   const KernelEntry* k = nullptr;
   rc = make_plan(in_type, out_type, M, N, K, cfg, ctx->num_sms, &plan, &k, &err);
@@ -491,6 +609,8 @@ void patina_gemm_context_destroy(PatinaGemmContext* ctx) {
   {
     DeviceGuard guard(ctx->device);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_sk_partials) cudaFree(ctx->d_sk_partials);
+    if (ctx->d_sk_counters) cudaFree(ctx->d_sk_counters);
     if (ctx->d_a) cudaFree(ctx->d_a);
     if (ctx->d_b) cudaFree(ctx->d_b);
     if (ctx->d_c) cudaFree(ctx->d_c);
@@ -526,6 +646,8 @@ int patina_gemm_status(PatinaGemmContext* ctx, void* stream) {
   set_error(ctx, PATINA_GEMM_ERR_TIMEOUT,
             fmt("device wait expired: %s (code %u, block %u, detail %u)", what, st[0], st[1], st[2]));
   cudaMemset(ctx->d_status, 0, sizeof(st));
+  // an abandoned stream-K launch may have left arrival counters half-way
+  if (ctx->d_sk_counters) cudaMemset(ctx->d_sk_counters, 0, ctx->cap_sk_counters);
   return PATINA_GEMM_ERR_TIMEOUT;
 }
 
@@ -612,6 +734,32 @@ int patina_gemm_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
                      const PatinaGemmConfig* cfg, int num_sms, PatinaGemmPlan* out) {
   if (!out || M <= 0 || N <= 0 || K <= 0) return PATINA_GEMM_ERR_INVALID_ARG;
   return make_plan(in_type, out_type, M, N, K, cfg, num_sms, out, nullptr, nullptr);
+}
+
+int patina_gemm_streamk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms,
+                             PatinaStreamKPlan* out) {
+  if (!out || N <= 0 || K <= 0 || num_sms <= 0 || !streamk_supported(in_type, kOutBF16, M))
+    return PATINA_GEMM_ERR_INVALID_ARG;
+  const SkPlan s = make_sk_plan(in_type, M, N, K, num_sms);
+  out->grid = s.grid;
+  out->tiles = s.tiles;
+  out->k_blocks = s.k_blocks;
+  out->m_pad = s.m_pad;
+  out->max_contrib = s.max_contrib;
+  out->stages = kSkStages;
+  out->smem_bytes = streamk_smem_bytes(kSkStages);
+  out->units = s.units;
+  out->partial_bytes = s.partial_bytes;
+  out->counter_bytes = s.counter_bytes;
+  return PATINA_GEMM_OK;
+}
+void patina_gemm_streamk_range(uint64_t cta, uint64_t units, uint64_t parts, uint64_t* begin,
+                               uint64_t* end) {
+  if (begin) *begin = streamk_range_start(cta, units, parts);
+  if (end) *end = streamk_range_start(cta + 1, units, parts);
+}
+uint32_t patina_gemm_streamk_owner(uint64_t unit, uint64_t units, uint64_t parts) {
+  return streamk_owner(unit, units, parts);
 }
 
 uint64_t patina_gemm_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,

@@ -1,0 +1,317 @@
+// patina_gemm_streamk.cuh -- the skinny ("decode-shaped") GEMM: few rows of A,
+// many rows of B, deep K. Memory-bound: the job is to stream B from HBM once,
+// at full bandwidth, on every SM.
+//
+//   C[M,N] = alpha * X[M,K] * W[N,K]^T,   M <= 128 (X = activations, W = weights)
+//
+// Differences from the large-tile kernel (patina_gemm_kernel.cuh):
+//   * operands swapped for the tensor core: 128 rows of W are the MMA's M side
+//     (TMEM lanes), the M rows of X (padded to a multiple of 16) its N side
+//     (TMEM columns), so a skinny M wastes no tensor-core rows;
+//   * work is the flat list of (weight tile, k-block) units, cut into one
+//     contiguous range per CTA ("stream-K"), so all SMs pull bytes until the
+//     end whatever the number of weight tiles;
+//   * a weight tile whose K range is shared by several CTAs is reduced through
+//     global scratch memory without any CTA waiting for another: every
+//     contributor writes its fp32 partial tile, bumps the tile's counter, and the
+//     contributor that arrives last adds the partials up in contributor order
+//     (so the result does not depend on who was last) and writes C.
+//
+// Roles are the same 1 + 1 + 4 warps as the reference's generated kernel
+// (crates/patina/tests/golden/v2_gemm_pipelined.ptx:89-94).
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "patina_desc.h"
+#include "patina_gemm_kernel.cuh"
+#include "patina_ptx.cuh"
+
+namespace patina {
+
+struct StreamKParams {
+  uint32_t M, N, K;
+  uint32_t m_pad;          // M rounded up to 16: the MMA's N extent
+  uint32_t tiles;          // 128-row tiles of W
+  uint32_t k_blocks;       // 128-byte k-blocks per tile
+  uint64_t units;          // tiles * k_blocks
+  uint32_t max_contrib;    // partial slots reserved per tile
+  float alpha;
+  __nv_bfloat16* C;
+  int64_t ldc;
+  float* partials;         // [tiles][max_contrib][m_pad][128] fp32
+  uint32_t* counters;      // [tiles], zero between launches
+  uint32_t* status;
+  uint64_t wait_limit_ns;
+};
+
+enum : uint32_t { kTimeoutStreamK = 6 };
+
+constexpr uint32_t kSkTileRows = 128;
+constexpr uint32_t kSkStageStride = 32768;  // 16 KB of W + up to 16 KB of X
+constexpr uint32_t kSkTmemCols = 256;       // two accumulators of up to 128 columns
+
+PATINA_HD constexpr uint32_t streamk_smem_bytes(uint32_t stages) {
+  return 1024 + stages * kSkStageStride + kBarrierRegionBytes;
+}
+
+// First unit of CTA c's range, and the CTA that owns unit u, for `units` units cut into
+// `parts` contiguous ranges whose lengths differ by at most one.
+PATINA_HD uint64_t streamk_range_start(uint64_t c, uint64_t units, uint64_t parts) {
+  return c * units / parts;
+}
+PATINA_HD uint32_t streamk_owner(uint64_t u, uint64_t units, uint64_t parts) {
+  return (uint32_t)(((u + 1) * parts - 1) / units);
+}
+// Upper bound on the CTAs that can share one tile of `k_blocks` units.
+PATINA_HD uint32_t streamk_max_contrib(uint64_t units, uint64_t parts, uint32_t k_blocks) {
+  const uint64_t min_len = units / parts ? units / parts : 1;
+  return (uint32_t)((k_blocks - 1) / min_len) + 2;
+}
+
+template <int kStages, int kIn>
+__global__ void __launch_bounds__(192, 1)
+gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                    const StreamKParams p) {
+  constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
+  constexpr uint32_t kBlockKElems = kBlockKBytes / input_bytes(kIn);
+  constexpr uint32_t kUmmaK = umma_k(kIn);
+  constexpr uint32_t kWBytes = kSkTileRows * kBlockKBytes;
+  static_assert((2 * kStages + 4) * 8 + 16 <= kBarrierRegionBytes, "barrier region too small");
+  static_assert(streamk_smem_bytes(kStages) <= kMaxDynSmem, "shared-memory plan exceeds 227 KB");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t ring = smem_base;
+  const uint32_t bars = ring + kStages * kSkStageStride;
+  const uint32_t full_bar = bars;
+  const uint32_t empty_bar = bars + 8u * kStages;
+  const uint32_t tfull_bar = bars + 16u * kStages;
+  const uint32_t tempty_bar = tfull_bar + 16u;
+  const uint32_t tmem_slot = tempty_bar + 16u;
+  const uint32_t abort_slot = tmem_slot + 4u;
+  const uint32_t last_slot = abort_slot + 4u;
+  uint8_t* const smem_generic = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  volatile uint32_t* const tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot - smem_base));
+  volatile uint32_t* const abort_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_generic + (abort_slot - smem_base));
+  volatile uint32_t* const last_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_generic + (last_slot - smem_base));
+
+  const uint32_t warp_idx = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t parts = gridDim.x;
+  const uint64_t u_begin = streamk_range_start(blockIdx.x, p.units, parts);
+  const uint64_t u_end = streamk_range_start(blockIdx.x + 1ull, p.units, parts);
+  const uint32_t x_bytes = p.m_pad * kBlockKBytes;
+
+  WaitCtx w;
+  w.abort_flag = abort_ptr;
+  w.peer_abort_addr = 0u;
+  w.status = p.status;
+  w.limit_ns = p.wait_limit_ns;
+  w.has_peer = false;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tm_w);
+    ptx::prefetch_tensormap(&tm_x);
+    for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+      ptx::mbar_init(full_bar + 8u * s, 1);
+      ptx::mbar_init(empty_bar + 8u * s, 1);
+    }
+    for (uint32_t b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar + 8u * b, 1);
+      ptx::mbar_init(tempty_bar + 8u * b, 4);
+    }
+    *abort_ptr = 0u;
+    *last_ptr = 0u;
+    ptx::fence_mbar_init();
+  }
+  if (warp_idx == 1) {
+    ptx::tmem_alloc<1>(tmem_slot, kSkTmemCols);
+    ptx::tmem_relinquish<1>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // ------------------------------------------------------------ TMA producer
+  if (warp_idx == 0) {
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (uint64_t u = u_begin; u < u_end && ok; ++u) {
+        const uint32_t t = (uint32_t)(u / p.k_blocks);
+        const uint32_t kb = (uint32_t)(u - (uint64_t)t * p.k_blocks);
+        ok = bounded_wait<false>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
+        if (!ok) break;
+        const uint32_t sw = ring + s * kSkStageStride;
+        const int32_t k0 = (int32_t)(kb * kBlockKElems);
+        ptx::mbar_arrive_expect_tx(full_bar + 8u * s, kWBytes + x_bytes);
+        ptx::tma_load_2d(sw, &tm_w, full_bar + 8u * s, k0, (int32_t)(t * kSkTileRows));
+        ptx::tma_load_2d(sw + kWBytes, &tm_x, full_bar + 8u * s, k0, 0);
+        if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+      }
+    }
+  }
+  // -------------------------------------------------------------- MMA issuer
+  else if (warp_idx == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_v = idesc(kIn, kSkTileRows, p.m_pad);
+      uint32_t s = 0, ph = 0, seg = 0;
+      bool ok = true;
+      uint64_t u = u_begin;
+      while (u < u_end && ok) {
+        const uint32_t t = (uint32_t)(u / p.k_blocks);
+        const uint32_t kb0 = (uint32_t)(u - (uint64_t)t * p.k_blocks);
+        const uint64_t left = u_end - u;
+        const uint32_t kb1 = (uint64_t)(p.k_blocks - kb0) <= left ? p.k_blocks : kb0 + (uint32_t)left;
+        const uint32_t buf = seg & 1u, acc_ph = (seg >> 1) & 1u;
+        ok = bounded_wait<false>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * 128u;
+        for (uint32_t kb = kb0; kb < kb1; ++kb) {
+          ok = bounded_wait<false>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t sw = ring + s * kSkStageStride;
+          const uint64_t dw = smem_desc_sw128_kmajor(sw);
+          const uint64_t dx = smem_desc_sw128_kmajor(sw + kWBytes);
+#pragma unroll
+          for (uint32_t k = 0; k < kBlockKElems / kUmmaK; ++k) {
+            const uint32_t adv = k_advance_units_sw128(k * kUmmaK, kIn);
+            ptx::umma<1, kKind>(tmem_d, dw + adv, dx + adv, idesc_v, (kb != kb0 || k != 0u) ? 1u : 0u);
+          }
+          ptx::umma_commit<1>(empty_bar + 8u * s);
+          if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit<1>(tfull_bar + 8u * buf);
+        u += kb1 - kb0;
+        ++seg;
+      }
+      if (ok && seg > 0) {
+        const uint32_t last = seg - 1;
+        bounded_wait<false>(tfull_bar + 8u * (last & 1u), (last >> 1) & 1u, w, kTimeoutMmaDrain, seg);
+      }
+    }
+  }
+  // ---------------------------------------------------------------- epilogue
+  else {
+    const uint32_t q = warp_idx & 3u;
+    const uint32_t epi_tid = threadIdx.x - 64u;
+    uint32_t seg = 0;
+    // A warp whose wait was abandoned goes "dead": it touches no more data but still walks
+    // the segment list and joins the named barriers, so the other epilogue warps (which may
+    // have passed the same wait a moment earlier) can never be left waiting for it.
+    bool dead = false;
+    uint64_t u = u_begin;
+    while (u < u_end) {
+      const uint32_t t = (uint32_t)(u / p.k_blocks);
+      const uint32_t kb0 = (uint32_t)(u - (uint64_t)t * p.k_blocks);
+      const uint64_t left = u_end - u;
+      const uint32_t kb1 = (uint64_t)(p.k_blocks - kb0) <= left ? p.k_blocks : kb0 + (uint32_t)left;
+      const uint32_t buf = seg & 1u, acc_ph = (seg >> 1) & 1u;
+      if (!dead) {
+        bool ok = bounded_wait<false>(tfull_bar + 8u * buf, acc_ph, w, kTimeoutEpilogueTmemFull, t);
+        ok = __all_sync(0xffffffffu, ok);
+        dead = !ok;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * 128u;
+      const uint32_t n = t * kSkTileRows + q * 32u + lane;  // the column of C this thread owns
+      const bool whole = (kb0 == 0u && kb1 == p.k_blocks);
+      uint32_t my_j = 0, contribs = 1;
+      bool is_last = !dead;
+      if (!whole) {
+        const uint64_t tile_u0 = (uint64_t)t * p.k_blocks;
+        const uint32_t first_cta = streamk_owner(tile_u0, p.units, parts);
+        contribs = streamk_owner(tile_u0 + p.k_blocks - 1, p.units, parts) - first_cta + 1u;
+        my_j = blockIdx.x - first_cta;
+        // 1. publish this CTA's partial tile: slot layout [m][128 weight rows], coalesced
+        if (!dead) {
+          float* mine = p.partials + ((size_t)t * p.max_contrib + my_j) * ((size_t)p.m_pad * 128u);
+          for (uint32_t m0 = 0; m0 < p.m_pad; m0 += 16u) {
+            uint32_t v[16];
+            ptx::tmem_ld_32x32b_x16(taddr + m0, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i)
+              __stcg(mine + (size_t)(m0 + i) * 128u + q * 32u + lane, __uint_as_float(v[i]));
+          }
+          __threadfence();
+        }
+        ptx::named_bar_sync(1, 128);
+        if (epi_tid == 0) {
+          bool last = false;
+          if (!dead && *abort_ptr == 0u) {
+            const uint32_t seen = atomicAdd(p.counters + t, 1u);
+            last = (seen == contribs - 1u);
+            if (last) p.counters[t] = 0u;  // everybody has arrived: leave it clean for the next launch
+          }
+          *last_ptr = last ? 1u : 0u;
+        }
+        ptx::named_bar_sync(1, 128);
+        is_last = !dead && (*last_ptr != 0u);
+        if (is_last) __threadfence();
+      }
+      if (is_last) {
+        // 2. sum the contributors in their fixed order (this CTA's part comes from TMEM), scale,
+        //    round to bf16 and store C[m][n]
+        const float* slot0 = p.partials + (size_t)t * p.max_contrib * ((size_t)p.m_pad * 128u);
+        for (uint32_t m0 = 0; m0 < p.m_pad; m0 += 16u) {
+          uint32_t v[16];
+          ptx::tmem_ld_32x32b_x16(taddr + m0, v);
+          ptx::tmem_ld_wait();
+          float acc[16];
+#pragma unroll
+          for (uint32_t i = 0; i < 16; ++i) acc[i] = 0.0f;
+          for (uint32_t j = 0; j < contribs; ++j) {
+            if (j == my_j) {
+#pragma unroll
+              for (uint32_t i = 0; i < 16; ++i)
+                acc[i] = (j == 0u) ? __uint_as_float(v[i]) : acc[i] + __uint_as_float(v[i]);
+            } else {
+              const float* other = slot0 + (size_t)j * ((size_t)p.m_pad * 128u);
+#pragma unroll
+              for (uint32_t i = 0; i < 16; ++i) {
+                const float x = __ldcg(other + (size_t)(m0 + i) * 128u + q * 32u + lane);
+                acc[i] = (j == 0u) ? x : acc[i] + x;
+              }
+            }
+          }
+          if (n < p.N) {
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i)
+              if (m0 + i < p.M) p.C[(size_t)(m0 + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
+          }
+        }
+      }
+      // accumulator drained: hand the TMEM buffer back
+      if (!dead) {
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(tempty_bar + 8u * buf);
+      }
+      u += kb1 - kb0;
+      ++seg;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  if (*abort_ptr) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  __syncwarp();
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (warp_idx == 1) ptx::tmem_dealloc<1>(tmem_base, kSkTmemCols);
+}
+
+}  // namespace patina

@@ -21,13 +21,21 @@ SYMBOLS = (
     "patina_gemm_f16_tn_f32out", "patina_gemm_ex", "patina_gemm_host", "patina_gemm_validate",
     "patina_gemm_plan", "patina_gemm_smem_desc", "patina_gemm_idesc",
     "patina_gemm_k_advance_units", "patina_gemm_tmem_lane_offset", "patina_gemm_tile_coord",
-    "patina_gemm_version",
+    "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_range",
+    "patina_gemm_streamk_owner",
 )
+
+
+class StreamKPlan(C.Structure):
+    _fields_ = [("grid", C.c_uint32), ("tiles", C.c_uint32), ("k_blocks", C.c_uint32),
+                ("m_pad", C.c_uint32), ("max_contrib", C.c_uint32), ("stages", C.c_uint32),
+                ("smem_bytes", C.c_uint32), ("units", C.c_uint64), ("partial_bytes", C.c_uint64),
+                ("counter_bytes", C.c_uint64)]
 
 
 class GemmConfig(C.Structure):
     _fields_ = [("cta_group", C.c_int32), ("block_n", C.c_int32), ("stages", C.c_int32),
-                ("group_m", C.c_int32), ("max_ctas", C.c_int32), ("m_sub", C.c_int32)]
+                ("group_m", C.c_int32), ("max_ctas", C.c_int32), ("m_sub", C.c_int32), ("stream_k", C.c_int32)]
 
 
 class GemmPlan(C.Structure):
@@ -87,6 +95,11 @@ def load() -> C.CDLL:
     L.patina_gemm_tile_coord.argtypes = [C.c_uint32] * 4 + [C.POINTER(C.c_uint32)] * 2
     L.patina_gemm_tile_coord.restype = None
     L.patina_gemm_version.restype = C.c_char_p
+    L.patina_gemm_streamk_plan.argtypes = [i32, i64, i64, i64, i32, C.POINTER(StreamKPlan)]
+    L.patina_gemm_streamk_range.argtypes = [C.c_uint64] * 3 + [C.POINTER(C.c_uint64)] * 2
+    L.patina_gemm_streamk_range.restype = None
+    L.patina_gemm_streamk_owner.argtypes = [C.c_uint64] * 3
+    L.patina_gemm_streamk_owner.restype = C.c_uint32
     _lib = L
     return L
 
@@ -107,6 +120,14 @@ def plan(in_type, out_type, M, N, K, config: GemmConfig | None = None, num_sms: 
                                  C.byref(p))
     if rc != OK:
         raise ValueError(f"patina_gemm_plan failed with code {rc}")
+    return p
+
+
+def streamk_plan(in_type, M, N, K, num_sms: int = 148) -> StreamKPlan:
+    p = StreamKPlan()
+    rc = load().patina_gemm_streamk_plan(in_type, M, N, K, num_sms, C.byref(p))
+    if rc != OK:
+        raise ValueError(f"patina_gemm_streamk_plan failed with code {rc}")
     return p
 
 

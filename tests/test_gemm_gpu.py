@@ -188,6 +188,54 @@ def test_fp8_e4m3(ctx, oracle_mod, M, N, K):
         check_norm(oracle_mod, out, want, f"fp8 {name}")
 
 
+# ------------------------------------------------------------ skinny (stream-K) path
+@pytest.mark.parametrize("M,N,K", [(16, 512, 256), (1, 136, 64), (64, 1000, 2120), (100, 3584, 1024),
+                                   (128, 2048, 8192), (33, 28672, 512)])
+def test_streamk_matches_oracle_and_large_tile_kernel(ctx, oracle_mod, M, N, K):
+    """Skinny problems through the stream-K kernel (forced), against the oracle and against
+    the large-tile kernel; run twice to check that the arrival counters are left clean."""
+    from patina_b200 import inputs, GemmConfig
+    A, B = inputs.make_operands("llm", M, N, K, seed=N + K)
+    want = expect_bf16(oracle_mod, A, B, alpha=1.5)
+    ldc = (N + 7) // 8 * 8
+    dA, dB = A.cuda(), B.cuda()
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :N]
+        ctx.gemm_tn(dA, dB, out=out, alpha=1.5, config=GemmConfig(0, 0, 0, 0, 0, 0, 1))
+        ctx.status()
+        check_norm(oracle_mod, out, want, f"stream-K {M}x{N}x{K}")
+        outs.append(out.clone())
+    assert torch.equal(outs[0], outs[1])  # deterministic: fixed reduction order
+    tiled = torch.empty((M, ldc), dtype=torch.bfloat16, device="cuda")[:, :N]
+    ctx.gemm_tn(dA, dB, out=tiled, alpha=1.5, config=GemmConfig(0, 0, 0, 0, 0, 0, -1))
+    ctx.status()
+    check_norm(oracle_mod, tiled, outs[0].float().cpu().numpy(), "large-tile vs stream-K")
+
+
+def test_streamk_decode_shapes_full_size(ctx, oracle_mod):
+    """The decode-shaped configurations at full size (N=28672, K=8192, M in {16, 64, 128}):
+    automatic dispatch must take the stream-K path; 128 sampled columns of C against the
+    oracle (computed as rows of B x A^T), and fp8 inputs on the same path."""
+    from patina_b200 import inputs
+    N, K = 28672, 8192
+    rng = np.random.default_rng(9)
+    cols = np.unique(np.concatenate([[0, 127, 128, N - 1], rng.integers(0, N, 124)])).astype(np.int64)
+    for M in (16, 64, 128):
+        A, B = inputs.make_operands("llm", M, N, K, seed=M)
+        before = ctx.launch_count
+        out = ctx.gemm_tn(A.cuda(), B.cuda())
+        ctx.status()
+        assert ctx.launch_count == before + 1
+        ref_t = oracle_mod.ref_gemm_tn(widen(oracle_mod, B), widen(oracle_mod, A), rows=cols)  # [cols, M]
+        want = oracle_mod.scale_round_bf16(ref_t.T.copy(), 1.0)
+        check_norm(oracle_mod, out[:, torch.from_numpy(cols).cuda()], want, f"decode M={M}")
+    Aq, sa, Bq, sb = inputs.make_fp8_operands(32, 4096, 4096)
+    out = ctx.gemm_fp8e4m3_tn(Aq.cuda(), Bq.cuda(), sa, sb)
+    ctx.status()
+    check_norm(oracle_mod, out, expect_bf16(oracle_mod, Aq, Bq, alpha=sa * sb), "fp8 stream-K")
+
+
 # ------------------------------------------------------- full benchmark sizes
 def test_bf16_8192_cubed_samples_and_properties(ctx, oracle_mod):
     """8192^3 (the benchmark size): 64 sampled rows against the oracle, plus

@@ -152,3 +152,38 @@ def test_inputs_are_deterministic():
     Aq, sa, Bq, sb = inputs.make_fp8_operands(32, 16, 64)
     assert Aq.dtype == torch.float8_e4m3fn and abs(float(Aq.float().abs().max()) - 448.0) < 1e-3
     assert sa > 0 and sb > 0
+
+
+# ------------------------------------------------------------------ stream-K partition
+@pytest.mark.parametrize("M,N,K,sms", [(16, 28672, 8192, 148), (128, 28672, 8192, 148), (64, 3584, 8192, 148),
+                                       (1, 128, 64, 148), (128, 1000, 200, 148), (32, 4096, 14336, 132),
+                                       (128, 28672, 8192, 7)])
+def test_streamk_partition(built_lib, M, N, K, sms):
+    p = L.streamk_plan(L.IN_BF16, M, N, K, sms)
+    assert p.m_pad % 16 == 0 and M <= p.m_pad < M + 16
+    assert p.tiles == -(-N // 128) and p.k_blocks == -(-K // 64) and p.units == p.tiles * p.k_blocks
+    assert p.grid == min(sms, p.units) and p.smem_bytes <= 232448
+    assert p.partial_bytes == p.tiles * p.max_contrib * p.m_pad * 128 * 4 and p.counter_bytes == p.tiles * 4
+    b, e = C.c_uint64(), C.c_uint64()
+    prev_end, lens = 0, []
+    for c in range(p.grid):
+        built_lib.patina_gemm_streamk_range(c, p.units, p.grid, C.byref(b), C.byref(e))
+        assert b.value == prev_end and e.value > b.value          # contiguous, never empty
+        prev_end = e.value
+        lens.append(e.value - b.value)
+        # the owner function inverts the ranges at both ends
+        assert built_lib.patina_gemm_streamk_owner(b.value, p.units, p.grid) == c
+        assert built_lib.patina_gemm_streamk_owner(e.value - 1, p.units, p.grid) == c
+    assert prev_end == p.units and max(lens) - min(lens) <= 1
+    # contributors of every tile fit the slots reserved for it
+    for t in range(0, p.tiles, max(1, p.tiles // 97)):
+        first = built_lib.patina_gemm_streamk_owner(t * p.k_blocks, p.units, p.grid)
+        last = built_lib.patina_gemm_streamk_owner((t + 1) * p.k_blocks - 1, p.units, p.grid)
+        assert 1 <= last - first + 1 <= p.max_contrib
+
+
+def test_streamk_plan_rejects_wide_m():
+    with pytest.raises(ValueError):
+        L.streamk_plan(L.IN_BF16, 129, 4096, 4096)
+    with pytest.raises(ValueError):
+        L.streamk_plan(L.IN_F16, 16, 4096, 4096)

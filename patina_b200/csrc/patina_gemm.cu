@@ -325,8 +325,6 @@ CUtensorMapDataType tmap_in_type(int in_type) {
 
 
 // ------------------------------------------------------------ stream-K path
-constexpr int kSkStages = 6;
-
 struct SkPlan {
   uint32_t grid, tiles, k_blocks, m_pad, max_contrib;
   uint64_t units, partial_bytes, counter_bytes;
@@ -360,11 +358,12 @@ bool streamk_preferred(int in_type, int out_type, int64_t M, int64_t N, int64_t 
 template <int kIn>
 cudaError_t launch_sk_kernel(const SkPlan& sp, cudaStream_t stream, const CUtensorMap& tm_w,
                              const CUtensorMap& tm_x, const StreamKParams& p, bool* attr_set) {
-  auto fn = gemm_streamk_kernel<kSkStages, kIn>;
-  const uint32_t smem = streamk_smem_bytes(kSkStages);
+  auto fn = gemm_streamk_kernel<kIn>;
+  const uint32_t smem = streamk_smem_bytes(p.m_pad);
   if (!*attr_set) {
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn),
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kMaxDynSmem);
     if (e != cudaSuccess) return e;
     *attr_set = true;
   }
@@ -412,6 +411,8 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.k_blocks = sp.k_blocks;
   p.units = sp.units;
   p.max_contrib = sp.max_contrib;
+  p.stages = streamk_stages(sp.m_pad);
+  p.stage_stride = streamk_stage_stride(sp.m_pad);
   p.alpha = alpha;
   p.C = static_cast<__nv_bfloat16*>(C);
   p.ldc = ldc;
@@ -746,8 +747,8 @@ int patina_gemm_streamk_plan(int in_type, int64_t M, int64_t N, int64_t K, int n
   out->k_blocks = s.k_blocks;
   out->m_pad = s.m_pad;
   out->max_contrib = s.max_contrib;
-  out->stages = kSkStages;
-  out->smem_bytes = streamk_smem_bytes(kSkStages);
+  out->stages = streamk_stages(s.m_pad);
+  out->smem_bytes = streamk_smem_bytes(s.m_pad);
   out->units = s.units;
   out->partial_bytes = s.partial_bytes;
   out->counter_bytes = s.counter_bytes;
@@ -781,3 +782,4 @@ void patina_gemm_tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint
 }
 
 }  // extern "C"
+

@@ -36,6 +36,8 @@ struct StreamKParams {
   uint32_t k_blocks;       // 128-byte k-blocks per tile
   uint64_t units;          // tiles * k_blocks
   uint32_t max_contrib;    // partial slots reserved per tile
+  uint32_t stages;         // ring depth (<= kSkMaxStages)
+  uint32_t stage_stride;   // bytes per stage: 16 KB of W + m_pad * 128 bytes of X
   float alpha;
   __nv_bfloat16* C;
   int64_t ldc;
@@ -48,11 +50,21 @@ struct StreamKParams {
 enum : uint32_t { kTimeoutStreamK = 6 };
 
 constexpr uint32_t kSkTileRows = 128;
-constexpr uint32_t kSkStageStride = 32768;  // 16 KB of W + up to 16 KB of X
+constexpr uint32_t kSkMaxStages = 13;       // what the barrier region has room for
 constexpr uint32_t kSkTmemCols = 256;       // two accumulators of up to 128 columns
 
-PATINA_HD constexpr uint32_t streamk_smem_bytes(uint32_t stages) {
-  return 1024 + stages * kSkStageStride + kBarrierRegionBytes;
+// One stage holds a 128-row slab of W and an m_pad-row slab of X, 128 bytes of K each. The
+// ring takes whatever shared memory allows: a skinny X leaves room for more stages, i.e. more
+// bytes of W in flight per SM, which is what a bandwidth-bound kernel lives on.
+PATINA_HD constexpr uint32_t streamk_stage_stride(uint32_t m_pad) {
+  return kSkTileRows * kBlockKBytes + m_pad * kBlockKBytes;
+}
+PATINA_HD constexpr uint32_t streamk_stages(uint32_t m_pad) {
+  const uint32_t fit = (kMaxDynSmem - 1024 - kBarrierRegionBytes) / streamk_stage_stride(m_pad);
+  return fit < kSkMaxStages ? fit : kSkMaxStages;
+}
+PATINA_HD constexpr uint32_t streamk_smem_bytes(uint32_t m_pad) {
+  return 1024 + streamk_stages(m_pad) * streamk_stage_stride(m_pad) + kBarrierRegionBytes;
 }
 
 // First unit of CTA c's range, and the CTA that owns unit u, for `units` units cut into
@@ -69,7 +81,7 @@ PATINA_HD uint32_t streamk_max_contrib(uint64_t units, uint64_t parts, uint32_t 
   return (uint32_t)((k_blocks - 1) / min_len) + 2;
 }
 
-template <int kStages, int kIn>
+template <int kIn>
 __global__ void __launch_bounds__(192, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     const StreamKParams p) {
@@ -77,16 +89,17 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   constexpr uint32_t kBlockKElems = kBlockKBytes / input_bytes(kIn);
   constexpr uint32_t kUmmaK = umma_k(kIn);
   constexpr uint32_t kWBytes = kSkTileRows * kBlockKBytes;
-  static_assert((2 * kStages + 4) * 8 + 16 <= kBarrierRegionBytes, "barrier region too small");
-  static_assert(streamk_smem_bytes(kStages) <= kMaxDynSmem, "shared-memory plan exceeds 227 KB");
+  static_assert((2 * kSkMaxStages + 4) * 8 + 16 <= kBarrierRegionBytes, "barrier region too small");
+  const uint32_t kStages = p.stages;
+  const uint32_t kSkStageStride = p.stage_stride;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = smem_base;
   const uint32_t bars = ring + kStages * kSkStageStride;
   const uint32_t full_bar = bars;
-  const uint32_t empty_bar = bars + 8u * kStages;
-  const uint32_t tfull_bar = bars + 16u * kStages;
+  const uint32_t empty_bar = bars + 8u * kSkMaxStages;
+  const uint32_t tfull_bar = bars + 16u * kSkMaxStages;
   const uint32_t tempty_bar = tfull_bar + 16u;
   const uint32_t tmem_slot = tempty_bar + 16u;
   const uint32_t abort_slot = tmem_slot + 4u;
@@ -116,7 +129,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_w);
     ptx::prefetch_tensormap(&tm_x);
-    for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+    for (uint32_t s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar + 8u * s, 1);
       ptx::mbar_init(empty_bar + 8u * s, 1);
     }
@@ -142,6 +155,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
+      // W is read exactly once: keep it from displacing X (re-read by every CTA) in L2.
+      const uint64_t stream_once = ptx::l2_policy_evict_first();
+      const uint64_t keep = ptx::l2_policy_evict_last();
       for (uint64_t u = u_begin; u < u_end && ok; ++u) {
         const uint32_t t = (uint32_t)(u / p.k_blocks);
         const uint32_t kb = (uint32_t)(u - (uint64_t)t * p.k_blocks);
@@ -150,9 +166,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t sw = ring + s * kSkStageStride;
         const int32_t k0 = (int32_t)(kb * kBlockKElems);
         ptx::mbar_arrive_expect_tx(full_bar + 8u * s, kWBytes + x_bytes);
-        ptx::tma_load_2d(sw, &tm_w, full_bar + 8u * s, k0, (int32_t)(t * kSkTileRows));
-        ptx::tma_load_2d(sw + kWBytes, &tm_x, full_bar + 8u * s, k0, 0);
-        if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+        ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * s, k0, (int32_t)(t * kSkTileRows), stream_once);
+        ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * s, k0, 0, keep);
+        if (++s == kStages) { s = 0; ph ^= 1u; }
       }
     }
   }
@@ -186,7 +202,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             ptx::umma<1, kKind>(tmem_d, dw + adv, dx + adv, idesc_v, (kb != kb0 || k != 0u) ? 1u : 0u);
           }
           ptx::umma_commit<1>(empty_bar + 8u * s);
-          if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+          if (++s == kStages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
         ptx::umma_commit<1>(tfull_bar + 8u * buf);

@@ -129,6 +129,39 @@ int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const vo
                      int64_t M, int64_t N, int64_t K, float alpha, const PatinaGemmConfig* cfg,
                      void* stream);
 
+/* ---- allocation-free entry point ---------------------------------------------- */
+/* No counterpart in the reference (which allocates per run, gemm_check.cpp:266-272).
+ *
+ * For callers that must not allocate device memory: code running inside an allocator's own
+ * callback, a process whose device memory is fully carved up and audited at start-up, a loop
+ * that cannot afford cudaMalloc's implicit device-wide synchronisation. The context API
+ * allocates (status word, scratch that grows on demand); this call allocates nothing, ever:
+ * no cudaMalloc, no cudaFree, no library routine that allocates.
+ *
+ * It runs the skinny stream-K GEMM, bf16 in / bf16 out, C = alpha * A[M,K] * B[N,K]^T with
+ * 1 <= M <= 128, on the CURRENT device, enqueued on `stream`, without synchronising. A, B, C
+ * are device pointers under the usual alignment rules. Its scratch (partial tiles, arrival
+ * counters, a wait-expiry record) is a fixed array inside the loaded module:
+ * PATINA_GEMM_NOALLOC_PARTIAL_BYTES of partial-tile space plus 64 KiB of counters. Every GPU
+ * that loads the library holds that array until the process exits. A problem whose partial
+ * tiles do not fit is refused with PATINA_GEMM_ERR_INVALID_ARG and a message saying how many
+ * bytes it would need (roughly: ceil(N/128) * 2 * round16(M) * 512 bytes).
+ *
+ * All calls on one GPU share the array and it keeps the last call's contents; the call clears
+ * what must start at zero, on `stream`, before launching. Two calls that overlap on the same
+ * GPU therefore race: issue them on one stream, or otherwise order them.
+ *
+ * The first call on each device does a one-time set-up (device queries, a driver entry-point
+ * lookup, the address of the scratch array); make that first call outside any stream capture.
+ * A device-side wait that runs out still ends the kernel after its bound, but this entry
+ * point has no way to report it; use the context API when that report is needed.
+ * err_buf (optional) receives a NUL-terminated diagnostic on failure. */
+#define PATINA_GEMM_NOALLOC_PARTIAL_BYTES (16u * 1024u * 1024u)
+int patina_gemm_bf16_tn_skinny_noalloc(const void* A, int64_t lda, const void* B, int64_t ldb,
+                                       void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                                       float alpha, void* stream, char* err_buf,
+                                       size_t err_buf_len);
+
 /* ---- host-only helpers (no device needed) ---------------------------------- */
 /* Argument check used by every entry point; on failure returns
  * PATINA_GEMM_ERR_INVALID_ARG and, if err_out != NULL, a heap diagnostic. */

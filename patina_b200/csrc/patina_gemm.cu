@@ -783,3 +783,162 @@ void patina_gemm_tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint
 
 }  // extern "C"
 
+// ====================================================== allocation-free entry ======
+// Some callers may not allocate device memory at all: code that runs inside a memory pool's
+// own allocation callback, a serving process whose device memory is fully pre-partitioned
+// and audited at start-up, or a latency-critical loop where cudaMalloc's implicit device
+// synchronisation is forbidden. The context API above allocates (status word, stream-K
+// scratch, growing on demand), so it is closed to them. This one entry point runs the
+// stream-K skinny GEMM with its scratch in a fixed array that is part of the loaded module.
+//
+// The array exists once per GPU that loads the library and stays until the process exits.
+// Every call on that GPU shares it and it keeps whatever the previous call left, so the
+// part that must start at zero is cleared on the stream before each launch, and two calls
+// that overlap on the same GPU (different streams, different threads) race on it.
+namespace {
+
+constexpr size_t kNoAllocStatusBytes = 256;                 // wait-expiry record
+constexpr size_t kNoAllocCounterBytes = 64 * 1024;          // up to 16384 tiles of B
+constexpr size_t kNoAllocPartialBytes = PATINA_GEMM_NOALLOC_PARTIAL_BYTES;
+constexpr size_t kNoAllocScratchBytes = kNoAllocStatusBytes + kNoAllocCounterBytes + kNoAllocPartialBytes;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // DEVICE address of g_noalloc_scratch on this GPU
+  int num_sms = 0;
+};
+NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+EncodeTiledFn g_noalloc_encode = nullptr;
+
+int noalloc_fail(char* buf, size_t len, int code, const char* f, ...) {
+  if (buf && len) {
+    va_list ap;
+    va_start(ap, f);
+    std::vsnprintf(buf, len, f, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+// The two maps the kernel needs, built on the stack; no cache, no heap.
+int noalloc_encode(EncodeTiledFn enc, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                   uint32_t box_rows, CUtensorMap* out) {
+  const cuuint64_t gdim[2] = {cols, rows};
+  const cuuint64_t gstride[1] = {ld * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estride[2] = {1, 1};
+  CUresult rc = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride,
+                    box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : (int)rc;
+}
+
+}  // namespace
+
+extern "C" int patina_gemm_bf16_tn_skinny_noalloc(const void* A, int64_t lda, const void* B,
+                                                  int64_t ldb, void* C, int64_t ldc, int64_t M,
+                                                  int64_t N, int64_t K, float alpha, void* stream_v,
+                                                  char* err_buf, size_t err_buf_len) {
+  if (err_buf && err_buf_len) err_buf[0] = '\0';
+  if (M < 1 || M > 128)
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_INVALID_ARG,
+                        "M=%lld is outside this entry point's range 1..128", (long long)M);
+  if (N < 1 || K < 1)
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_INVALID_ARG, "N and K must be positive");
+  std::string why;
+  int rc = validate_args(kBF16, kOutBF16, A, lda, B, ldb, C, ldc, M, N, K, &why);
+  if (rc != PATINA_GEMM_OK) return noalloc_fail(err_buf, err_buf_len, rc, "%s", why.c_str());
+
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0) {
+    cudaGetLastError();
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_UNSUPPORTED_ARCH, "no current CUDA device");
+  }
+  if (dev >= kNoAllocMaxDevices)
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_INVALID_ARG, "device index %d too large", dev);
+
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (!d.ready) {
+    // First call on this device: one-time set-up, with this device current. It queries the
+    // device, resolves a driver entry point and asks the runtime for the DEVICE address of the
+    // scratch array (in host code the array's name is only a host-side handle; passing it to a
+    // kernel would hand the GPU a host address). Do this first call outside any stream capture.
+    int major = 0, sms = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess)
+      return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_CUDA, "cudaDeviceGetAttribute: %s",
+                          cudaGetErrorString(e));
+    if (major != 10)
+      return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_UNSUPPORTED_ARCH,
+                          "device %d is not sm_100 (tcgen05 needs Blackwell)", dev);
+    if (!g_noalloc_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+      if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+        return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_CUDA, "cuTensorMapEncodeTiled not found");
+      g_noalloc_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    unsigned char* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr)
+      return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_CUDA, "cudaGetSymbolAddress(scratch): %s",
+                          cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(gemm_streamk_kernel<kBF16>),
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
+    if (e != cudaSuccess)
+      return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_CUDA, "cudaFuncSetAttribute: %s",
+                          cudaGetErrorString(e));
+    d.scratch = ptr;
+    d.num_sms = sms;
+    d.ready = true;
+  }
+
+  const SkPlan sp = make_sk_plan(kBF16, M, N, K, d.num_sms);
+  if (sp.partial_bytes > kNoAllocPartialBytes || sp.counter_bytes > kNoAllocCounterBytes)
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_INVALID_ARG,
+                        "problem needs %llu bytes of partial-tile scratch and %llu of counters; this entry "
+                        "point's fixed scratch holds %llu and %llu (use the context API for larger problems)",
+                        (unsigned long long)sp.partial_bytes, (unsigned long long)sp.counter_bytes,
+                        (unsigned long long)kNoAllocPartialBytes, (unsigned long long)kNoAllocCounterBytes);
+
+  CUtensorMap tm_w, tm_x;
+  if (noalloc_encode(g_noalloc_encode, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, kSkTileRows, &tm_w) ||
+      noalloc_encode(g_noalloc_encode, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, sp.m_pad, &tm_x))
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  // The previous call's leftovers: the status record and the arrival counters must be zero.
+  e = cudaMemsetAsync(d.scratch, 0, kNoAllocStatusBytes + sp.counter_bytes, stream);
+  if (e != cudaSuccess)
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+
+  StreamKParams p{};
+  p.M = (uint32_t)M;
+  p.N = (uint32_t)N;
+  p.K = (uint32_t)K;
+  p.m_pad = sp.m_pad;
+  p.tiles = sp.tiles;
+  p.k_blocks = sp.k_blocks;
+  p.units = sp.units;
+  p.max_contrib = sp.max_contrib;
+  p.stages = streamk_stages(sp.m_pad);
+  p.stage_stride = streamk_stage_stride(sp.m_pad);
+  p.alpha = alpha;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.ldc = ldc;
+  p.status = reinterpret_cast<uint32_t*>(d.scratch);
+  p.counters = reinterpret_cast<uint32_t*>(d.scratch + kNoAllocStatusBytes);
+  p.partials = reinterpret_cast<float*>(d.scratch + kNoAllocStatusBytes + kNoAllocCounterBytes);
+  p.wait_limit_ns = 2000000000ull;
+  gemm_streamk_kernel<kBF16><<<sp.grid, 192, streamk_smem_bytes(sp.m_pad), stream>>>(tm_w, tm_x, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return noalloc_fail(err_buf, err_buf_len, PATINA_GEMM_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return PATINA_GEMM_OK;
+}

@@ -35,13 +35,37 @@ METRIC = "GEMM TFLOP/s per GPU and % of tcgen05 peak (bf16 8192³) at 1/2/4/8 B2
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def _wl(M, N, K, dist, desc, dtype="bf16", bound="tensor", scaling="weak", rotate=1):
+    return {"M": M, "N": N, "K": K, "dist": dist, "desc": desc, "dtype": dtype, "bound": bound,
+            "scaling": scaling, "rotate": rotate}
+
+
+# scaling "weak": every GPU gets N columns (N-column shards of an N*gpus-wide problem);
+# scaling "strong": the N columns are split over the GPUs (N / gpus each).
 WORKLOADS = {
-    # name: (M, N per GPU, K, distribution, description)
-    "bf16_tn_8192": (8192, 8192, 8192, "normal_0p1",
-                     "bf16 TN GEMM M=N=K=8192, N(0,1)*0.1, fp32 accumulate, bf16 out"),
-    "bf16_tn_4096": (4096, 4096, 4096, "normal_0p1",
-                     "bf16 TN GEMM M=N=K=4096, N(0,1)*0.1, fp32 accumulate, bf16 out"),
+    "bf16_tn_8192": _wl(8192, 8192, 8192, "normal_0p1",
+                        "bf16 TN GEMM M=N=K=8192, N(0,1)*0.1, fp32 accumulate, bf16 out"),
+    "bf16_tn_4096": _wl(4096, 4096, 4096, "normal_0p1",
+                        "bf16 TN GEMM M=N=K=4096, N(0,1)*0.1, fp32 accumulate, bf16 out"),
+    "fp8_tn_8192": _wl(8192, 8192, 8192, "unit_normal", "fp8 e4m3 TN GEMM M=N=K=8192, per-tensor scales "
+                       "amax/448, fp32 accumulate, bf16 out scaled by sa*sb", dtype="e4m3"),
+    "fp8_tn_16384": _wl(16384, 16384, 16384, "unit_normal", "fp8 e4m3 TN GEMM M=N=K=16384, per-tensor "
+                        "scales, bf16 out; N split over the GPUs", dtype="e4m3", scaling="strong"),
 }
+for _n, _k in ((4096, 4096), (14336, 4096), (4096, 14336), (28672, 8192)):
+    WORKLOADS[f"llm_proj_{_n}x{_k}"] = _wl(
+        8192, _n, _k, "llm", f"LLM projection bf16 TN GEMM M=8192 tokens, N={_n}, K={_k}, activations "
+        "N(0,1), weights N(0,0.02); N split over the GPUs", scaling="strong")
+for _m in (16, 64, 128):
+    WORKLOADS[f"skinny_m{_m}"] = _wl(
+        _m, 28672, 8192, "llm", f"decode-shaped bf16 TN GEMM M={_m}, N=28672, K=8192 (memory-bound); "
+        "N split over the GPUs; 3 weight buffers in rotation (each larger than L2)",
+        bound="hbm", scaling="strong", rotate=3)
 
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture;
 # see profiles/. None until a capture of that workload exists.
@@ -186,27 +210,47 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     rank, local_rank, world = dist_env()
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run "
-                             "--nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench.py --gpus N")
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run "
+                         "--nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench.py --gpus N")
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     import patina_b200
-    from patina_b200 import inputs
+    from patina_b200 import inputs, sharded
 
-    M, N, K, distn, desc = WORKLOADS[args.workload]
+    wl = WORKLOADS[args.workload]
+    M, K = wl["M"], wl["K"]
+    if wl["scaling"] == "strong":
+        n0, n1 = sharded.column_shard(wl["N"], world, rank)
+        N = n1 - n0
+        n_total = wl["N"]
+    else:
+        N = wl["N"]
+        n_total = wl["N"] * world
+    fp8 = wl["dtype"] == "e4m3"
+    ebytes = 1 if fp8 else 2
     ctx = patina_b200.GemmContext(local_rank)
-    # Column shard of this rank: its own seed, so shards differ like real weight shards do.
-    A_h, B_h = inputs.make_operands(distn, M, N, K, seed=inputs.DEFAULT_SEED + rank, pin=True)
-    if world > 1:
-        # A is replicated: every rank uses rank 0's activations.
-        A_h0, _ = inputs.make_operands(distn, M, 1, K, seed=inputs.DEFAULT_SEED)
-        A_h.copy_(A_h0)
+    # This rank's column shard: its own seed, so shards differ like real weight shards do;
+    # A (activations) is replicated: every rank draws it from rank 0's seed.
+    alpha = 1.0
+    if fp8:
+        A32, _ = inputs.make_operands(wl["dist"], M, 1, K, dtype=torch.float32, seed=inputs.DEFAULT_SEED)
+        _, B32 = inputs.make_operands(wl["dist"], 1, N, K, dtype=torch.float32, seed=inputs.DEFAULT_SEED + rank)
+        A_h, sa = inputs.quantize_e4m3(A32)
+        B_h, sb = inputs.quantize_e4m3(B32)
+        alpha = sa * sb
+        A_h, B_h = A_h.pin_memory(), B_h.pin_memory()
+        del A32, B32
+    else:
+        A_h, _ = inputs.make_operands(wl["dist"], M, 1, K, seed=inputs.DEFAULT_SEED, pin=True)
+        _, B_h = inputs.make_operands(wl["dist"], 1, N, K, seed=inputs.DEFAULT_SEED + rank, pin=True)
     C_h = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
-    dA, dB = A_h.cuda(non_blocking=True), B_h.cuda(non_blocking=True)
+    dA = A_h.cuda(non_blocking=True)
+    dBs = [B_h.cuda(non_blocking=True)]
+    for _ in range(wl["rotate"] - 1):
+        dBs.append(dBs[0].clone())
     dC = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     torch.cuda.synchronize()
 
@@ -216,13 +260,13 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
+        for i in range(warmup):
+            fn(i)
         barrier()
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         evs[0].record()
         for i in range(steps):
-            fn()
+            fn(i)
             evs[i + 1].record()
         barrier()
         total_ms = evs[0].elapsed_time(evs[-1])
@@ -234,26 +278,30 @@ def run_ours(args):
         return total_ms, per
 
     flops_per_gpu = 2.0 * M * N * K
+    flops_total = 2.0 * M * n_total * K
+    bytes_per_gpu = (M * K + N * K) * ebytes + M * N * 2
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches0 = ctx.launch_count
-    total_ms, per = timed(lambda: ctx.gemm_tn(dA, dB, out=dC), args.steps, args.warmup)
+    total_ms, per = timed(lambda i: ctx.gemm_tn(dA, dBs[i % len(dBs)], out=dC, alpha=alpha),
+                          args.steps, args.warmup)
     launches = ctx.launch_count - launches0 - args.warmup
     clocks = sampler.stop() if rank == 0 else None
     ctx.status()
     ms_per_step = total_ms / args.steps
-    value = world * flops_per_gpu / (ms_per_step * 1e-3) / 1e12
+    value = flops_total / (ms_per_step * 1e-3) / 1e12
 
     # end to end: host buffers in, host buffer out, every step
     e2e_steps = args.steps
     if args.no_e2e:
         e2e_total_ms = float("nan")
     else:
-        e2e_total_ms, _ = timed(lambda: ctx.gemm_host(A_h, B_h, C_h), e2e_steps, min(args.warmup, 3))
+        e2e_total_ms, _ = timed(lambda i: ctx.gemm_host(A_h, B_h, C_h, alpha=alpha), e2e_steps,
+                                min(args.warmup, 3))
         ctx.status()
-    e2e_value = world * flops_per_gpu / (e2e_total_ms / e2e_steps * 1e-3) / 1e12
-    h2d = (M * K + N * K) * 2
+    e2e_value = flops_total / (e2e_total_ms / e2e_steps * 1e-3) / 1e12
+    h2d = (M * K + N * K) * ebytes
     d2h = M * N * 2
 
     if rank != 0:
@@ -261,51 +309,69 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
-    # Denominator: the measured library GEMM on this pool. A timed region of a second or more
-    # runs under the power cap like the "sustained" measurement; a shorter one is compared with
-    # the (higher) burst figure.
+    # Denominators: measured on this pool (MEASURED_PEAKS.json). A timed region of a second or
+    # more runs under the power cap like the "sustained" measurement; a shorter one is compared
+    # with the (higher) burst figure.
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(peaks_path)) if os.path.isfile(peaks_path) else None
     region_s = total_ms * 1e-3
-    if os.path.isfile(peaks_path):
-        peaks = json.load(open(peaks_path))
-        burst = float(peaks["bf16_tflops"])
-        sustained = float(peaks.get("bf16_tflops_sustained", burst))
-        if region_s >= 1.0:
-            peak, peak_src = sustained, "of measured (MEASURED_PEAKS.json bf16_tflops_sustained; timed region >= 1 s)"
-        else:
-            peak, peak_src = burst, "of measured (MEASURED_PEAKS.json bf16_tflops, burst; timed region < 1 s)"
-    else:
-        burst = sustained = None
-        peak, peak_src = FALLBACK_BF16_TFLOPS, "of fallback"
     kernel_ms = statistics.mean(per)
-    achieved = flops_per_gpu / (kernel_ms * 1e-3) / 1e12
-    traffic = NCU_DRAM_TRAFFIC_BYTES.get(args.workload)
+    extra = {}
+    if wl["bound"] == "hbm":
+        achieved = bytes_per_gpu / (kernel_ms * 1e-3) / 1e9
+        unit = "GB/s"
+        if peaks:
+            peak, peak_src = float(peaks["hbm_gbs"]), "of measured (MEASURED_PEAKS.json hbm_gbs, copy read+write)"
+        else:
+            peak, peak_src = FALLBACK_HBM_GBS, "of fallback"
+        extra["frac_of_nominal_8TBs"] = round(achieved / NOMINAL_HBM_GBS, 4)
+    else:
+        achieved = flops_per_gpu / (kernel_ms * 1e-3) / 1e12
+        unit = "TFLOP/s"
+        if peaks and not fp8:
+            burst = float(peaks["bf16_tflops"])
+            sustained = float(peaks.get("bf16_tflops_sustained", burst))
+            if region_s >= 1.0:
+                peak, peak_src = sustained, "of measured (MEASURED_PEAKS.json bf16_tflops_sustained; timed region >= 1 s)"
+            else:
+                peak, peak_src = burst, "of measured (MEASURED_PEAKS.json bf16_tflops, burst; timed region < 1 s)"
+            extra["frac_of_burst_peak"] = round(achieved / burst, 4)
+            extra["frac_of_sustained_peak"] = round(achieved / sustained, 4)
+        elif fp8:
+            # no fp8 figure was measured on this pool: twice the measured bf16 burst is used
+            base = float(peaks["bf16_tflops"]) if peaks else FALLBACK_BF16_TFLOPS
+            peak, peak_src = 2.0 * base, "2 x the measured bf16 burst (no fp8 peak was measured)"
+        else:
+            peak, peak_src = FALLBACK_BF16_TFLOPS, "of fallback"
+    nominal = NOMINAL_FP8_TFLOPS if fp8 else NOMINAL_BF16_TFLOPS
+    traffic = NCU_DRAM_TRAFFIC_BYTES.get(args.workload) if world == 1 else None
 
     out = {
         "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {desc}" +
+        "higher_is_better": True, "scaling": wl["scaling"], "vs_baseline": None,
+        "dtype": "fp8_e4m3" if fp8 else "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {wl['desc']}" +
                                (f"; N-column shards, one {N}-column shard per GPU, A replicated"
                                 if world > 1 else ""),
-                   "M": M, "N_per_gpu": N, "K": K, "layout": "TN (A row-major MxK, B K-major NxK)",
-                   "l2": "inputs (268 MB) larger than L2 (126 MB); no flush between steps",
-                   "kernel": "persistent tcgen05 GEMM, auto tile config"},
+                   "M": M, "N_per_gpu": N, "N_total": n_total, "K": K,
+                   "layout": "TN (A row-major MxK, B K-major NxK)",
+                   "l2": (f"{wl['rotate']} weight buffers of {N * K * ebytes / 1e6:.0f} MB in rotation"
+                          if wl["rotate"] > 1 else
+                          f"inputs ({(M * K + N * K) * ebytes / 1e6:.0f} MB) vs L2 126 MB; no flush between steps"),
+                   "kernel": "library's automatic choice (tcgen05 large-tile or stream-K kernel)"},
         "per_gpu_tflops": round(value / world, 2),
-        "pct_of_nominal_bf16_peak": round(100.0 * value / world / NOMINAL_BF16_TFLOPS, 2),
+        "pct_of_nominal_peak": round(100.0 * value / world / nominal, 2),
         "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_total_ms / e2e_steps, 4)},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak,
-                     "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": traffic,
-                     "peak_source": peak_src, "kernel_ms_mean": round(kernel_ms, 5),
-                     "kernel_ms_min": round(min(per), 5), "timed_region_s": round(region_s, 4),
-                     "frac_of_burst_peak": round(achieved / burst, 4) if burst else None,
-                     "frac_of_sustained_peak": round(achieved / sustained, 4) if sustained else None,
+        "roofline": {"bound": wl["bound"], "achieved": round(achieved, 2), "peak": peak, "unit": unit,
+                     "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_src,
+                     "kernel_ms_mean": round(kernel_ms, 5), "kernel_ms_min": round(min(per), 5),
+                     "timed_region_s": round(region_s, 4),
                      "algorithmic_flops_per_launch": flops_per_gpu,
-                     "algorithmic_bytes_per_launch": (M * K + N * K) * 2 + M * N * 2},
+                     "algorithmic_bytes_per_launch": bytes_per_gpu, **extra},
     }
     if world == 1 and not args.no_cpu_baseline:
         tf, cores, kind, sample, _ = cpu_reference_sample(K, budget_s=12.0)
@@ -321,13 +387,14 @@ def run_reference(args):
     rank, _, world = dist_env()
     if rank != 0:
         return
-    M, N, K, distn, desc = WORKLOADS[args.workload]
+    wl = WORKLOADS[args.workload]
+    M, N, K, desc = wl["M"], wl["N"], wl["K"], wl["desc"]
     tf, cores, kind, sample, ms = cpu_reference_sample(K, budget_s=150.0, steps=args.steps,
                                                        warmup=args.warmup)
     out = {
         "impl": "reference", "metric": METRIC, "value": round(tf, 6), "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": wl["scaling"],
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {desc}", "M": M, "N_per_gpu": N, "K": K,
                    "layout": "TN (A row-major MxK, B K-major NxK)",

@@ -250,6 +250,7 @@ struct PatinaGemmContext {
   uint32_t* d_sk_counters = nullptr;
   size_t cap_sk_partials = 0, cap_sk_counters = 0;
   bool sk_attr_set[2] = {false, false};
+  uint32_t sk_burst = 4;
   // device staging for patina_gemm_host
   void* d_a = nullptr;
   void* d_b = nullptr;
@@ -351,6 +352,10 @@ SkPlan make_sk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms) {
 // K across CTAs pays (otherwise the large-tile kernel's 128-wide tiles already fill the GPU).
 bool streamk_preferred(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
   if (!streamk_supported(in_type, out_type, M)) return false;
+  // Measured at N = 28672, K = 8192: stream-K leads for M <= 32 (5.8 vs 5.6 TB/s at M = 16);
+  // from M = 64 on the X slab is as large as the W slab and the large-tile kernel, which loads
+  // one X slab per 256 rows of W, is ahead (5.7-5.8 TB/s).
+  if (M > 32) return false;
   const SkPlan s = make_sk_plan(in_type, M, N, K, num_sms);
   return s.units >= 4ull * (uint64_t)num_sms;
 }
@@ -413,6 +418,7 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.max_contrib = sp.max_contrib;
   p.stages = streamk_stages(sp.m_pad);
   p.stage_stride = streamk_stage_stride(sp.m_pad);
+  p.burst = ctx->sk_burst < p.stages / 2 ? ctx->sk_burst : p.stages / 2;
   p.alpha = alpha;
   p.C = static_cast<__nv_bfloat16*>(C);
   p.ldc = ldc;
@@ -595,6 +601,10 @@ int patina_gemm_context_create(int device, PatinaGemmContext** out) {
     return PATINA_GEMM_ERR_CUDA;
   }
   ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  if (const char* b = std::getenv("PATINA_SK_BURST")) {  // tuning knob, 1..6
+    const int v = std::atoi(b);
+    if (v >= 1 && v <= 6) ctx->sk_burst = (uint32_t)v;
+  }
   e = cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), 4 * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 4 * sizeof(uint32_t));
   if (e != cudaSuccess) {
@@ -929,6 +939,7 @@ extern "C" int patina_gemm_bf16_tn_skinny_noalloc(const void* A, int64_t lda, co
   p.max_contrib = sp.max_contrib;
   p.stages = streamk_stages(sp.m_pad);
   p.stage_stride = streamk_stage_stride(sp.m_pad);
+  p.burst = 4 < p.stages / 2 ? 4 : p.stages / 2;
   p.alpha = alpha;
   p.C = static_cast<__nv_bfloat16*>(C);
   p.ldc = ldc;

@@ -38,6 +38,9 @@ struct StreamKParams {
   uint32_t max_contrib;    // partial slots reserved per tile
   uint32_t stages;         // ring depth (<= kSkMaxStages)
   uint32_t stage_stride;   // bytes per stage: 16 KB of W + m_pad * 128 bytes of X
+  uint32_t burst;          // stages the producer fills back to back, so that adjacent k-blocks
+                           // of the same rows of W reach DRAM together (measured: 1 -> 4 stages
+                           // lifts a 470 MB stream from 4.8 to 5.8 TB/s)
   float alpha;
   __nv_bfloat16* C;
   int64_t ldc;
@@ -158,17 +161,28 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       // W is read exactly once: keep it from displacing X (re-read by every CTA) in L2.
       const uint64_t stream_once = ptx::l2_policy_evict_first();
       const uint64_t keep = ptx::l2_policy_evict_last();
-      for (uint64_t u = u_begin; u < u_end && ok; ++u) {
-        const uint32_t t = (uint32_t)(u / p.k_blocks);
-        const uint32_t kb = (uint32_t)(u - (uint64_t)t * p.k_blocks);
-        ok = bounded_wait<false>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
+      uint64_t u = u_begin;
+      uint32_t t = (uint32_t)(u_begin / p.k_blocks);
+      uint32_t kb = (uint32_t)(u_begin - (uint64_t)t * p.k_blocks);
+      while (u < u_end && ok) {
+        const uint64_t left = u_end - u;
+        const uint32_t group = left < p.burst ? (uint32_t)left : p.burst;
+        // all stages of the group must be free before any of it is issued
+        uint32_t s2 = s, ph2 = ph;
+        for (uint32_t g = 0; g < group && ok; ++g) {
+          ok = bounded_wait<false>(empty_bar + 8u * s2, ph2 ^ 1u, w, kTimeoutProducerEmpty, t);
+          if (++s2 == kStages) { s2 = 0; ph2 ^= 1u; }
+        }
         if (!ok) break;
-        const uint32_t sw = ring + s * kSkStageStride;
-        const int32_t k0 = (int32_t)(kb * kBlockKElems);
-        ptx::mbar_arrive_expect_tx(full_bar + 8u * s, kWBytes + x_bytes);
-        ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * s, k0, (int32_t)(t * kSkTileRows), stream_once);
-        ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * s, k0, 0, keep);
-        if (++s == kStages) { s = 0; ph ^= 1u; }
+        for (uint32_t g = 0; g < group; ++g, ++u) {
+          const uint32_t sw = ring + s * kSkStageStride;
+          const int32_t k0 = (int32_t)(kb * kBlockKElems);
+          ptx::mbar_arrive_expect_tx(full_bar + 8u * s, kWBytes + x_bytes);
+          ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * s, k0, (int32_t)(t * kSkTileRows), stream_once);
+          ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * s, k0, 0, keep);
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+          if (++kb == p.k_blocks) { kb = 0; ++t; }
+        }
       }
     }
   }

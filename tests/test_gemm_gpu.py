@@ -215,7 +215,7 @@ def test_streamk_matches_oracle_and_large_tile_kernel(ctx, oracle_mod, M, N, K):
 
 def test_streamk_decode_shapes_full_size(ctx, oracle_mod):
     """The decode-shaped configurations at full size (N=28672, K=8192, M in {16, 64, 128}):
-    automatic dispatch must take the stream-K path; 128 sampled columns of C against the
+    one launch each (stream-K for M = 16, the large-tile kernel above that); 128 sampled columns of C against the
     oracle (computed as rows of B x A^T), and fp8 inputs on the same path."""
     from patina_b200 import inputs
     N, K = 28672, 8192

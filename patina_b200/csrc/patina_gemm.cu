@@ -265,6 +265,14 @@ int set_error(PatinaGemmContext* ctx, int code, const std::string& msg) {
   return code;
 }
 
+// The runtime keeps the last error of any earlier call until somebody reads it. Read (and so
+// clear) it before a launch, so that a launch check never reports another call's failure.
+void drain_stale_error(const char* where) {
+  const cudaError_t stale = cudaGetLastError();
+  if (stale != cudaSuccess && std::getenv("PATINA_DEBUG"))
+    std::fprintf(stderr, "[patina] stale CUDA error before %s: %s\n", where, cudaGetErrorName(stale));
+}
+
 int cuda_fail(PatinaGemmContext* ctx, cudaError_t e, const char* what) {
   return set_error(ctx, PATINA_GEMM_ERR_CUDA,
                    fmt("%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e)));
@@ -407,6 +415,7 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
                       sp.m_pad, kelems, &tm_x);
   if (rc != PATINA_GEMM_OK) return rc;
+  drain_stale_error("stream-K launch");
   StreamKParams p{};
   p.M = (uint32_t)M;
   p.N = (uint32_t)N;
@@ -539,6 +548,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = (k->cta_group > 1) ? 1 : 0;
+  drain_stale_error("large-tile launch");
   cudaError_t e = cudaLaunchKernelEx(&lc, k->fn, tm_a, tm_b, tm_c, p);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaLaunchKernelEx");
   ctx->launches += 1;

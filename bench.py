@@ -297,6 +297,13 @@ def run_ours(args):
     ms_per_step = total_ms / args.steps
     value = flops_total / (ms_per_step * 1e-3) / 1e12
 
+    # optional: every rank gets the full C (NCCL all-gather of the column shards), timed apart
+    gather_ms = None
+    if args.allgather and world > 1:
+        g_steps = min(args.steps, 20)
+        g_total, _ = timed(lambda i: sharded.all_gather_columns(dC, n_total), g_steps, 3)
+        gather_ms = g_total / g_steps
+
     # end to end: host buffers in, host buffer out, every step
     e2e_steps = args.steps
     if args.no_e2e:
@@ -378,6 +385,10 @@ def run_ours(args):
                      "algorithmic_flops_per_launch": flops_per_gpu,
                      "algorithmic_bytes_per_launch": bytes_per_gpu, **extra},
     }
+    if gather_ms is not None:
+        out["allgather"] = {"ms_per_step": round(gather_ms, 4), "bytes_received_per_gpu": M * (n_total - N) * 2,
+                            "gemm_plus_allgather_tflops": round(flops_total / ((ms_per_step + gather_ms) * 1e-3) / 1e12, 2),
+                            "note": "optional; not part of `value`"}
     if world == 1 and not args.no_cpu_baseline:
         tf, cores, kind, sample, _ = cpu_reference_sample(K, budget_s=12.0)
         out["cpu_baseline"] = {"value": round(tf, 6), "unit": "TFLOP/s", "cores": cores,
@@ -422,6 +433,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bf16_tn_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--allgather", action="store_true",
+                    help="N > 1: also time the optional NCCL all-gather of the C column shards")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -112,22 +112,29 @@ struct SmemPlan {
 constexpr uint32_t kBlockKBytes = 128;      // one swizzle span of K per stage
 constexpr uint32_t kCtaRows = 128;          // accumulator rows (TMEM lanes) per CTA sub-tile
 constexpr uint32_t kStoreBoxRows = 32;      // one epilogue warp's rows
-constexpr uint32_t kStagingBufBytes = kStoreBoxRows * 128;  // 32 rows x 128 B
 constexpr uint32_t kBarrierRegionBytes = 256;
 constexpr uint32_t kMaxDynSmem = 232448;    // 227 KB
 
-// Staging buffers per epilogue warp: two when four warps drain a tile, one when eight do
-// (32 KB of staging either way).
-PATINA_HD constexpr uint32_t staging_bufs(uint32_t m_sub) { return m_sub == 1 ? 2u : 1u; }
+// Epilogue staging: every epilogue warp owns two buffers of 32 rows, double-buffered so that
+// filling one overlaps the TMA store reading the other. With four epilogue warps a row
+// segment is 128 bytes (128-byte swizzle); with eight warps (m_sub = 2) it is 64 bytes
+// (64-byte swizzle), which keeps the total at 32 KB.
+PATINA_HD constexpr uint32_t staging_bufs(uint32_t) { return 2u; }
+PATINA_HD constexpr uint32_t staging_row_bytes(uint32_t m_sub, uint32_t out_bytes) {
+  return (m_sub == 2 && out_bytes == 2) ? 64u : 128u;
+}
+PATINA_HD constexpr uint32_t staging_buf_bytes(uint32_t m_sub, uint32_t out_bytes) {
+  return kStoreBoxRows * staging_row_bytes(m_sub, out_bytes);
+}
 
 PATINA_HD constexpr SmemPlan smem_plan(uint32_t cta_group, uint32_t m_sub, uint32_t block_n,
-                                       uint32_t stages) {
+                                       uint32_t stages, uint32_t out_bytes = 2) {
   SmemPlan p{};
   p.a_bytes = m_sub * kCtaRows * kBlockKBytes;
   p.b_bytes = (block_n / cta_group) * kBlockKBytes;
   p.stage_bytes = p.a_bytes + p.b_bytes;
   p.stages = stages;
-  p.staging_bytes = 4 * m_sub * staging_bufs(m_sub) * kStagingBufBytes;
+  p.staging_bytes = 4 * m_sub * staging_bufs(m_sub) * staging_buf_bytes(m_sub, out_bytes);
   p.barrier_bytes = kBarrierRegionBytes;
   // +1024: the ring is placed on the next 1024-byte boundary (swizzle atom).
   p.total_bytes = 1024 + stages * p.stage_bytes + p.staging_bytes + p.barrier_bytes;

@@ -176,7 +176,8 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   p.cluster = best->cta_group;
   p.smem_bytes = best->smem_bytes;
   p.tmem_cols = (2 * best->m_sub * best->block_n <= 512 ? 2 : 1) * best->m_sub * best->block_n;
-  const SmemPlan sp = smem_plan(best->cta_group, best->m_sub, best->block_n, best->stages);
+  const SmemPlan sp = smem_plan(best->cta_group, best->m_sub, best->block_n, best->stages,
+                                output_bytes(out_type));
   p.stage_bytes = sp.stage_bytes;
   p.expect_tx_bytes = sp.stage_bytes * best->cta_group;
   p.idesc = idesc(in_type, 128 * best->cta_group, best->block_n);
@@ -223,6 +224,7 @@ struct TensorMapKey {
   uint32_t box_rows, box_cols;
   int dtype;  // CUtensorMapDataType
   bool operator==(const TensorMapKey& o) const {
+    // (the swizzle mode follows from box_cols * element size: 128 or 64 bytes)
     return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
            box_rows == o.box_rows && box_cols == o.box_cols && dtype == o.dtype;
   }
@@ -292,7 +294,9 @@ struct DeviceGuard {
 };
 
 // A K-major matrix [rows, cols] with row pitch ld elements, tiled in boxes of
-// box_rows x box_cols where box_cols spans exactly 128 bytes, 128-byte swizzle.
+// box_rows x box_cols where box_cols spans exactly one swizzle span: 128 bytes (128-byte
+// swizzle: operands, and C from four-warp epilogues) or 64 bytes (64-byte swizzle: C from
+// eight-warp epilogues).
 // (The reference's map is 4-D, unswizzled: harness/gemm_check.cpp:127-147.)
 int get_tensor_map(PatinaGemmContext* ctx, const void* ptr, CUtensorMapDataType dtype,
                    uint32_t elt_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
@@ -304,7 +308,8 @@ int get_tensor_map(PatinaGemmContext* ctx, const void* ptr, CUtensorMapDataType 
       return PATINA_GEMM_OK;
     }
   }
-  if (box_cols * elt_bytes != 128 || box_rows == 0 || box_rows > 256)
+  const uint32_t span = box_cols * elt_bytes;
+  if ((span != 128 && span != 64) || box_rows == 0 || box_rows > 256)
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "internal: illegal TMA box");
   const cuuint64_t gdim[2] = {cols, rows};
   const cuuint64_t gstride[1] = {ld * elt_bytes};
@@ -312,7 +317,8 @@ int get_tensor_map(PatinaGemmContext* ctx, const void* ptr, CUtensorMapDataType 
   const cuuint32_t estride[2] = {1, 1};
   CUtensorMap tm;
   CUresult rc = ctx->encode(&tm, dtype, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            span == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS)
     return set_error(ctx, PATINA_GEMM_ERR_CUDA,
@@ -362,10 +368,14 @@ bool streamk_preferred(int in_type, int out_type, int64_t M, int64_t N, int64_t 
   if (!streamk_supported(in_type, out_type, M)) return false;
   // Measured at N = 28672, K = 8192: stream-K leads for M <= 32 (5.8 vs 5.6 TB/s at M = 16);
   // from M = 64 on the X slab is as large as the W slab and the large-tile kernel, which loads
-  // one X slab per 256 rows of W, is ahead (5.7-5.8 TB/s).
-  if (M > 32) return false;
+  // one X slab per 256 rows of W, is ahead (5.7-5.8 TB/s) -- as long as it has a tile for most
+  // SMs. A narrow shard (N / 8 = 3584 columns is 14 tiles of 256) leaves it starved: 14 CTAs
+  // cannot pull the HBM bandwidth, and cutting K across all SMs wins again.
   const SkPlan s = make_sk_plan(in_type, M, N, K, num_sms);
-  return s.units >= 4ull * (uint64_t)num_sms;
+  if (s.units < 4ull * (uint64_t)num_sms) return false;
+  if (M <= 32) return true;
+  const uint64_t large_tiles = (uint64_t)ceil_div(N, 256);  // one 128-row tile covers all of M
+  return large_tiles * 10 < (uint64_t)num_sms * 7;
 }
 
 template <int kIn>
@@ -484,7 +494,8 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   rc = get_tensor_map(ctx, C,
                       out_type == kOutF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                           : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                      ob, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kStoreBoxRows, 128 / ob, &tm_c);
+                      ob, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kStoreBoxRows,
+                      staging_row_bytes((uint32_t)k->m_sub, ob) / ob, &tm_c);
   if (rc != PATINA_GEMM_OK) return rc;
 
   const int ki = (int)(k - kKernels);

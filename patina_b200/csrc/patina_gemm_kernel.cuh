@@ -116,9 +116,12 @@ struct GemmTraits {
   static constexpr uint32_t kAccBufs = (2 * kAccCols <= 512) ? 2 : 1;
   static constexpr uint32_t kTmemCols = kAccBufs * kAccCols;
   static constexpr uint32_t kStageBufs = staging_bufs(kMSub);       // per epilogue warp
-  static constexpr uint32_t kChunkCols = 128 / output_bytes(kOut);  // one 128-byte row segment
+  static constexpr uint32_t kRowBytes = staging_row_bytes(kMSub, output_bytes(kOut));  // 128 or 64
+  static constexpr uint32_t kBufBytes = staging_buf_bytes(kMSub, output_bytes(kOut));
+  static constexpr uint32_t kChunkCols = kRowBytes / output_bytes(kOut);  // columns per store box
   static constexpr uint32_t kChunks = BN / kChunkCols;
-  static constexpr uint32_t kSmemBytes = smem_plan(kCtaGroup, kMSub, BN, kStages).total_bytes;
+  static constexpr uint32_t kSmemBytes =
+      smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut)).total_bytes;
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
   static_assert(kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
@@ -141,7 +144,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = smem_base;
   const uint32_t staging = ring + kStages * T::kStageBytes;
-  const uint32_t bars = staging + kEpiWarps * T::kStageBufs * kStagingBufBytes;
+  const uint32_t bars = staging + kEpiWarps * T::kStageBufs * T::kBufBytes;
   const uint32_t full_bar = bars;                      // [kStages]
   const uint32_t empty_bar = bars + 8u * kStages;      // [kStages]
   const uint32_t tfull_bar = bars + 16u * kStages;     // [2]
@@ -288,9 +291,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t q = warp_idx & 3u;          // TMEM lane quarter this warp may touch
     const uint32_t e = warp_idx - 2u;          // epilogue warp index
     const uint32_t ms = e >> 2;                // accumulator sub-tile this warp drains
-    const uint32_t stg0 = staging + e * (T::kStageBufs * kStagingBufBytes);
+    const uint32_t stg0 = staging + e * (T::kStageBufs * T::kBufBytes);
     const uint32_t leader_tempty = kPair ? ptx::mapa(tempty_bar, 0) : tempty_bar;
-    const uint32_t row_sw = lane & 7u;
+    // Swizzled position of 16-byte piece j of this lane's row, matching the store's tensor map:
+    // 128-byte rows: j ^ (row & 7); 64-byte rows: j ^ ((row >> 1) & 3).
+    const uint32_t row_sw = (T::kRowBytes == 128u) ? (lane & 7u) : ((lane >> 1) & 3u);
     uint32_t it = 0, sbuf = 0;
     bool ok = true;
     for (uint32_t t = cluster_id; t < p.num_tiles && ok; t += num_clusters, ++it) {
@@ -304,12 +309,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             q * kStoreBoxRows;
       const uint32_t col0 = c.n * BN;
       const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * T::kAccCols + ms * BN;
+      constexpr uint32_t kFp32PerChunk = T::kChunkCols;            // accumulator words per chunk
+      constexpr uint32_t kPieces = T::kRowBytes / 16u;             // 16-byte pieces per staged row
 #pragma unroll 1
       for (uint32_t ch = 0; ch < T::kChunks; ++ch) {
-        uint32_t v[kOut == kOutBF16 ? 64 : 32];
-        ptx::tmem_ld_32x32b_x32(taddr + ch * T::kChunkCols, &v[0]);
-        if constexpr (kOut == kOutBF16)
-          ptx::tmem_ld_32x32b_x32(taddr + ch * T::kChunkCols + 32u, &v[32]);
+        uint32_t v[kFp32PerChunk];
+#pragma unroll
+        for (uint32_t h = 0; h < kFp32PerChunk; h += 32u)
+          ptx::tmem_ld_32x32b_x32(taddr + ch * T::kChunkCols + h, &v[h]);
         ptx::tmem_ld_wait();
         if (ch == T::kChunks - 1) {
           // Accumulator fully read: hand the TMEM buffer back to the MMA issuer.
@@ -323,9 +330,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // The staging buffer about to be rewritten must have been read by its store.
         if (lane == 0) ptx::tma_store_wait_read<T::kStageBufs - 1>();
         __syncwarp();
-        const uint32_t row_addr = stg0 + sbuf * kStagingBufBytes + lane * 128u;
+        const uint32_t row_addr = stg0 + sbuf * T::kBufBytes + lane * T::kRowBytes;
 #pragma unroll
-        for (uint32_t j = 0; j < 8; ++j) {
+        for (uint32_t j = 0; j < kPieces; ++j) {
           uint32_t w0, w1, w2, w3;
           if constexpr (kOut == kOutBF16) {
             auto pack = [&](uint32_t a, uint32_t b) -> uint32_t {
@@ -353,10 +360,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
           const uint32_t cc = col0 + ch * T::kChunkCols;
           if (row0 < p.M && cc < p.N)
-            ptx::tma_store_2d(&tm_c, stg0 + sbuf * kStagingBufBytes, (int32_t)cc, (int32_t)row0);
+            ptx::tma_store_2d(&tm_c, stg0 + sbuf * T::kBufBytes, (int32_t)cc, (int32_t)row0);
           ptx::tma_store_commit();
         }
-        if constexpr (T::kStageBufs > 1) sbuf ^= 1u;
+        sbuf ^= 1u;
       }
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();

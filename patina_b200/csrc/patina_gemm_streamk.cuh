@@ -44,7 +44,7 @@ struct StreamKParams {
   float alpha;
   __nv_bfloat16* C;
   int64_t ldc;
-  float* partials;         // [tiles][max_contrib][m_pad][128] fp32
+  float* partials;         // [tiles][max_contrib][m_pad / 4][128 rows][4] fp32
   uint32_t* counters;      // [tiles], zero between launches
   uint32_t* status;
   uint64_t wait_limit_ns;
@@ -261,16 +261,21 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t first_cta = streamk_owner(tile_u0, p.units, parts);
         contribs = streamk_owner(tile_u0 + p.k_blocks - 1, p.units, parts) - first_cta + 1u;
         my_j = blockIdx.x - first_cta;
-        // 1. publish this CTA's partial tile: slot layout [m][128 weight rows], coalesced
+        // 1. publish this CTA's partial tile. Slot layout [m / 4][128 weight rows][4]: a thread
+        //    writes four consecutive m of its row as one 16-byte word, a warp 512 contiguous bytes.
         if (!dead) {
-          float* mine = p.partials + ((size_t)t * p.max_contrib + my_j) * ((size_t)p.m_pad * 128u);
+          float4* mine = reinterpret_cast<float4*>(
+                             p.partials + ((size_t)t * p.max_contrib + my_j) * ((size_t)p.m_pad * 128u)) +
+                         q * 32u + lane;
           for (uint32_t m0 = 0; m0 < p.m_pad; m0 += 16u) {
             uint32_t v[16];
             ptx::tmem_ld_32x32b_x16(taddr + m0, v);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (uint32_t i = 0; i < 16; ++i)
-              __stcg(mine + (size_t)(m0 + i) * 128u + q * 32u + lane, __uint_as_float(v[i]));
+            for (uint32_t g = 0; g < 4; ++g)
+              __stcg(mine + (size_t)(m0 / 4u + g) * 128u,
+                     make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
+                                 __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3])));
           }
           __threadfence();
         }
@@ -290,33 +295,52 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       if (is_last) {
         // 2. sum the contributors in their fixed order (this CTA's part comes from TMEM), scale,
-        //    round to bf16 and store C[m][n]
-        const float* slot0 = p.partials + (size_t)t * p.max_contrib * ((size_t)p.m_pad * 128u);
-        for (uint32_t m0 = 0; m0 < p.m_pad; m0 += 16u) {
-          uint32_t v[16];
-          ptx::tmem_ld_32x32b_x16(taddr + m0, v);
-          ptx::tmem_ld_wait();
-          float acc[16];
+        //    round to bf16 and store C[m][n]. Up to 64 values of m at a time, contributor
+        //    outermost, so that one contributor's 16 loads are in flight together.
+        const float4* slot0 = reinterpret_cast<const float4*>(
+                                  p.partials + (size_t)t * p.max_contrib * ((size_t)p.m_pad * 128u)) +
+                              q * 32u + lane;
+        const size_t slot_quads = (size_t)p.m_pad * 32u;  // float4 words per slot
+        for (uint32_t mb = 0; mb < p.m_pad; mb += 64u) {
+          const uint32_t nq = (p.m_pad - mb) >= 64u ? 16u : (p.m_pad - mb) / 4u;  // quads in this batch
+          float acc[64];
 #pragma unroll
-          for (uint32_t i = 0; i < 16; ++i) acc[i] = 0.0f;
+          for (uint32_t i = 0; i < 64; ++i) acc[i] = 0.0f;
           for (uint32_t j = 0; j < contribs; ++j) {
+            float x[64];
             if (j == my_j) {
 #pragma unroll
-              for (uint32_t i = 0; i < 16; ++i)
-                acc[i] = (j == 0u) ? __uint_as_float(v[i]) : acc[i] + __uint_as_float(v[i]);
-            } else {
-              const float* other = slot0 + (size_t)j * ((size_t)p.m_pad * 128u);
+              for (uint32_t c16 = 0; c16 < 4; ++c16) {
+                if (c16 * 4u < nq) {
+                  uint32_t v[16];
+                  ptx::tmem_ld_32x32b_x16(taddr + mb + c16 * 16u, v);
+                  ptx::tmem_ld_wait();
 #pragma unroll
-              for (uint32_t i = 0; i < 16; ++i) {
-                const float x = __ldcg(other + (size_t)(m0 + i) * 128u + q * 32u + lane);
-                acc[i] = (j == 0u) ? x : acc[i] + x;
+                  for (uint32_t i = 0; i < 16; ++i) x[c16 * 16u + i] = __uint_as_float(v[i]);
+                }
+              }
+            } else {
+              const float4* other = slot0 + (size_t)j * slot_quads + (size_t)(mb / 4u) * 128u;
+#pragma unroll
+              for (uint32_t g = 0; g < 16; ++g) {
+                if (g < nq) {
+                  const float4 w4 = __ldcg(other + (size_t)g * 128u);
+                  x[4 * g] = w4.x;
+                  x[4 * g + 1] = w4.y;
+                  x[4 * g + 2] = w4.z;
+                  x[4 * g + 3] = w4.w;
+                }
               }
             }
+#pragma unroll
+            for (uint32_t i = 0; i < 64; ++i)
+              if (i < nq * 4u) acc[i] = (j == 0u) ? x[i] : acc[i] + x[i];
           }
           if (n < p.N) {
 #pragma unroll
-            for (uint32_t i = 0; i < 16; ++i)
-              if (m0 + i < p.M) p.C[(size_t)(m0 + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
+            for (uint32_t i = 0; i < 64; ++i)
+              if (i < nq * 4u && mb + i < p.M)
+                p.C[(size_t)(mb + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
           }
         }
       }

@@ -304,6 +304,24 @@ def run_ours(args):
         g_total, _ = timed(lambda i: sharded.all_gather_columns(dC, n_total), g_steps, 3)
         gather_ms = g_total / g_steps
 
+    fused_ms = None
+    if args.fused_allgather and world > 1 and not fp8:
+        local_c, views = sharded.share_full_c(M, n_total)
+        barrier()
+        if wl["scaling"] == "strong":
+            run_fused = lambda i: sharded.gemm_scatter_columns(ctx, dA, dBs[i % len(dBs)], views, n_total)
+        else:
+            # weak workloads: rank r owns columns [r*N, (r+1)*N) of the N*world-wide C
+            order = [rank] + [r for r in range(world) if r != rank]
+            dests = [views[r][:, rank * N:(rank + 1) * N] for r in order]
+            run_fused = lambda i: ctx.gemm_bf16_tn_scatter(dA, dBs[i % len(dBs)], dests)
+        f_steps = min(args.steps, 50)
+        f_total, _ = timed(run_fused, f_steps, 3)
+        ctx.status()
+        fused_ms = f_total / f_steps
+        barrier()
+        del views
+
     # end to end: host buffers in, host buffer out, every step
     e2e_steps = args.steps
     if args.no_e2e:
@@ -389,6 +407,11 @@ def run_ours(args):
         out["allgather"] = {"ms_per_step": round(gather_ms, 4), "bytes_received_per_gpu": M * (n_total - N) * 2,
                             "gemm_plus_allgather_tflops": round(flops_total / ((ms_per_step + gather_ms) * 1e-3) / 1e12, 2),
                             "note": "optional; not part of `value`"}
+    if fused_ms is not None:
+        out["fused_allgather"] = {"ms_per_step": round(fused_ms, 4),
+                                  "tflops": round(flops_total / (fused_ms * 1e-3) / 1e12, 2),
+                                  "bytes_sent_per_gpu": M * N * 2 * (world - 1),
+                                  "note": "GEMM whose epilogue writes its column block into every GPU's C"}
     if world == 1 and not args.no_cpu_baseline:
         tf, cores, kind, sample, _ = cpu_reference_sample(K, budget_s=12.0)
         out["cpu_baseline"] = {"value": round(tf, 6), "unit": "TFLOP/s", "cores": cores,
@@ -433,6 +456,9 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bf16_tn_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--fused-allgather", action="store_true",
+                    help="N > 1: also time the GEMM whose epilogue stores its column block into every "
+                         "GPU's full-width C (peer writes over NVLink instead of a collective)")
     ap.add_argument("--allgather", action="store_true",
                     help="N > 1: also time the optional NCCL all-gather of the C column shards")
     args = ap.parse_args()

@@ -120,6 +120,18 @@ int patina_gemm_ex(PatinaGemmContext* ctx, int in_type, int out_type, const void
                    const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N,
                    int64_t K, float alpha, const PatinaGemmConfig* cfg, void* stream);
 
+/* Column-shard scatter (no counterpart in the reference, which is single-GPU): the same bf16
+ * GEMM, but every finished tile of C is stored to n_dests (1..8) destinations that share M, N
+ * and ldc. On a multi-GPU node each GPU passes, for every GPU g, the address of ITS column block
+ * inside g's full-width C (its own buffer plus peer buffers mapped into this process, e.g. with
+ * CUDA IPC), so that when all GPUs are done each holds the whole C: the optional all-gather is
+ * fused into the epilogue as peer writes over NVLink (TMA stores; nothing is loaded from a
+ * peer, nothing is multicast, no GPU waits for another inside the kernel). The caller
+ * synchronises the GPUs around the call (nobody may still read a C that is being written). */
+int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                int64_t ldb, void* const* C_dests, int n_dests, int64_t ldc,
+                                int64_t M, int64_t N, int64_t K, float alpha, void* stream);
+
 /* End-to-end form with HOST buffers, the shape of run.rs `run_gemm`
  * (alloc + memcpy_htod + launch + memcpy_dtoh, run.rs:484-528): copies A and B
  * to context-owned device buffers, runs the GEMM, copies C back, all on

@@ -39,7 +39,7 @@ std::string fmt(const char* f, ...) {
 }
 
 // ------------------------------------------------------------------ kernels
-using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CStoreMaps, const GemmParams);
 
 struct KernelEntry {
   int cta_group, m_sub, block_n, stages, in_type, out_type;
@@ -252,6 +252,7 @@ struct PatinaGemmContext {
   uint32_t* d_sk_counters = nullptr;
   size_t cap_sk_partials = 0, cap_sk_counters = 0;
   bool sk_attr_set[2] = {false, false};
+  bool peer_enabled[64] = {};
   uint32_t sk_burst = 4;
   // device staging for patina_gemm_host
   void* d_a = nullptr;
@@ -455,11 +456,17 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
 
 int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A, int64_t lda,
                 const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
-                float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream) {
+                float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream,
+                void* const* extra_dests = nullptr, int n_extra = 0) {
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   std::string err;
   int rc = validate_args(in_type, out_type, A, lda, B, ldb, C, ldc, M, N, K, &err);
   if (rc != PATINA_GEMM_OK) return set_error(ctx, rc, err);
+  if (n_extra < 0 || n_extra > kMaxDests - 1 || (n_extra > 0 && !extra_dests))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "bad destination list");
+  for (int d = 0; d < n_extra; ++d)
+    if (!extra_dests[d] || (reinterpret_cast<uintptr_t>(extra_dests[d]) & 15u) != 0)
+      return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "a destination of C is null or not 16-byte aligned");
   if (M == 0 || N == 0) return PATINA_GEMM_OK;
   DeviceGuard guard(ctx->device);
   if (!guard.ok) return set_error(ctx, PATINA_GEMM_ERR_CUDA, "cudaSetDevice failed");
@@ -474,8 +481,9 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
                      "stream_k needs M <= 128, bf16 or e4m3 inputs and bf16 output");
   const bool explicit_tile = cfg && (cfg->cta_group != 0 || cfg->block_n != 0 || cfg->m_sub != 0);
-  if (want_sk > 0 || (want_sk == 0 && !explicit_tile &&
-                      streamk_preferred(in_type, out_type, M, N, K, ctx->num_sms)))
+  if (n_extra == 0 &&
+      (want_sk > 0 || (want_sk == 0 && !explicit_tile &&
+                       streamk_preferred(in_type, out_type, M, N, K, ctx->num_sms))))
     return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream);
   PatinaGemmPlan plan;
   const KernelEntry* k = nullptr;
@@ -484,19 +492,23 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
 
   const uint32_t ib = input_bytes(in_type);
   const uint32_t kelems = kBlockKBytes / ib;
-  CUtensorMap tm_a, tm_b, tm_c;
+  CUtensorMap tm_a, tm_b;
+  CStoreMaps tm_c;
   rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
                       kCtaRows, kelems, &tm_a);
   if (rc != PATINA_GEMM_OK) return rc;
   rc = get_tensor_map(ctx, B, tmap_in_type(in_type), ib, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
                       (uint32_t)(k->block_n / k->cta_group), kelems, &tm_b);
   if (rc != PATINA_GEMM_OK) return rc;
-  rc = get_tensor_map(ctx, C,
-                      out_type == kOutF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                      ob, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kStoreBoxRows,
-                      staging_row_bytes((uint32_t)k->m_sub, ob) / ob, &tm_c);
-  if (rc != PATINA_GEMM_OK) return rc;
+  for (int d = 0; d <= n_extra; ++d) {
+    rc = get_tensor_map(ctx, d == 0 ? C : extra_dests[d - 1],
+                        out_type == kOutF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                        ob, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kStoreBoxRows,
+                        staging_row_bytes((uint32_t)k->m_sub, ob) / ob, &tm_c.map[d]);
+    if (rc != PATINA_GEMM_OK) return rc;
+  }
+  for (int d = n_extra + 1; d < kMaxDests; ++d) tm_c.map[d] = tm_c.map[0];
 
   const int ki = (int)(k - kKernels);
   if (!ctx->smem_attr_set[ki]) {
@@ -544,6 +556,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   p.k_blocks = plan.k_blocks;
   p.group_m = (uint32_t)plan.group_m;
   p.alpha = alpha;
+  p.n_dests = (uint32_t)(1 + n_extra);
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
 
@@ -709,6 +722,40 @@ int patina_gemm_f16_tn_f32out(PatinaGemmContext* ctx, const void* A, int64_t lda
                               float alpha, void* stream) {
   return launch_gemm(ctx, kF16, kOutF32, A, lda, B, ldb, C, ldc, M, N, K, alpha, nullptr,
                      static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                int64_t ldb, void* const* C_dests, int n_dests, int64_t ldc,
+                                int64_t M, int64_t N, int64_t K, float alpha, void* stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  if (!C_dests || n_dests < 1 || n_dests > kMaxDests)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "n_dests must be 1..8 and C_dests non-null");
+  {
+    // Destinations in another GPU's memory need peer access from this context's device.
+    DeviceGuard guard(ctx->device);
+    for (int d = 0; d < n_dests; ++d) {
+      cudaPointerAttributes at{};
+      if (!C_dests[d] || cudaPointerGetAttributes(&at, C_dests[d]) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "a destination of C is not a device pointer");
+      }
+      if (at.type == cudaMemoryTypeDevice && at.device != ctx->device && at.device >= 0 &&
+          at.device < 64 && !ctx->peer_enabled[at.device]) {
+        int can = 0;
+        cudaDeviceCanAccessPeer(&can, ctx->device, at.device);
+        if (!can)
+          return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
+                           fmt("device %d cannot access memory of device %d", ctx->device, at.device));
+        const cudaError_t pe = cudaDeviceEnablePeerAccess(at.device, 0);
+        if (pe != cudaSuccess && pe != cudaErrorPeerAccessAlreadyEnabled)
+          return cuda_fail(ctx, pe, "cudaDeviceEnablePeerAccess");
+        cudaGetLastError();
+        ctx->peer_enabled[at.device] = true;
+      }
+    }
+  }
+  return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C_dests[0], ldc, M, N, K, alpha, nullptr,
+                     static_cast<cudaStream_t>(stream), C_dests + 1, n_dests - 1);
 }
 
 int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const void* hostA,

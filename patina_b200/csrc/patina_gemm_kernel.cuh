@@ -36,12 +36,22 @@
 
 namespace patina {
 
+// Where a finished sub-tile of C is stored: one tensor map per destination. One destination is
+// the normal case; several are the column-shard scatter, where every GPU of a node writes its
+// column block into each GPU's full-width C (the other maps point into peer memory mapped
+// over NVLink; TMA *stores* there are plain peer writes, nothing is multicast or loaded).
+constexpr int kMaxDests = 8;
+struct CStoreMaps {
+  CUtensorMap map[kMaxDests];
+};
+
 struct GemmParams {
   uint32_t M, N, K;
   uint32_t tiles_m, tiles_n, num_tiles;  // in units of the cluster tile
   uint32_t k_blocks;                     // ceil(K / elements per 128 bytes)
   uint32_t group_m;                      // scheduler band height (tiles)
   float alpha;
+  uint32_t n_dests;        // destinations of C (1..kMaxDests)
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
 };
@@ -134,7 +144,7 @@ struct GemmTraits {
 template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut>
 __global__ void __launch_bounds__(64 + 128 * kMSub, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-               const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+               const __grid_constant__ CStoreMaps tm_c, const GemmParams p) {
   using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut>;
   constexpr bool kPair = (kCtaGroup == 2);
   constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
@@ -175,7 +185,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_b);
-    ptx::prefetch_tensormap(&tm_c);
+    for (uint32_t d = 0; d < p.n_dests; ++d) ptx::prefetch_tensormap(&tm_c.map[d]);
     for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
       ptx::mbar_init(full_bar + 8u * s, 1);
       ptx::mbar_init(empty_bar + 8u * s, 1);
@@ -359,8 +369,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         __syncwarp();
         if (lane == 0) {
           const uint32_t cc = col0 + ch * T::kChunkCols;
-          if (row0 < p.M && cc < p.N)
-            ptx::tma_store_2d(&tm_c, stg0 + sbuf * T::kBufBytes, (int32_t)cc, (int32_t)row0);
+          if (row0 < p.M && cc < p.N) {
+            for (uint32_t d = 0; d < p.n_dests; ++d)
+              ptx::tma_store_2d(&tm_c.map[d], stg0 + sbuf * T::kBufBytes, (int32_t)cc, (int32_t)row0);
+          }
           ptx::tma_store_commit();
         }
         sbuf ^= 1u;

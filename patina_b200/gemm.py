@@ -167,6 +167,23 @@ class GemmContext:
             self._raise(rc)
         return out
 
+    def gemm_bf16_tn_scatter(self, A, B, dests, alpha=1.0):
+        """C = alpha * A @ B^T stored to every tensor in `dests` (same shape and row stride; the
+        first is normally local, the others peer buffers mapped into this process)."""
+        M, K = A.shape
+        N = B.shape[0]
+        ldc = dests[0].stride(0)
+        for d in dests:
+            if tuple(d.shape) != (M, N) or d.stride(0) != ldc or d.stride(1) != 1 or d.dtype != torch.bfloat16:
+                raise PatinaGemmError(_l.ERR_INVALID_ARG, "destinations must be [M,N] bf16 with one row stride")
+        arr = (C.c_void_p * len(dests))(*[d.data_ptr() for d in dests])
+        rc = self._lib.patina_gemm_bf16_tn_scatter(self._h, A.data_ptr(), A.stride(0), B.data_ptr(),
+                                                   B.stride(0), arr, len(dests), ldc, M, N, K,
+                                                   float(alpha), _stream_ptr(self.device))
+        if rc != _l.OK:
+            self._raise(rc)
+        return dests[0]
+
     def gemm_host(self, hA: torch.Tensor, hB: torch.Tensor, hC: torch.Tensor, alpha: float = 1.0,
                   config: GemmConfig | None = None) -> torch.Tensor:
         """End-to-end call on HOST (ideally pinned) tensors: H2D, GEMM, D2H on the current

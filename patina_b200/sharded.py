@@ -66,3 +66,36 @@ def all_gather_columns(c_shard: torch.Tensor, n_total: int, group=None, align: i
             out[:, col:col + w] = gathered[r, :, :w]
         col += w
     return out
+
+
+def share_full_c(M: int, n_total: int, group=None) -> tuple[torch.Tensor, list[torch.Tensor]]:
+    """Every rank allocates one full-width C[M, n_total] (bf16) and maps every other rank's
+    into its own process (CUDA IPC through torch's tensor sharing). Returns
+    (local_C, [C of rank 0, ..., C of rank W-1]); the entry of this rank is local_C itself.
+    Keep local_C alive as long as any rank may still write to it."""
+    from torch.multiprocessing.reductions import reduce_tensor
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    local = torch.empty((M, n_total), dtype=torch.bfloat16, device="cuda")
+    handles = [None] * world
+    dist.all_gather_object(handles, reduce_tensor(local), group=group)
+    views = []
+    for r, (rebuild, args) in enumerate(handles):
+        views.append(local if r == rank else rebuild(*args))
+    return local, views
+
+
+def gemm_scatter_columns(ctx, A: torch.Tensor, B_shard: torch.Tensor, full_views: list[torch.Tensor],
+                         n_total: int, group=None, alpha: float = 1.0, align: int = 256) -> torch.Tensor:
+    """This rank's column block of C, written by the GEMM's epilogue into EVERY rank's full C
+    (the all-gather fused into the kernel as peer stores over NVLink). No collective is called;
+    ranks must synchronise (e.g. dist.barrier + stream sync) before anyone reads its C or reuses it."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    n0, n1 = column_shard(n_total, world, rank, align)
+    if B_shard.shape[0] != n1 - n0:
+        raise ValueError(f"rank {rank}: B shard has {B_shard.shape[0]} rows, expected {n1 - n0}")
+    if n1 == n0:
+        return full_views[rank]
+    order = [rank] + [r for r in range(world) if r != rank]       # own buffer first
+    dests = [full_views[r][:, n0:n1] for r in order]
+    ctx.gemm_bf16_tn_scatter(A, B_shard, dests, alpha=alpha)
+    return full_views[rank]

@@ -42,7 +42,19 @@ def _worker(rank, world, port, q):
         wide = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
         sharded.gemm_column_shard(ctx, dA, dB[n0:n1], out=wide[:, n0:n1])
         ctx.status()
-        ok = bool(torch.equal(full, single)) and bool(torch.equal(wide[:, n0:n1], single[:, n0:n1]))
+        # the gather fused into the epilogue: every rank's GEMM stores its block into every rank's C
+        local_c, views = sharded.share_full_c(M, N)
+        local_c.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sharded.gemm_scatter_columns(ctx, dA, dB[n0:n1], views, N)
+        ctx.status()
+        dist.barrier()
+        fused_ok = bool(torch.equal(local_c, single))
+        dist.barrier()
+        del views
+        ok = (bool(torch.equal(full, single)) and bool(torch.equal(wide[:, n0:n1], single[:, n0:n1]))
+              and fused_ok)
         untouched = bool((wide[:, :n0] == 0).all()) and bool((wide[:, n1:] == 0).all())
         q.put((rank, ok and untouched, tuple(full.shape)))
         dist.destroy_process_group()

@@ -306,21 +306,18 @@ def run_ours(args):
 
     fused_ms = None
     if args.fused_allgather and world > 1 and not fp8:
-        local_c, views = sharded.share_full_c(M, n_total)
+        shared = sharded.SharedC(ctx, M, n_total)
         barrier()
-        if wl["scaling"] == "strong":
-            run_fused = lambda i: sharded.gemm_scatter_columns(ctx, dA, dBs[i % len(dBs)], views, n_total)
-        else:
-            # weak workloads: rank r owns columns [r*N, (r+1)*N) of the N*world-wide C
-            order = [rank] + [r for r in range(world) if r != rank]
-            dests = [views[r][:, rank * N:(rank + 1) * N] for r in order]
-            run_fused = lambda i: ctx.gemm_bf16_tn_scatter(dA, dBs[i % len(dBs)], dests)
+        # weak workloads: rank r owns columns [r*N, (r+1)*N) of the N*world-wide C
+        n_first = sharded.column_shard(n_total, world, rank)[0] if wl["scaling"] == "strong" else rank * N
+        dest_ptrs = shared.column_block_ptrs(n_first)
         f_steps = min(args.steps, 50)
-        f_total, _ = timed(run_fused, f_steps, 3)
+        f_total, _ = timed(lambda i: ctx.gemm_bf16_tn_scatter(dA, dBs[i % len(dBs)], dest_ptrs, n_total),
+                           f_steps, 3)
         ctx.status()
         fused_ms = f_total / f_steps
         barrier()
-        del views
+        shared.close()
 
     # end to end: host buffers in, host buffer out, every step
     e2e_steps = args.steps

@@ -132,6 +132,15 @@ int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t l
                                 int64_t ldb, void* const* C_dests, int n_dests, int64_t ldc,
                                 int64_t M, int64_t N, int64_t K, float alpha, void* stream);
 
+/* Buffers for the scatter above (no counterpart in the reference). peer_alloc gives device
+ * memory of this context's GPU plus a 64-byte handle that another PROCESS on the node passes
+ * to peer_open (with its own context) to get a pointer its GPU can write through NVLink.
+ * Close every opened pointer before the owner frees the buffer. */
+int patina_gemm_peer_alloc(PatinaGemmContext* ctx, size_t bytes, void** ptr, unsigned char handle_out[64]);
+int patina_gemm_peer_open(PatinaGemmContext* ctx, const unsigned char handle[64], void** ptr);
+int patina_gemm_peer_close(PatinaGemmContext* ctx, void* ptr);
+int patina_gemm_peer_free(PatinaGemmContext* ctx, void* ptr);
+
 /* End-to-end form with HOST buffers, the shape of run.rs `run_gemm`
  * (alloc + memcpy_htod + launch + memcpy_dtoh, run.rs:484-528): copies A and B
  * to context-owned device buffers, runs the GEMM, copies C back, all on

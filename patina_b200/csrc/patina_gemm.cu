@@ -252,7 +252,6 @@ struct PatinaGemmContext {
   uint32_t* d_sk_counters = nullptr;
   size_t cap_sk_partials = 0, cap_sk_counters = 0;
   bool sk_attr_set[2] = {false, false};
-  bool peer_enabled[64] = {};
   uint32_t sk_burst = 4;
   // device staging for patina_gemm_host
   void* d_a = nullptr;
@@ -730,32 +729,56 @@ int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t l
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   if (!C_dests || n_dests < 1 || n_dests > kMaxDests)
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "n_dests must be 1..8 and C_dests non-null");
-  {
-    // Destinations in another GPU's memory need peer access from this context's device.
-    DeviceGuard guard(ctx->device);
-    for (int d = 0; d < n_dests; ++d) {
-      cudaPointerAttributes at{};
-      if (!C_dests[d] || cudaPointerGetAttributes(&at, C_dests[d]) != cudaSuccess) {
-        cudaGetLastError();
-        return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "a destination of C is not a device pointer");
-      }
-      if (at.type == cudaMemoryTypeDevice && at.device != ctx->device && at.device >= 0 &&
-          at.device < 64 && !ctx->peer_enabled[at.device]) {
-        int can = 0;
-        cudaDeviceCanAccessPeer(&can, ctx->device, at.device);
-        if (!can)
-          return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
-                           fmt("device %d cannot access memory of device %d", ctx->device, at.device));
-        const cudaError_t pe = cudaDeviceEnablePeerAccess(at.device, 0);
-        if (pe != cudaSuccess && pe != cudaErrorPeerAccessAlreadyEnabled)
-          return cuda_fail(ctx, pe, "cudaDeviceEnablePeerAccess");
-        cudaGetLastError();
-        ctx->peer_enabled[at.device] = true;
-      }
-    }
-  }
   return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C_dests[0], ldc, M, N, K, alpha, nullptr,
                      static_cast<cudaStream_t>(stream), C_dests + 1, n_dests - 1);
+}
+
+// ---- buffers that other processes on the node can write ------------------------------------
+int patina_gemm_peer_alloc(PatinaGemmContext* ctx, size_t bytes, void** ptr, unsigned char handle_out[64]) {
+  if (!ctx || !ptr || !handle_out || bytes == 0) return PATINA_GEMM_ERR_INVALID_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  DeviceGuard guard(ctx->device);
+  *ptr = nullptr;
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMalloc(peer buffer)");
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, *ptr);
+  if (e != cudaSuccess) {
+    cudaFree(*ptr);
+    *ptr = nullptr;
+    return cuda_fail(ctx, e, "cudaIpcGetMemHandle");
+  }
+  std::memcpy(handle_out, &h, 64);
+  return PATINA_GEMM_OK;
+}
+
+int patina_gemm_peer_open(PatinaGemmContext* ctx, const unsigned char handle[64], void** ptr) {
+  if (!ctx || !ptr || !handle) return PATINA_GEMM_ERR_INVALID_ARG;
+  // Opened with THIS context's device current: the driver maps the exporter's memory for this
+  // device and enables peer access between the two as part of the open.
+  DeviceGuard guard(ctx->device);
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  *ptr = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaIpcOpenMemHandle");
+  return PATINA_GEMM_OK;
+}
+
+int patina_gemm_peer_close(PatinaGemmContext* ctx, void* ptr) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  if (!ptr) return PATINA_GEMM_OK;
+  DeviceGuard guard(ctx->device);
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? PATINA_GEMM_OK : cuda_fail(ctx, e, "cudaIpcCloseMemHandle");
+}
+
+int patina_gemm_peer_free(PatinaGemmContext* ctx, void* ptr) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  if (!ptr) return PATINA_GEMM_OK;
+  DeviceGuard guard(ctx->device);
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? PATINA_GEMM_OK : cuda_fail(ctx, e, "cudaFree(peer buffer)");
 }
 
 int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const void* hostA,

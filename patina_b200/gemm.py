@@ -167,22 +167,45 @@ class GemmContext:
             self._raise(rc)
         return out
 
-    def gemm_bf16_tn_scatter(self, A, B, dests, alpha=1.0):
-        """C = alpha * A @ B^T stored to every tensor in `dests` (same shape and row stride; the
-        first is normally local, the others peer buffers mapped into this process)."""
+    def gemm_bf16_tn_scatter(self, A, B, dest_ptrs, ldc: int, alpha=1.0):
+        """C = alpha * A @ B^T stored to every device address in `dest_ptrs` (row stride `ldc`
+        elements for all of them; the first is normally local, the others peer buffers opened
+        with peer_open)."""
         M, K = A.shape
         N = B.shape[0]
-        ldc = dests[0].stride(0)
-        for d in dests:
-            if tuple(d.shape) != (M, N) or d.stride(0) != ldc or d.stride(1) != 1 or d.dtype != torch.bfloat16:
-                raise PatinaGemmError(_l.ERR_INVALID_ARG, "destinations must be [M,N] bf16 with one row stride")
-        arr = (C.c_void_p * len(dests))(*[d.data_ptr() for d in dests])
+        arr = (C.c_void_p * len(dest_ptrs))(*[int(p) for p in dest_ptrs])
         rc = self._lib.patina_gemm_bf16_tn_scatter(self._h, A.data_ptr(), A.stride(0), B.data_ptr(),
-                                                   B.stride(0), arr, len(dests), ldc, M, N, K,
+                                                   B.stride(0), arr, len(dest_ptrs), int(ldc), M, N, K,
                                                    float(alpha), _stream_ptr(self.device))
         if rc != _l.OK:
             self._raise(rc)
-        return dests[0]
+
+    # ------------------------------------------------------------- peer buffers
+    def peer_alloc(self, nbytes: int) -> tuple[int, bytes]:
+        """Device memory other processes of the node can map: (pointer, 64-byte handle)."""
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        rc = self._lib.patina_gemm_peer_alloc(self._h, int(nbytes), C.byref(ptr), handle)
+        if rc != _l.OK:
+            self._raise(rc)
+        return int(ptr.value), handle.raw
+
+    def peer_open(self, handle: bytes) -> int:
+        ptr = C.c_void_p()
+        rc = self._lib.patina_gemm_peer_open(self._h, handle, C.byref(ptr))
+        if rc != _l.OK:
+            self._raise(rc)
+        return int(ptr.value)
+
+    def peer_close(self, ptr: int) -> None:
+        rc = self._lib.patina_gemm_peer_close(self._h, ptr)
+        if rc != _l.OK:
+            self._raise(rc)
+
+    def peer_free(self, ptr: int) -> None:
+        rc = self._lib.patina_gemm_peer_free(self._h, ptr)
+        if rc != _l.OK:
+            self._raise(rc)
 
     def gemm_host(self, hA: torch.Tensor, hB: torch.Tensor, hC: torch.Tensor, alpha: float = 1.0,
                   config: GemmConfig | None = None) -> torch.Tensor:
@@ -199,6 +222,21 @@ class GemmContext:
         if rc != _l.OK:
             self._raise(rc)
         return hC
+
+
+class _RawCuda:
+    """A raw device pointer seen through the CUDA array interface (16-bit words)."""
+
+    def __init__(self, ptr: int, shape: tuple[int, ...]):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": "<i2", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def wrap_bf16(ptr: int, rows: int, cols: int, device: int) -> torch.Tensor:
+    """A [rows, cols] bf16 tensor over memory this library (or a peer) allocated; no copy.
+    The tensor does not own the memory."""
+    t = torch.as_tensor(_RawCuda(ptr, (rows, cols)), device=torch.device("cuda", device))
+    return t.view(torch.bfloat16)
 
 
 _default_ctx: dict[int, GemmContext] = {}

@@ -68,34 +68,47 @@ def all_gather_columns(c_shard: torch.Tensor, n_total: int, group=None, align: i
     return out
 
 
-def share_full_c(M: int, n_total: int, group=None) -> tuple[torch.Tensor, list[torch.Tensor]]:
-    """Every rank allocates one full-width C[M, n_total] (bf16) and maps every other rank's
-    into its own process (CUDA IPC through torch's tensor sharing). Returns
-    (local_C, [C of rank 0, ..., C of rank W-1]); the entry of this rank is local_C itself.
-    Keep local_C alive as long as any rank may still write to it."""
-    from torch.multiprocessing.reductions import reduce_tensor
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    local = torch.empty((M, n_total), dtype=torch.bfloat16, device="cuda")
-    handles = [None] * world
-    dist.all_gather_object(handles, reduce_tensor(local), group=group)
-    views = []
-    for r, (rebuild, args) in enumerate(handles):
-        views.append(local if r == rank else rebuild(*args))
-    return local, views
+class SharedC:
+    """One full-width C[M, n_total] (bf16) per rank, each mapped into every other rank's process
+    (CUDA IPC through the library's peer_alloc / peer_open). `ptrs[r]` is the address of rank
+    r's C as seen from this rank's GPU; `local` is this rank's own C as a tensor. Call close()
+    on every rank before the process exits."""
+
+    def __init__(self, ctx, M: int, n_total: int, group=None):
+        from .gemm import wrap_bf16
+        self.ctx, self.group = ctx, group
+        self.M, self.n_total = M, n_total
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        own_ptr, handle = ctx.peer_alloc(M * n_total * 2)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.ptrs = [own_ptr if r == self.rank else ctx.peer_open(handles[r]) for r in range(self.world)]
+        self.local = wrap_bf16(own_ptr, M, n_total, ctx.device)
+
+    def column_block_ptrs(self, n0: int) -> list[int]:
+        """Where column n0 of this rank's block starts in every rank's C, own buffer first."""
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        return [self.ptrs[r] + 2 * n0 for r in order]
+
+    def close(self) -> None:
+        self.local = None
+        dist.barrier(self.group)           # nobody is still writing into anybody's buffer
+        for r, ptr in enumerate(self.ptrs):
+            if r != self.rank:
+                self.ctx.peer_close(ptr)
+        dist.barrier(self.group)           # nobody holds a mapping of anybody's buffer any more
+        self.ctx.peer_free(self.ptrs[self.rank])
+        self.ptrs = []
 
 
-def gemm_scatter_columns(ctx, A: torch.Tensor, B_shard: torch.Tensor, full_views: list[torch.Tensor],
-                         n_total: int, group=None, alpha: float = 1.0, align: int = 256) -> torch.Tensor:
+def gemm_scatter_columns(ctx, A: torch.Tensor, B_shard: torch.Tensor, shared: SharedC,
+                         alpha: float = 1.0, align: int = 256) -> torch.Tensor:
     """This rank's column block of C, written by the GEMM's epilogue into EVERY rank's full C
     (the all-gather fused into the kernel as peer stores over NVLink). No collective is called;
-    ranks must synchronise (e.g. dist.barrier + stream sync) before anyone reads its C or reuses it."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    n0, n1 = column_shard(n_total, world, rank, align)
+    ranks must synchronise (e.g. stream sync + dist.barrier) before anyone reads its C or reuses it."""
+    n0, n1 = column_shard(shared.n_total, shared.world, shared.rank, align)
     if B_shard.shape[0] != n1 - n0:
-        raise ValueError(f"rank {rank}: B shard has {B_shard.shape[0]} rows, expected {n1 - n0}")
-    if n1 == n0:
-        return full_views[rank]
-    order = [rank] + [r for r in range(world) if r != rank]       # own buffer first
-    dests = [full_views[r][:, n0:n1] for r in order]
-    ctx.gemm_bf16_tn_scatter(A, B_shard, dests, alpha=alpha)
-    return full_views[rank]
+        raise ValueError(f"rank {shared.rank}: B shard has {B_shard.shape[0]} rows, expected {n1 - n0}")
+    if n1 > n0:
+        ctx.gemm_bf16_tn_scatter(A, B_shard, shared.column_block_ptrs(n0), shared.n_total, alpha=alpha)
+    return shared.local

@@ -43,16 +43,16 @@ def _worker(rank, world, port, q):
         sharded.gemm_column_shard(ctx, dA, dB[n0:n1], out=wide[:, n0:n1])
         ctx.status()
         # the gather fused into the epilogue: every rank's GEMM stores its block into every rank's C
-        local_c, views = sharded.share_full_c(M, N)
-        local_c.zero_()
+        shared = sharded.SharedC(ctx, M, N)
+        shared.local.zero_()
         torch.cuda.synchronize()
         dist.barrier()
-        sharded.gemm_scatter_columns(ctx, dA, dB[n0:n1], views, N)
+        sharded.gemm_scatter_columns(ctx, dA, dB[n0:n1], shared)
         ctx.status()
         dist.barrier()
-        fused_ok = bool(torch.equal(local_c, single))
+        fused_ok = bool(torch.equal(shared.local, single))
         dist.barrier()
-        del views
+        shared.close()
         ok = (bool(torch.equal(full, single)) and bool(torch.equal(wide[:, n0:n1], single[:, n0:n1]))
               and fused_ok)
         untouched = bool((wide[:, :n0] == 0).all()) and bool((wide[:, n1:] == 0).all())

@@ -397,6 +397,7 @@ def run_ours(args):
                      "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_src,
                      "kernel_ms_mean": round(kernel_ms, 5), "kernel_ms_min": round(min(per), 5),
                      "timed_region_s": round(region_s, 4),
+                     "best_launch_tflops": round(flops_per_gpu / (min(per) * 1e-3) / 1e12, 2),
                      "algorithmic_flops_per_launch": flops_per_gpu,
                      "algorithmic_bytes_per_launch": bytes_per_gpu, **extra},
     }

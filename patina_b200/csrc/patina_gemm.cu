@@ -56,11 +56,8 @@ const KernelEntry kKernels[] = {
     // bf16 -> bf16
     PATINA_KERNEL(2, 2, 256, 4, kBF16, kOutBF16),  // 512 x 256 per pair, accumulators fill TMEM
     PATINA_KERNEL(2, 1, 256, 6, kBF16, kOutBF16),  // 256 x 256 per pair, double-buffered TMEM
-    PATINA_KERNEL(2, 1, 256, 5, kBF16, kOutBF16),
-    PATINA_KERNEL(2, 1, 256, 4, kBF16, kOutBF16),
-    PATINA_KERNEL(2, 1, 256, 3, kBF16, kOutBF16),
+    PATINA_KERNEL(2, 1, 256, 4, kBF16, kOutBF16),  // (4 and 6 stages measured alike: not latency-bound)
     PATINA_KERNEL(1, 1, 256, 4, kBF16, kOutBF16),
-    PATINA_KERNEL(1, 1, 256, 3, kBF16, kOutBF16),
     PATINA_KERNEL(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
     PATINA_KERNEL(2, 1, 128, 8, kBF16, kOutBF16),
     PATINA_KERNEL(1, 1, 128, 6, kBF16, kOutBF16),

@@ -236,6 +236,31 @@ def test_streamk_decode_shapes_full_size(ctx, oracle_mod):
     check_norm(oracle_mod, out, expect_bf16(oracle_mod, Aq, Bq, alpha=sa * sb), "fp8 stream-K")
 
 
+def test_scatter_to_several_destinations_on_one_gpu(ctx, oracle_mod):
+    """patina_gemm_bf16_tn_scatter with three destinations that all live on this GPU: each must
+    receive exactly what the single-destination call produces (on a multi-GPU node the extra
+    destinations are peer buffers; the kernel path is the same)."""
+    import patina_b200
+    from patina_b200 import inputs, lib as L
+    M, N, K, ldc = 1000, 520, 328, 2048
+    A, B = inputs.make_operands("llm", M, N, K, seed=77)
+    dA, dB = A.cuda(), B.cuda()
+    single = ctx.gemm_tn(dA, dB)
+    wide = [torch.full((M, ldc), 9.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    offs = [0, 256, 1024]                      # a different column offset in every destination
+    ptrs = [w.data_ptr() + 2 * o for w, o in zip(wide, offs)]
+    ctx.gemm_bf16_tn_scatter(dA, dB, ptrs, ldc)
+    ctx.status()
+    for w, o in zip(wide, offs):
+        assert torch.equal(w[:, o:o + N], single)
+        assert bool((w[:, :o] == 9.0).all()) and bool((w[:, o + N:] == 9.0).all())
+    check_norm(oracle_mod, single, expect_bf16(oracle_mod, A, B), "scatter reference")
+    with pytest.raises(patina_b200.PatinaGemmError, match="n_dests"):
+        ctx.gemm_bf16_tn_scatter(dA, dB, ptrs * 3, ldc)            # nine destinations
+    with pytest.raises(patina_b200.PatinaGemmError):
+        ctx.gemm_bf16_tn_scatter(dA, dB, [ptrs[0], ptrs[1] + 2], ldc)   # misaligned destination
+
+
 # ------------------------------------------------------- full benchmark sizes
 def test_bf16_8192_cubed_samples_and_properties(ctx, oracle_mod):
     """8192^3 (the benchmark size): 64 sampled rows against the oracle, plus

@@ -25,7 +25,8 @@ REF_SO = os.path.join(_HERE, "_ref", "libpatina_ref.so")
 def build(reference_root: str | None = None) -> None:
     """Compile the restatement; also the reference wrapper when its sources exist."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
-    root = reference_root or os.environ.get("PATINA_REFERENCE_ROOT", "/root/reference")
+    root = (reference_root or os.environ.get("PATINA_REFERENCE_ROOT")
+            or os.path.abspath(os.path.join(_HERE, "..", "..", "reference")))
     if os.path.isfile(os.path.join(root, "harness", "gemm_check.cpp")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={root}"])
 

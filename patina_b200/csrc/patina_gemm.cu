@@ -232,6 +232,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+constexpr int kHostChunksMax = 8;
+constexpr int kHostEvents = 3 + 2 * kHostChunksMax;
+
 struct PatinaGemmContext {
   int device = 0;
   int num_sms = 0;
@@ -250,6 +253,9 @@ struct PatinaGemmContext {
   size_t cap_sk_partials = 0, cap_sk_counters = 0;
   bool sk_attr_set[2] = {false, false};
   uint32_t sk_burst = 4;
+  // copy streams and events of patina_gemm_host's pipelined form
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  cudaEvent_t ev[3 + 2 * 8] = {};
   // device staging for patina_gemm_host
   void* d_a = nullptr;
   void* d_b = nullptr;
@@ -652,6 +658,12 @@ void patina_gemm_context_destroy(PatinaGemmContext* ctx) {
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_sk_partials) cudaFree(ctx->d_sk_partials);
     if (ctx->d_sk_counters) cudaFree(ctx->d_sk_counters);
+    if (ctx->s_in) {
+      cudaStreamDestroy(ctx->s_in);
+      cudaStreamDestroy(ctx->s_out);
+      for (int i = 0; i < kHostEvents; ++i)
+        if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
+    }
     if (ctx->d_a) cudaFree(ctx->d_a);
     if (ctx->d_b) cudaFree(ctx->d_b);
     if (ctx->d_c) cudaFree(ctx->d_c);
@@ -801,20 +813,86 @@ int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const vo
   if ((rc = grow(ctx, &ctx->d_b, &ctx->cap_b, (size_t)N * dk * ib + 16)) != 0) return rc;
   if ((rc = grow(ctx, &ctx->d_c, &ctx->cap_c, (size_t)M * dn * ob + 16)) != 0) return rc;
   cudaError_t e;
-  if (K > 0) {
-    e = cudaMemcpy2DAsync(ctx->d_a, (size_t)dk * ib, hostA, (size_t)lda * ib, (size_t)K * ib,
-                          (size_t)M, cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(A)");
-    e = cudaMemcpy2DAsync(ctx->d_b, (size_t)dk * ib, hostB, (size_t)ldb * ib, (size_t)K * ib,
-                          (size_t)N, cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(B)");
+  // Large problems are cut into row blocks of A / C so that the copy of block i+1 to the
+  // device, the GEMM of block i and the copy of block i-1 back overlap (PCIe is full duplex and
+  // is what bounds this call). Two context-owned streams carry the copies; events tie them to
+  // the caller's stream in both directions, so the call still behaves as work enqueued on it.
+  const size_t total_bytes = ((size_t)M * K + (size_t)N * K) * ib + (size_t)M * N * ob;
+  int chunks = 1;
+  if (K > 0 && total_bytes >= ((size_t)32 << 20) && M >= 1024) {
+    chunks = (int)(M / 1024);
+    if (chunks > kHostChunksMax) chunks = kHostChunksMax;
   }
-  rc = launch_gemm(ctx, in_type, out_type, ctx->d_a, dk, ctx->d_b, dk, ctx->d_c, dn, M, N, K, alpha,
-                   cfg, stream);
-  if (rc != PATINA_GEMM_OK) return rc;
-  e = cudaMemcpy2DAsync(hostC, (size_t)ldc * ob, ctx->d_c, (size_t)dn * ob, (size_t)N * ob,
-                        (size_t)M, cudaMemcpyDeviceToHost, stream);
-  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(C)");
+  if (chunks <= 1) {
+    if (K > 0) {
+      e = cudaMemcpy2DAsync(ctx->d_a, (size_t)dk * ib, hostA, (size_t)lda * ib, (size_t)K * ib,
+                            (size_t)M, cudaMemcpyHostToDevice, stream);
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(A)");
+      e = cudaMemcpy2DAsync(ctx->d_b, (size_t)dk * ib, hostB, (size_t)ldb * ib, (size_t)K * ib,
+                            (size_t)N, cudaMemcpyHostToDevice, stream);
+      if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(B)");
+    }
+    rc = launch_gemm(ctx, in_type, out_type, ctx->d_a, dk, ctx->d_b, dk, ctx->d_c, dn, M, N, K, alpha,
+                     cfg, stream);
+    if (rc != PATINA_GEMM_OK) return rc;
+    e = cudaMemcpy2DAsync(hostC, (size_t)ldc * ob, ctx->d_c, (size_t)dn * ob, (size_t)N * ob,
+                          (size_t)M, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemcpy2DAsync(C)");
+    return PATINA_GEMM_OK;
+  }
+
+  if (!ctx->s_in) {
+    e = cudaStreamCreateWithFlags(&ctx->s_in, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking);
+    for (int i = 0; e == cudaSuccess && i < kHostEvents; ++i)
+      e = cudaEventCreateWithFlags(&ctx->ev[i], cudaEventDisableTiming);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "creating copy streams/events");
+  }
+  cudaEvent_t ev_start = ctx->ev[0], ev_b = ctx->ev[1], ev_done = ctx->ev[2];
+  cudaEvent_t* ev_a = &ctx->ev[3];
+  cudaEvent_t* ev_g = &ctx->ev[3 + kHostChunksMax];
+  // rows per block: a whole number of 512-row tiles
+  int64_t rows = (M + chunks - 1) / chunks;
+  rows = (rows + 511) / 512 * 512;
+#define PATINA_TRY(call, what)                       \
+  do {                                               \
+    e = (call);                                      \
+    if (e != cudaSuccess) return cuda_fail(ctx, e, what); \
+  } while (0)
+  PATINA_TRY(cudaEventRecord(ev_start, stream), "cudaEventRecord");
+  PATINA_TRY(cudaStreamWaitEvent(ctx->s_in, ev_start, 0), "cudaStreamWaitEvent");
+  PATINA_TRY(cudaStreamWaitEvent(ctx->s_out, ev_start, 0), "cudaStreamWaitEvent");
+  PATINA_TRY(cudaMemcpy2DAsync(ctx->d_b, (size_t)dk * ib, hostB, (size_t)ldb * ib, (size_t)K * ib,
+                               (size_t)N, cudaMemcpyHostToDevice, ctx->s_in), "cudaMemcpy2DAsync(B)");
+  PATINA_TRY(cudaEventRecord(ev_b, ctx->s_in), "cudaEventRecord");
+  int used = 0;
+  for (int64_t r0 = 0; r0 < M; r0 += rows, ++used) {
+    const int64_t mr = (M - r0) < rows ? (M - r0) : rows;
+    PATINA_TRY(cudaMemcpy2DAsync(static_cast<char*>(ctx->d_a) + (size_t)r0 * dk * ib, (size_t)dk * ib,
+                                 static_cast<const char*>(hostA) + (size_t)r0 * lda * ib,
+                                 (size_t)lda * ib, (size_t)K * ib, (size_t)mr, cudaMemcpyHostToDevice,
+                                 ctx->s_in), "cudaMemcpy2DAsync(A block)");
+    PATINA_TRY(cudaEventRecord(ev_a[used], ctx->s_in), "cudaEventRecord");
+  }
+  PATINA_TRY(cudaStreamWaitEvent(stream, ev_b, 0), "cudaStreamWaitEvent");
+  used = 0;
+  for (int64_t r0 = 0; r0 < M; r0 += rows, ++used) {
+    const int64_t mr = (M - r0) < rows ? (M - r0) : rows;
+    PATINA_TRY(cudaStreamWaitEvent(stream, ev_a[used], 0), "cudaStreamWaitEvent");
+    rc = launch_gemm(ctx, in_type, out_type, static_cast<char*>(ctx->d_a) + (size_t)r0 * dk * ib, dk,
+                     ctx->d_b, dk, static_cast<char*>(ctx->d_c) + (size_t)r0 * dn * ob, dn, mr, N, K,
+                     alpha, cfg, stream);
+    if (rc != PATINA_GEMM_OK) return rc;
+    PATINA_TRY(cudaEventRecord(ev_g[used], stream), "cudaEventRecord");
+    PATINA_TRY(cudaStreamWaitEvent(ctx->s_out, ev_g[used], 0), "cudaStreamWaitEvent");
+    PATINA_TRY(cudaMemcpy2DAsync(static_cast<char*>(hostC) + (size_t)r0 * ldc * ob, (size_t)ldc * ob,
+                                 static_cast<char*>(ctx->d_c) + (size_t)r0 * dn * ob, (size_t)dn * ob,
+                                 (size_t)N * ob, (size_t)mr, cudaMemcpyDeviceToHost, ctx->s_out),
+               "cudaMemcpy2DAsync(C block)");
+  }
+  PATINA_TRY(cudaEventRecord(ev_done, ctx->s_out), "cudaEventRecord");
+  PATINA_TRY(cudaStreamWaitEvent(stream, ev_done, 0), "cudaStreamWaitEvent");
+#undef PATINA_TRY
   return PATINA_GEMM_OK;
 }
 

@@ -300,6 +300,27 @@ def test_host_entry_point(ctx, oracle_mod):
     check_norm(oracle_mod, Cn, expect_bf16(oracle_mod, A, B), "host entry")
 
 
+def test_host_entry_point_pipelined_blocks(ctx, oracle_mod):
+    """A problem large enough for patina_gemm_host to cut into row blocks whose copies and
+    GEMMs overlap; ragged M, padded host pitches; two calls in a row on the same buffers."""
+    from patina_b200 import inputs
+    M, N, K = 4100, 2048, 2056
+    A, B = inputs.make_operands("llm", M, N, K, seed=5)
+    Ap = torch.zeros((M, K + 8), dtype=torch.bfloat16).pin_memory(); Ap[:, :K] = A
+    Bp = torch.zeros((N, K + 24), dtype=torch.bfloat16).pin_memory(); Bp[:, :K] = B
+    Cp = torch.full((M, N + 16), 3.0, dtype=torch.bfloat16).pin_memory()
+    want_dev = ctx.gemm_tn(A.cuda(), B.cuda())
+    ctx.status()
+    for _ in range(2):
+        Cp.fill_(3.0)
+        ctx.gemm_host(Ap[:, :K], Bp[:, :K], Cp[:, :N])
+        ctx.status()
+        assert torch.equal(Cp[:, :N], want_dev.cpu())
+        assert bool((Cp[:, N:] == 3.0).all())
+    rows = np.arange(0, M, 41, dtype=np.int64)
+    check_norm(oracle_mod, Cp[:, :N][torch.from_numpy(rows)], expect_bf16(oracle_mod, A, B, rows=rows), "pipelined host entry")
+
+
 def test_wait_expiry_is_reported_and_context_survives(ctx, oracle_mod):
     """A wait that runs out must come back as PATINA_GEMM_ERR_TIMEOUT, not a hang.
     The limit is set to 1 ns on a single-tile problem with a long K loop, so the

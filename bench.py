@@ -289,8 +289,13 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     launches0 = ctx.launch_count
-    total_ms, per = timed(lambda i: ctx.gemm_tn(dA, dBs[i % len(dBs)], out=dC, alpha=alpha),
-                          args.steps, args.warmup)
+    if args.fused_epilogue and not fp8:
+        bias_d = torch.randn(N, generator=torch.Generator().manual_seed(1)).cuda()
+        step = lambda i: ctx.gemm_bf16_tn_fused(dA, dBs[i % len(dBs)], out=dC, alpha=alpha, bias=bias_d,
+                                                activation="gelu")
+    else:
+        step = lambda i: ctx.gemm_tn(dA, dBs[i % len(dBs)], out=dC, alpha=alpha)
+    total_ms, per = timed(step, args.steps, args.warmup)
     launches = ctx.launch_count - launches0 - args.warmup
     clocks = sampler.stop() if rank == 0 else None
     ctx.status()
@@ -386,7 +391,8 @@ def run_ours(args):
                    "l2": (f"{wl['rotate']} weight buffers of {N * K * ebytes / 1e6:.0f} MB in rotation"
                           if wl["rotate"] > 1 else
                           f"inputs ({(M * K + N * K) * ebytes / 1e6:.0f} MB) vs L2 126 MB; no flush between steps"),
-                   "kernel": "library's automatic choice (tcgen05 large-tile or stream-K kernel)"},
+                   "kernel": "library's automatic choice (tcgen05 large-tile or stream-K kernel)" +
+                             ("; bias + GELU fused into the epilogue" if args.fused_epilogue and not fp8 else "")},
         "per_gpu_tflops": round(value / world, 2),
         "pct_of_nominal_peak": round(100.0 * value / world / nominal, 2),
         "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
@@ -459,6 +465,8 @@ def main():
     ap.add_argument("--fused-allgather", action="store_true",
                     help="N > 1: also time the GEMM whose epilogue stores its column block into every "
                          "GPU's full-width C (peer writes over NVLink instead of a collective)")
+    ap.add_argument("--fused-epilogue", action="store_true",
+                    help="time the bf16 GEMM with bias + GELU applied in its epilogue instead of the plain one")
     ap.add_argument("--allgather", action="store_true",
                     help="N > 1: also time the optional NCCL all-gather of the C column shards")
     args = ap.parse_args()

@@ -120,6 +120,22 @@ int patina_gemm_ex(PatinaGemmContext* ctx, int in_type, int out_type, const void
                    const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N,
                    int64_t K, float alpha, const PatinaGemmConfig* cfg, void* stream);
 
+/* Fused epilogue (no counterpart in the reference, whose kernel stores the raw accumulator,
+ * v2_gemm_pipelined.ptx:252-330): C = act(alpha * A*B^T + bias[n] + beta * R[m,n]), evaluated in
+ * fp32 on the accumulator before the single rounding to bf16. bias: N floats or NULL; residual:
+ * [M, ldr] bf16 or NULL (may alias C only if ldr == ldc and it is the same buffer);
+ * activation: 0 none, 1 relu, 2 gelu (erf form), 3 silu. */
+typedef struct PatinaGemmEpilogue {
+  const void* bias;
+  const void* residual;
+  int64_t ldr;
+  float beta;
+  int32_t activation;
+} PatinaGemmEpilogue;
+int patina_gemm_bf16_tn_fused(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                              int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                              float alpha, const PatinaGemmEpilogue* epi, void* stream);
+
 /* Column-shard scatter (no counterpart in the reference, which is single-GPU): the same bf16
  * GEMM, but every finished tile of C is stored to n_dests (1..8) destinations that share M, N
  * and ldc. On a multi-GPU node each GPU passes, for every GPU g, the address of ITS column block

@@ -158,6 +158,29 @@ def scale_round_bf16(ref: np.ndarray, alpha: float = 1.0) -> np.ndarray:
     return out
 
 
+def fused_epilogue_bf16(ref: np.ndarray, alpha=1.0, bias=None, residual=None, beta=1.0,
+                        activation="none") -> np.ndarray:
+    """bf16(act(alpha * ref + bias[n] + beta * residual[m, n])) widened to float32, all of it in
+    double before the single rounding: the expected output of the fused-epilogue entry point.
+    (The reference's kernel has no epilogue arithmetic; this extends its double-precision check.)"""
+    import math
+    x = alpha * np.asarray(ref, dtype=np.float64)
+    if bias is not None:
+        x = x + np.asarray(bias, dtype=np.float64)[None, :]
+    if residual is not None:
+        x = x + beta * np.asarray(residual, dtype=np.float64)
+    if activation == "relu":
+        x = np.maximum(x, 0.0)
+    elif activation == "gelu":
+        erf = np.vectorize(math.erf)
+        x = 0.5 * x * (1.0 + erf(x / math.sqrt(2.0)))
+    elif activation == "silu":
+        x = x / (1.0 + np.exp(-x))
+    elif activation != "none":
+        raise ValueError(activation)
+    return scale_round_bf16(x, 1.0)
+
+
 # --------------------------------------------------------------- comparisons
 def compare_legacy(got: np.ndarray, ref: np.ndarray, atol=1e-3, rtol=1e-3):
     """The reference harness's rule. Returns (mismatches, max_abs, max_rel, sum_got)."""

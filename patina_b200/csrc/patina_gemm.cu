@@ -44,23 +44,27 @@ using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CStoreMaps
 struct KernelEntry {
   int cta_group, m_sub, block_n, stages, in_type, out_type;
   KernelFn fn;
+  KernelFn fn_fused;  // same kernel with the bias / residual / activation epilogue, or null
   uint32_t smem_bytes;
 };
 
-#define PATINA_KERNEL(G, MS, BN, S, IN, OUT)                  \
-  { G, MS, BN, S, IN, OUT, gemm_tn_kernel<G, MS, BN, S, IN, OUT>, \
+#define PATINA_KERNEL(G, MS, BN, S, IN, OUT)                           \
+  { G, MS, BN, S, IN, OUT, gemm_tn_kernel<G, MS, BN, S, IN, OUT>, nullptr, \
     GemmTraits<G, MS, BN, S, IN, OUT>::kSmemBytes }
+#define PATINA_KERNEL_F(G, MS, BN, S, IN, OUT)                 \
+  { G, MS, BN, S, IN, OUT, gemm_tn_kernel<G, MS, BN, S, IN, OUT>, \
+    gemm_tn_kernel<G, MS, BN, S, IN, OUT, true>, GemmTraits<G, MS, BN, S, IN, OUT>::kSmemBytes }
 
 // Listed best-first per type pair: an explicit request takes the first match.
 const KernelEntry kKernels[] = {
     // bf16 -> bf16
-    PATINA_KERNEL(2, 2, 256, 4, kBF16, kOutBF16),  // 512 x 256 per pair, accumulators fill TMEM
-    PATINA_KERNEL(2, 1, 256, 6, kBF16, kOutBF16),  // 256 x 256 per pair, double-buffered TMEM
-    PATINA_KERNEL(2, 1, 256, 4, kBF16, kOutBF16),  // (4 and 6 stages measured alike: not latency-bound)
-    PATINA_KERNEL(1, 1, 256, 4, kBF16, kOutBF16),
-    PATINA_KERNEL(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
-    PATINA_KERNEL(2, 1, 128, 8, kBF16, kOutBF16),
-    PATINA_KERNEL(1, 1, 128, 6, kBF16, kOutBF16),
+    PATINA_KERNEL_F(2, 2, 256, 4, kBF16, kOutBF16),  // 512 x 256 per pair, accumulators fill TMEM
+    PATINA_KERNEL_F(2, 1, 256, 6, kBF16, kOutBF16),  // 256 x 256 per pair, double-buffered TMEM
+    PATINA_KERNEL_F(2, 1, 256, 4, kBF16, kOutBF16),  // (4 and 6 stages measured alike: not latency-bound)
+    PATINA_KERNEL_F(1, 1, 256, 4, kBF16, kOutBF16),
+    PATINA_KERNEL_F(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
+    PATINA_KERNEL_F(2, 1, 128, 8, kBF16, kOutBF16),
+    PATINA_KERNEL_F(1, 1, 128, 6, kBF16, kOutBF16),
     // e4m3 -> bf16
     PATINA_KERNEL(2, 2, 256, 4, kE4M3, kOutBF16),
     PATINA_KERNEL(2, 1, 256, 6, kE4M3, kOutBF16),
@@ -459,7 +463,8 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
 int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A, int64_t lda,
                 const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                 float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream,
-                void* const* extra_dests = nullptr, int n_extra = 0) {
+                void* const* extra_dests = nullptr, int n_extra = 0,
+                const PatinaGemmEpilogue* epi = nullptr) {
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   std::string err;
   int rc = validate_args(in_type, out_type, A, lda, B, ldb, C, ldc, M, N, K, &err);
@@ -483,7 +488,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
                      "stream_k needs M <= 128, bf16 or e4m3 inputs and bf16 output");
   const bool explicit_tile = cfg && (cfg->cta_group != 0 || cfg->block_n != 0 || cfg->m_sub != 0);
-  if (n_extra == 0 &&
+  if (n_extra == 0 && epi == nullptr &&
       (want_sk > 0 || (want_sk == 0 && !explicit_tile &&
                        streamk_preferred(in_type, out_type, M, N, K, ctx->num_sms))))
     return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream);
@@ -517,6 +522,9 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k->fn),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)k->smem_bytes);
+    if (e == cudaSuccess && k->fn_fused)
+      e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k->fn_fused),
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->smem_bytes);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(smem)");
     ctx->smem_attr_set[ki] = true;
   }
@@ -558,6 +566,16 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   p.k_blocks = plan.k_blocks;
   p.group_m = (uint32_t)plan.group_m;
   p.alpha = alpha;
+  KernelFn fn = k->fn;
+  if (epi) {
+    if (!k->fn_fused) return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "no fused-epilogue kernel for these types");
+    fn = k->fn_fused;
+    p.bias = static_cast<const float*>(epi->bias);
+    p.residual = static_cast<const __nv_bfloat16*>(epi->residual);
+    p.ldr = epi->ldr;
+    p.beta = epi->beta;
+    p.activation = (uint32_t)epi->activation;
+  }
   p.n_dests = (uint32_t)(1 + n_extra);
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
@@ -575,7 +593,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   lc.attrs = attr;
   lc.numAttrs = (k->cta_group > 1) ? 1 : 0;
   drain_stale_error("large-tile launch");
-  cudaError_t e = cudaLaunchKernelEx(&lc, k->fn, tm_a, tm_b, tm_c, p);
+  cudaError_t e = cudaLaunchKernelEx(&lc, fn, tm_a, tm_b, tm_c, p);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaLaunchKernelEx");
   ctx->launches += 1;
   return PATINA_GEMM_OK;
@@ -730,6 +748,25 @@ int patina_gemm_f16_tn_f32out(PatinaGemmContext* ctx, const void* A, int64_t lda
                               float alpha, void* stream) {
   return launch_gemm(ctx, kF16, kOutF32, A, lda, B, ldb, C, ldc, M, N, K, alpha, nullptr,
                      static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_bf16_tn_fused(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                              int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                              float alpha, const PatinaGemmEpilogue* epi, void* stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  if (!epi) return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "epilogue description is null");
+  if (epi->activation < 0 || epi->activation > 3)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "unknown activation");
+  if (epi->bias && (reinterpret_cast<uintptr_t>(epi->bias) & 3u))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "bias is not 4-byte aligned");
+  if (epi->residual) {
+    if ((reinterpret_cast<uintptr_t>(epi->residual) & 15u) || epi->ldr < N || (epi->ldr * 2) % 16 != 0)
+      return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
+                       "residual must be 16-byte aligned with ldr >= N and a row pitch multiple of 16 bytes");
+  }
+  if (K == 0) return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "fused epilogue needs K > 0");
+  return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C, ldc, M, N, K, alpha, nullptr,
+                     static_cast<cudaStream_t>(stream), nullptr, 0, epi);
 }
 
 int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,

@@ -51,10 +51,27 @@ struct GemmParams {
   uint32_t k_blocks;                     // ceil(K / elements per 128 bytes)
   uint32_t group_m;                      // scheduler band height (tiles)
   float alpha;
+  // fused epilogue (kernels instantiated with kFused): C = act(alpha*acc + bias[n] + beta*R[m,n])
+  const float* bias;            // N floats or null
+  const __nv_bfloat16* residual;  // [M, ldr] bf16 or null
+  int64_t ldr;
+  float beta;
+  uint32_t activation;     // Activation
   uint32_t n_dests;        // destinations of C (1..kMaxDests)
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
 };
+
+enum Activation : uint32_t { kActNone = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
+
+__device__ __forceinline__ float apply_activation(float x, uint32_t act) {
+  switch (act) {
+    case kActRelu: return fmaxf(x, 0.0f);
+    case kActGelu: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case kActSilu: return x / (1.0f + __expf(-x));
+    default: return x;
+  }
+}
 
 enum StatusCode : uint32_t {
   kStatusOk = 0,
@@ -141,7 +158,7 @@ struct GemmTraits {
   static_assert((2 * kStages + 4) * 8 + 8 <= kBarrierRegionBytes, "barrier region too small");
 };
 
-template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut>
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused = false>
 __global__ void __launch_bounds__(64 + 128 * kMSub, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CStoreMaps tm_c, const GemmParams p) {
@@ -337,6 +354,40 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             else ptx::mbar_arrive(tempty_bar + 8u * buf);
           }
         }
+        if constexpr (kFused) {
+          // v := act(alpha * v + bias[col] + beta * R[row, col]) in fp32; every lane of the warp
+          // reads the same bias words (one broadcast transaction per load), and its own row of R.
+          const uint32_t cc = col0 + ch * T::kChunkCols;
+          const uint32_t r = row0 + lane;
+          float add[kFp32PerChunk];
+#pragma unroll
+          for (uint32_t i = 0; i < kFp32PerChunk; ++i)
+            add[i] = (p.bias != nullptr && cc + i < p.N) ? __ldg(p.bias + cc + i) : 0.0f;
+          if (p.residual != nullptr && r < p.M) {
+            const __nv_bfloat16* rr = p.residual + (size_t)r * p.ldr + cc;
+#pragma unroll
+            for (uint32_t g = 0; g < kFp32PerChunk / 8u; ++g) {
+              if (cc + 8u * g + 8u <= p.N) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rr + 8u * g));
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (uint32_t e2 = 0; e2 < 4; ++e2) {
+                  const float2 f = __bfloat1622float2(h2[e2]);
+                  add[8u * g + 2u * e2] += p.beta * f.x;
+                  add[8u * g + 2u * e2 + 1u] += p.beta * f.y;
+                }
+              } else {
+#pragma unroll
+                for (uint32_t e1 = 0; e1 < 8; ++e1)
+                  if (cc + 8u * g + e1 < p.N) add[8u * g + e1] += p.beta * __bfloat162float(rr[8u * g + e1]);
+              }
+            }
+          }
+#pragma unroll
+          for (uint32_t i = 0; i < kFp32PerChunk; ++i)
+            v[i] = __float_as_uint(apply_activation(__uint_as_float(v[i]) * p.alpha + add[i], p.activation));
+        }
+        const float out_scale = kFused ? 1.0f : p.alpha;
         // The staging buffer about to be rewritten must have been read by its store.
         if (lane == 0) ptx::tma_store_wait_read<T::kStageBufs - 1>();
         __syncwarp();
@@ -346,8 +397,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           uint32_t w0, w1, w2, w3;
           if constexpr (kOut == kOutBF16) {
             auto pack = [&](uint32_t a, uint32_t b) -> uint32_t {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a) * p.alpha,
-                                                       __uint_as_float(b) * p.alpha);
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a) * out_scale,
+                                                       __uint_as_float(b) * out_scale);
               return *reinterpret_cast<uint32_t*>(&h);
             };
             w0 = pack(v[8 * j + 0], v[8 * j + 1]);
@@ -355,10 +406,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             w2 = pack(v[8 * j + 4], v[8 * j + 5]);
             w3 = pack(v[8 * j + 6], v[8 * j + 7]);
           } else {
-            w0 = __float_as_uint(__uint_as_float(v[4 * j + 0]) * p.alpha);
-            w1 = __float_as_uint(__uint_as_float(v[4 * j + 1]) * p.alpha);
-            w2 = __float_as_uint(__uint_as_float(v[4 * j + 2]) * p.alpha);
-            w3 = __float_as_uint(__uint_as_float(v[4 * j + 3]) * p.alpha);
+            w0 = __float_as_uint(__uint_as_float(v[4 * j + 0]) * out_scale);
+            w1 = __float_as_uint(__uint_as_float(v[4 * j + 1]) * out_scale);
+            w2 = __float_as_uint(__uint_as_float(v[4 * j + 2]) * out_scale);
+            w3 = __float_as_uint(__uint_as_float(v[4 * j + 3]) * out_scale);
           }
           const uint32_t dst = row_addr + ((j ^ row_sw) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1),

@@ -167,6 +167,32 @@ class GemmContext:
             self._raise(rc)
         return out
 
+    def gemm_bf16_tn_fused(self, A, B, out=None, alpha=1.0, bias=None, residual=None, beta=1.0,
+                           activation="none"):
+        """out = act(alpha * A @ B^T + bias[n] + beta * residual[m, n]) in one kernel
+        (bias: float32 [N]; residual: bf16 [M, N]; activation: none | relu | gelu | silu)."""
+        M, K = A.shape
+        N = B.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+        acts = {"none": _l.ACT_NONE, "relu": _l.ACT_RELU, "gelu": _l.ACT_GELU, "silu": _l.ACT_SILU}
+        if activation not in acts:
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, f"unknown activation {activation!r}")
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "bias must be a contiguous float32 vector of N elements")
+        if residual is not None and (residual.dtype != torch.bfloat16 or tuple(residual.shape) != (M, N)
+                                     or residual.stride(1) != 1):
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "residual must be bf16 [M, N], contiguous rows")
+        epi = _l.GemmEpilogue(bias.data_ptr() if bias is not None else None,
+                              residual.data_ptr() if residual is not None else None,
+                              residual.stride(0) if residual is not None else 0, float(beta), acts[activation])
+        rc = self._lib.patina_gemm_bf16_tn_fused(self._h, A.data_ptr(), A.stride(0), B.data_ptr(),
+                                                 B.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+                                                 float(alpha), C.byref(epi), _stream_ptr(self.device))
+        if rc != _l.OK:
+            self._raise(rc)
+        return out
+
     def gemm_bf16_tn_scatter(self, A, B, dest_ptrs, ldc: int, alpha=1.0):
         """C = alpha * A @ B^T stored to every device address in `dest_ptrs` (row stride `ldc`
         elements for all of them; the first is normally local, the others peer buffers opened

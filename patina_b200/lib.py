@@ -22,7 +22,7 @@ SYMBOLS = (
     "patina_gemm_plan", "patina_gemm_smem_desc", "patina_gemm_idesc",
     "patina_gemm_k_advance_units", "patina_gemm_tmem_lane_offset", "patina_gemm_tile_coord",
     "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_range",
-    "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_peer_alloc",
+    "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_peer_alloc",
     "patina_gemm_peer_open", "patina_gemm_peer_close", "patina_gemm_peer_free",
 )
 
@@ -37,6 +37,14 @@ class StreamKPlan(C.Structure):
 class GemmConfig(C.Structure):
     _fields_ = [("cta_group", C.c_int32), ("block_n", C.c_int32), ("stages", C.c_int32),
                 ("group_m", C.c_int32), ("max_ctas", C.c_int32), ("m_sub", C.c_int32), ("stream_k", C.c_int32)]
+
+
+class GemmEpilogue(C.Structure):
+    _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_int64), ("beta", C.c_float),
+                ("activation", C.c_int32)]
+
+
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 
 
 class GemmPlan(C.Structure):
@@ -102,6 +110,7 @@ def load() -> C.CDLL:
     L.patina_gemm_streamk_owner.argtypes = [C.c_uint64] * 3
     L.patina_gemm_streamk_owner.restype = C.c_uint32
     L.patina_gemm_bf16_tn_scatter.argtypes = [vp, vp, i64, vp, i64, C.POINTER(vp), i32, i64, i64, i64, i64, f32, vp]
+    L.patina_gemm_bf16_tn_fused.argtypes = gemm_args + [f32, C.POINTER(GemmEpilogue), vp]
     L.patina_gemm_peer_alloc.argtypes = [vp, C.c_size_t, C.POINTER(vp), C.c_char_p]
     L.patina_gemm_peer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
     L.patina_gemm_peer_close.argtypes = [vp, vp]

@@ -236,6 +236,44 @@ def test_streamk_decode_shapes_full_size(ctx, oracle_mod):
     check_norm(oracle_mod, out, expect_bf16(oracle_mod, Aq, Bq, alpha=sa * sb), "fp8 stream-K")
 
 
+@pytest.mark.parametrize("activation", ["none", "relu", "gelu", "silu"])
+def test_fused_epilogue(ctx, oracle_mod, activation):
+    """bias + residual + activation applied to the fp32 accumulator inside the kernel, against the
+    oracle's double-precision epilogue; ragged shape; also each term alone, and the empty
+    epilogue, which must reproduce the plain entry point bit for bit."""
+    from patina_b200 import inputs
+    M, N, K = 1000, 776, 520
+    A, B = inputs.make_operands("llm", M, N, K, seed=9)
+    g = torch.Generator().manual_seed(4)
+    bias = torch.randn(N, generator=g, dtype=torch.float32)
+    res = (torch.randn((M, N), generator=g) * 0.5).to(torch.bfloat16)
+    ref = oracle_mod.ref_gemm_tn(widen(oracle_mod, A), widen(oracle_mod, B))
+    dA, dB = A.cuda(), B.cuda()
+    ldc = (N + 7) // 8 * 8
+    cases = [dict(bias=bias, residual=res, beta=0.75), dict(bias=bias), dict(residual=res, beta=-1.0)]
+    for kw in cases:
+        out = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :N]
+        dev_kw = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in kw.items()}
+        ctx.gemm_bf16_tn_fused(dA, dB, out=out, alpha=1.25, activation=activation, **dev_kw)
+        ctx.status()
+        want = oracle_mod.fused_epilogue_bf16(
+            ref, 1.25, bias=kw.get("bias").numpy() if "bias" in kw else None,
+            residual=widen(oracle_mod, kw["residual"]) if "residual" in kw else None,
+            beta=kw.get("beta", 1.0), activation=activation)
+        check_norm(oracle_mod, out, want, f"fused {activation} {sorted(kw)}")
+    if activation == "none":
+        plain = ctx.gemm_tn(dA, dB, alpha=1.25)
+        empty = ctx.gemm_bf16_tn_fused(dA, dB, alpha=1.25)
+        ctx.status()
+        assert torch.equal(plain, empty)
+        # residual read from the output buffer itself (C += A B^T)
+        acc = res.cuda().clone()
+        ctx.gemm_bf16_tn_fused(dA, dB, out=acc, residual=acc, beta=1.0)
+        ctx.status()
+        check_norm(oracle_mod, acc, oracle_mod.fused_epilogue_bf16(ref, 1.0, residual=widen(oracle_mod, res)),
+                   "in-place accumulate")
+
+
 def test_scatter_to_several_destinations_on_one_gpu(ctx, oracle_mod):
     """patina_gemm_bf16_tn_scatter with three destinations that all live on this GPU: each must
     receive exactly what the single-destination call produces (on a multi-GPU node the extra

@@ -142,3 +142,21 @@ def test_bf16_output_rounding(oracle_mod):
     out = oracle_mod.scale_round_bf16(ref, alpha=1.0)
     assert out[0] == 1.0 and out[1] == 3.0
     assert oracle_mod.scale_round_bf16(ref, alpha=0.5)[1] == 1.5
+
+
+def test_fused_epilogue_reference(oracle_mod):
+    """The oracle's double-precision epilogue against torch float64, every activation."""
+    rng = np.random.default_rng(8)
+    ref = rng.standard_normal((9, 14)) * 3
+    bias = rng.standard_normal(14).astype(np.float32)
+    res = rng.standard_normal((9, 14)).astype(np.float32)
+    t = torch.from_numpy(0.5 * ref) + torch.from_numpy(bias.astype(np.float64))[None, :] + 2.0 * torch.from_numpy(res.astype(np.float64))
+    want = {"none": t, "relu": torch.relu(t), "gelu": torch.nn.functional.gelu(t), "silu": torch.nn.functional.silu(t)}
+    for act, w in want.items():
+        got = oracle_mod.fused_epilogue_bf16(ref, 0.5, bias=bias, residual=res, beta=2.0, activation=act)
+        exp = w.to(torch.float32).to(torch.bfloat16).float().numpy()
+        # double -> bf16 directly vs double -> float -> bf16 may differ by one bf16 ulp at a tie
+        assert np.max(np.abs(got - exp)) <= np.max(np.abs(exp)) * 2 ** -7
+        assert np.mean(got != exp) < 0.02
+    with pytest.raises(ValueError):
+        oracle_mod.fused_epilogue_bf16(ref, activation="tanh")

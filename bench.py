@@ -290,9 +290,12 @@ def run_ours(args):
         sampler.start()
     launches0 = ctx.launch_count
     if args.fused_epilogue and not fp8:
-        bias_d = torch.randn(N, generator=torch.Generator().manual_seed(1)).cuda()
+        mode = args.fused_epilogue
+        bias_d = torch.randn(N, generator=torch.Generator().manual_seed(1)).cuda() if "bias" in mode else None
+        res_d = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda") if "res" in mode else None
+        act = "gelu" if "gelu" in mode else ("relu" if "relu" in mode else "none")
         step = lambda i: ctx.gemm_bf16_tn_fused(dA, dBs[i % len(dBs)], out=dC, alpha=alpha, bias=bias_d,
-                                                activation="gelu")
+                                                residual=res_d, activation=act)
     else:
         step = lambda i: ctx.gemm_tn(dA, dBs[i % len(dBs)], out=dC, alpha=alpha)
     total_ms, per = timed(step, args.steps, args.warmup)
@@ -392,7 +395,7 @@ def run_ours(args):
                           if wl["rotate"] > 1 else
                           f"inputs ({(M * K + N * K) * ebytes / 1e6:.0f} MB) vs L2 126 MB; no flush between steps"),
                    "kernel": "library's automatic choice (tcgen05 large-tile or stream-K kernel)" +
-                             ("; bias + GELU fused into the epilogue" if args.fused_epilogue and not fp8 else "")},
+                             (f"; fused epilogue: {args.fused_epilogue}" if args.fused_epilogue and not fp8 else "")},
         "per_gpu_tflops": round(value / world, 2),
         "pct_of_nominal_peak": round(100.0 * value / world / nominal, 2),
         "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
@@ -465,8 +468,8 @@ def main():
     ap.add_argument("--fused-allgather", action="store_true",
                     help="N > 1: also time the GEMM whose epilogue stores its column block into every "
                          "GPU's full-width C (peer writes over NVLink instead of a collective)")
-    ap.add_argument("--fused-epilogue", action="store_true",
-                    help="time the bf16 GEMM with bias + GELU applied in its epilogue instead of the plain one")
+    ap.add_argument("--fused-epilogue", default="", choices=["", "none", "bias", "relu", "gelu", "bias_gelu", "bias_res_gelu"],
+                    help="time the bf16 GEMM with this epilogue fused in (patina_gemm_bf16_tn_fused) instead of the plain one")
     ap.add_argument("--allgather", action="store_true",
                     help="N > 1: also time the optional NCCL all-gather of the C column shards")
     args = ap.parse_args()

@@ -765,8 +765,19 @@ int patina_gemm_bf16_tn_fused(PatinaGemmContext* ctx, const void* A, int64_t lda
                        "residual must be 16-byte aligned with ldr >= N and a row pitch multiple of 16 bytes");
   }
   if (K == 0) return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "fused epilogue needs K > 0");
-  return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C, ldc, M, N, K, alpha, nullptr,
-                     static_cast<cudaStream_t>(stream), nullptr, 0, epi);
+  // A transcendental per output is too much work for the epilogue of the TMEM-filling tile,
+  // which runs between two mainloops: take the double-buffered 256 x 256 pair tile, whose
+  // epilogue overlaps the next tile's mainloop (measured at 8192 x 14336 x 4096 with bias + GELU:
+  // see the results file).
+  PatinaGemmConfig overlap{};
+  overlap.cta_group = 2;
+  overlap.block_n = 256;
+  overlap.m_sub = 1;
+  const bool heavy = epi->activation == (int)kActGelu || epi->activation == (int)kActSilu;
+  const char* force = std::getenv("PATINA_FUSED_TILE");  // tuning knob: "big" or "overlap"
+  const bool use_overlap = force ? (force[0] == 'o') : heavy;
+  return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C, ldc, M, N, K, alpha,
+                     use_overlap ? &overlap : nullptr, static_cast<cudaStream_t>(stream), nullptr, 0, epi);
 }
 
 int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,

@@ -64,11 +64,25 @@ struct GemmParams {
 
 enum Activation : uint32_t { kActNone = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
 
+// erf to about 1e-6 absolute (Abramowitz & Stegun 7.1.26 with approximate reciprocal and
+// exponential): two special-function instructions and a degree-5 polynomial; far inside the
+// rounding of a bf16 result.
+__device__ __forceinline__ float fast_erf(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));  // approximate reciprocal: 1 ulp-ish
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float y = 1.0f - poly * t * __expf(-ax * ax);
+  return copysignf(y, x);
+}
+
 __device__ __forceinline__ float apply_activation(float x, uint32_t act) {
   switch (act) {
     case kActRelu: return fmaxf(x, 0.0f);
-    case kActGelu: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
-    case kActSilu: return x / (1.0f + __expf(-x));
+    case kActGelu: return 0.5f * x * (1.0f + fast_erf(x * 0.70710678118654752f));
+    case kActSilu: return __fdividef(x, 1.0f + __expf(-x));
     default: return x;
   }
 }
@@ -360,9 +374,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           const uint32_t cc = col0 + ch * T::kChunkCols;
           const uint32_t r = row0 + lane;
           float add[kFp32PerChunk];
+          if (p.bias != nullptr && cc + kFp32PerChunk <= p.N &&
+              (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
 #pragma unroll
-          for (uint32_t i = 0; i < kFp32PerChunk; ++i)
-            add[i] = (p.bias != nullptr && cc + i < p.N) ? __ldg(p.bias + cc + i) : 0.0f;
+            for (uint32_t g = 0; g < kFp32PerChunk / 4u; ++g) {
+              const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + cc) + g);
+              add[4u * g] = b4.x;
+              add[4u * g + 1u] = b4.y;
+              add[4u * g + 2u] = b4.z;
+              add[4u * g + 3u] = b4.w;
+            }
+          } else {
+#pragma unroll
+            for (uint32_t i = 0; i < kFp32PerChunk; ++i)
+              add[i] = (p.bias != nullptr && cc + i < p.N) ? __ldg(p.bias + cc + i) : 0.0f;
+          }
           if (p.residual != nullptr && r < p.M) {
             const __nv_bfloat16* rr = p.residual + (size_t)r * p.ldr + cc;
 #pragma unroll

@@ -62,6 +62,8 @@ const KernelEntry kKernels[] = {
     PATINA_KERNEL_F(2, 1, 256, 6, kBF16, kOutBF16),  // 256 x 256 per pair, double-buffered TMEM
     PATINA_KERNEL_F(2, 1, 256, 4, kBF16, kOutBF16),  // (4 and 6 stages measured alike: not latency-bound)
     PATINA_KERNEL_F(1, 1, 256, 4, kBF16, kOutBF16),
+    PATINA_KERNEL_F(2, 2, 224, 4, kBF16, kOutBF16),  // 512 x 224: widths like 1792 or 3584 (multiples of
+                                                     // 224 with an awkward count of 256-wide tiles)
     PATINA_KERNEL_F(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
     PATINA_KERNEL_F(2, 1, 128, 8, kBF16, kOutBF16),
     PATINA_KERNEL_F(1, 1, 128, 6, kBF16, kOutBF16),
@@ -177,6 +179,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   p.cluster = best->cta_group;
   p.smem_bytes = best->smem_bytes;
   p.tmem_cols = (2 * best->m_sub * best->block_n <= 512 ? 2 : 1) * best->m_sub * best->block_n;
+  p.tmem_cols = p.tmem_cols <= 256 ? 256 : 512;  // allocation granularity: a power of two
   const SmemPlan sp = smem_plan(best->cta_group, best->m_sub, best->block_n, best->stages,
                                 output_bytes(out_type));
   p.stage_bytes = sp.stage_bytes;

@@ -155,7 +155,10 @@ struct GemmTraits {
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kAccCols = kMSub * BN;                  // TMEM columns of one tile
   static constexpr uint32_t kAccBufs = (2 * kAccCols <= 512) ? 2 : 1;
-  static constexpr uint32_t kTmemCols = kAccBufs * kAccCols;
+  static constexpr uint32_t kTmemUsed = kAccBufs * kAccCols;
+  // tcgen05.alloc takes powers of two (32..512): round the request up
+  static constexpr uint32_t kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128
+                                        : kTmemUsed <= 256 ? 256 : 512;
   static constexpr uint32_t kStageBufs = staging_bufs(kMSub);       // per epilogue warp
   static constexpr uint32_t kRowBytes = staging_row_bytes(kMSub, output_bytes(kOut));  // 128 or 64
   static constexpr uint32_t kBufBytes = staging_buf_bytes(kMSub, output_bytes(kOut));
@@ -165,8 +168,8 @@ struct GemmTraits {
       smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut)).total_bytes;
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
-  static_assert(kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
-                "TMEM allocations are powers of two up to 512 columns");
+  static_assert(kTmemUsed <= 512, "accumulators exceed the 512 TMEM columns");
+  static_assert(BN % kChunkCols == 0, "tile width must be a whole number of store boxes");
   static_assert((kBBytes % 1024) == 0, "swizzle atoms must stay 1024-byte aligned");
   static_assert(kSmemBytes <= kMaxDynSmem, "shared-memory plan exceeds 227 KB");
   static_assert((2 * kStages + 4) * 8 + 8 <= kBarrierRegionBytes, "barrier region too small");

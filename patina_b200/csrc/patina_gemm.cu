@@ -64,6 +64,8 @@ const KernelEntry kKernels[] = {
     PATINA_KERNEL_F(1, 1, 256, 4, kBF16, kOutBF16),
     PATINA_KERNEL_F(2, 2, 224, 4, kBF16, kOutBF16),  // 512 x 224: widths like 1792 or 3584 (multiples of
                                                      // 224 with an awkward count of 256-wide tiles)
+    PATINA_KERNEL_F(2, 2, 192, 4, kBF16, kOutBF16),
+    PATINA_KERNEL_F(2, 2, 160, 4, kBF16, kOutBF16),
     PATINA_KERNEL_F(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
     PATINA_KERNEL_F(2, 1, 128, 8, kBF16, kOutBF16),
     PATINA_KERNEL_F(1, 1, 128, 6, kBF16, kOutBF16),
@@ -100,11 +102,18 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int num_sms) {
   const double area = (double)M * (double)N /
                       ((double)ceil_div(M, tile_m) * tile_m * (double)ceil_div(N, k.block_n) * k.block_n);
   const double eff = (double)tiles / (double)(waves * slots) * area;
-  // operand bytes fetched per output element, relative to the largest tile
-  const double per_out = (double)(tile_m + k.block_n) / ((double)tile_m * k.block_n);
-  const double best = (512.0 + 256.0) / (512.0 * 256.0);
-  double speed = 1.0 / (1.0 + 0.35 * (per_out / best - 1.0));
-  if (k.cta_group == 1) speed *= 0.97;  // a pair halves its B traffic from shared memory
+  // Throughput of each tile shape on exactly filled waves, relative to the 512 x 256 pair tile
+  // (measured at M = 8192, K = 4096, N = 37 tile widths; smaller tiles move more operand bytes
+  // from L2 per flop and the part is L2-bandwidth / power bound).
+  double speed = 0.6;
+  if (k.cta_group == 2 && k.m_sub == 2) {
+    speed = k.block_n >= 256 ? 1.0 : k.block_n >= 224 ? 0.985 : k.block_n >= 192 ? 0.95
+            : k.block_n >= 160 ? 0.86 : 0.80;
+  } else if (k.cta_group == 2) {
+    speed = k.block_n >= 256 ? 0.955 : 0.70;
+  } else {
+    speed = k.block_n >= 256 ? 0.895 : 0.62;
+  }
   return eff * speed;
 }
 

@@ -64,6 +64,9 @@ const KernelEntry kKernels[] = {
     PATINA_KERNEL_F(1, 1, 256, 4, kBF16, kOutBF16),
     PATINA_KERNEL_F(2, 2, 224, 4, kBF16, kOutBF16),  // 512 x 224: widths like 1792 or 3584 (multiples of
                                                      // 224 with an awkward count of 256-wide tiles)
+    PATINA_KERNEL(2, 2, 240, 4, kBF16, kOutBF16),    // widths with half a store box at the end:
+    PATINA_KERNEL(2, 2, 208, 4, kBF16, kOutBF16),    // plain epilogue only
+    PATINA_KERNEL(2, 2, 176, 4, kBF16, kOutBF16),
     PATINA_KERNEL_F(2, 2, 192, 4, kBF16, kOutBF16),
     PATINA_KERNEL_F(2, 2, 160, 4, kBF16, kOutBF16),
     PATINA_KERNEL_F(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
@@ -71,6 +74,8 @@ const KernelEntry kKernels[] = {
     PATINA_KERNEL_F(1, 1, 128, 6, kBF16, kOutBF16),
     // e4m3 -> bf16
     PATINA_KERNEL(2, 2, 256, 4, kE4M3, kOutBF16),
+    PATINA_KERNEL(2, 2, 240, 4, kE4M3, kOutBF16),
+    PATINA_KERNEL(2, 2, 224, 4, kE4M3, kOutBF16),
     PATINA_KERNEL(2, 1, 256, 6, kE4M3, kOutBF16),
     PATINA_KERNEL(1, 1, 256, 4, kE4M3, kOutBF16),
     PATINA_KERNEL(1, 1, 128, 6, kE4M3, kOutBF16),
@@ -90,36 +95,39 @@ bool type_pair_supported(int in_type, int out_type) {
 // ------------------------------------------------------------------ planning
 uint32_t ceil_div(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
 
-// Fraction of the persistent slots that do useful work, times a speed factor of
-// the tile shape (bigger tiles move fewer operand bytes per flop).
+// Useful work per unit of modelled time, as a fraction of what the 512 x 256 pair tile does on
+// exactly filled waves. Two measured facts go in:
+//  * the throughput of each tile shape on filled waves (M = 8192, K = 4096, 37 tile columns):
+//    smaller tiles move more operand bytes from L2 per flop, and the part is bound by shared
+//    L2 bandwidth and power, not by any one SM;
+//  * for the same reason a partly filled last wave is cheaper than a full one: with half the
+//    clusters active each tile ran 29 % faster, so a wave filled to f costs about 0.55 + 0.45 f.
 double config_score(const KernelEntry& k, int64_t M, int64_t N, int num_sms) {
   const int64_t tile_m = 128 * k.cta_group * k.m_sub;
   const uint64_t tiles = (uint64_t)ceil_div(M, tile_m) * ceil_div(N, k.block_n);
   const uint64_t slots = (uint64_t)(num_sms / k.cta_group);
   if (slots == 0 || tiles == 0) return 0.0;
   const uint64_t waves = (tiles + slots - 1) / slots;
-  // useful fraction of the padded tile area
-  const double area = (double)M * (double)N /
-                      ((double)ceil_div(M, tile_m) * tile_m * (double)ceil_div(N, k.block_n) * k.block_n);
-  const double eff = (double)tiles / (double)(waves * slots) * area;
-  // Throughput of each tile shape on exactly filled waves, relative to the 512 x 256 pair tile
-  // (measured at M = 8192, K = 4096, N = 37 tile widths; smaller tiles move more operand bytes
-  // from L2 per flop and the part is L2-bandwidth / power bound).
+  const double last_fill = (double)(tiles - (waves - 1) * slots) / (double)slots;
   double speed = 0.6;
   if (k.cta_group == 2 && k.m_sub == 2) {
-    speed = k.block_n >= 256 ? 1.0 : k.block_n >= 224 ? 0.985 : k.block_n >= 192 ? 0.95
+    speed = k.block_n >= 256 ? 1.0 : k.block_n >= 240 ? 0.99 : k.block_n >= 224 ? 0.985
+            : k.block_n >= 208 ? 0.975 : k.block_n >= 192 ? 0.95 : k.block_n >= 176 ? 0.91
             : k.block_n >= 160 ? 0.86 : 0.80;
   } else if (k.cta_group == 2) {
     speed = k.block_n >= 256 ? 0.955 : 0.70;
+    if (k.in_type == kE4M3) speed *= 0.97;  // twice the MMA rate: the smaller tile falls back further
   } else {
     speed = k.block_n >= 256 ? 0.895 : 0.62;
   }
-  return eff * speed;
+  const double tile_cost = (double)tile_m * (double)k.block_n / speed;  // per-tile time, area units
+  const double time = tile_cost * ((double)(waves - 1) + 0.55 + 0.45 * last_fill);
+  return (double)M * (double)N / (time * (double)slots);
 }
 
 int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
               const PatinaGemmConfig* cfg, int num_sms, PatinaGemmPlan* out,
-              const KernelEntry** entry_out, std::string* err) {
+              const KernelEntry** entry_out, std::string* err, bool need_fused = false) {
   if (!type_pair_supported(in_type, out_type)) {
     if (err) *err = fmt("unsupported type pair in=%d out=%d", in_type, out_type);
     return PATINA_GEMM_ERR_INVALID_ARG;
@@ -140,6 +148,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (c.block_n != 0 && k.block_n != c.block_n) continue;
       if (c.stages != 0 && k.stages != c.stages) continue;
       if (k.m_sub != (c.m_sub != 0 ? c.m_sub : 1)) continue;  // explicit requests default to m_sub = 1
+      if (need_fused && !k.fn_fused) continue;
       best = &k;
     }
     if (!best) {
@@ -155,6 +164,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (k.in_type != in_type || k.out_type != out_type) continue;
       if (c.stages != 0 && k.stages != c.stages) continue;
       if (k.cta_group == 2 && num_sms < 2) continue;
+      if (need_fused && !k.fn_fused) continue;
       const double s = config_score(k, M, N, num_sms);
       if (s > best_score) {
         best_score = s;
@@ -506,7 +516,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream);
   PatinaGemmPlan plan;
   const KernelEntry* k = nullptr;
-  rc = make_plan(in_type, out_type, M, N, K, cfg, ctx->num_sms, &plan, &k, &err);
+  rc = make_plan(in_type, out_type, M, N, K, cfg, ctx->num_sms, &plan, &k, &err, epi != nullptr);
   if (rc != PATINA_GEMM_OK) return set_error(ctx, rc, err);
 
   const uint32_t ib = input_bytes(in_type);

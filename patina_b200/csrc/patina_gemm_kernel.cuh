@@ -163,13 +163,17 @@ struct GemmTraits {
   static constexpr uint32_t kRowBytes = staging_row_bytes(kMSub, output_bytes(kOut));  // 128 or 64
   static constexpr uint32_t kBufBytes = staging_buf_bytes(kMSub, output_bytes(kOut));
   static constexpr uint32_t kChunkCols = kRowBytes / output_bytes(kOut);  // columns per store box
-  static constexpr uint32_t kChunks = BN / kChunkCols;
+  // A width that is not a whole number of store boxes ends with one box moved left so that it
+  // finishes at the tile's edge; the columns it shares with its neighbour are written twice
+  // with the same values.
+  static constexpr uint32_t kChunks = (BN + kChunkCols - 1) / kChunkCols;
+  static constexpr bool kOverlapLastChunk = (BN % kChunkCols) != 0;
   static constexpr uint32_t kSmemBytes =
       smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut)).total_bytes;
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
   static_assert(kTmemUsed <= 512, "accumulators exceed the 512 TMEM columns");
-  static_assert(BN % kChunkCols == 0, "tile width must be a whole number of store boxes");
+  static_assert(BN >= kChunkCols && BN % 16 == 0, "tile width: at least one store box, multiple of 16");
   static_assert((kBBytes % 1024) == 0, "swizzle atoms must stay 1024-byte aligned");
   static_assert(kSmemBytes <= kMaxDynSmem, "shared-memory plan exceeds 227 KB");
   static_assert((2 * kStages + 4) * 8 + 8 <= kBarrierRegionBytes, "barrier region too small");
@@ -183,6 +187,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   constexpr bool kPair = (kCtaGroup == 2);
   constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
   constexpr uint32_t kEpiWarps = T::kEpiWarps;
+  // The fused epilogue may read C itself as the residual, so no column may be produced twice.
+  static_assert(!(kFused && T::kOverlapLastChunk), "fused epilogue needs whole store boxes");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -358,9 +364,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll 1
       for (uint32_t ch = 0; ch < T::kChunks; ++ch) {
         uint32_t v[kFp32PerChunk];
+        const uint32_t ch_col = (T::kOverlapLastChunk && ch == T::kChunks - 1)
+                                    ? (uint32_t)BN - T::kChunkCols : ch * T::kChunkCols;
 #pragma unroll
         for (uint32_t h = 0; h < kFp32PerChunk; h += 32u)
-          ptx::tmem_ld_32x32b_x32(taddr + ch * T::kChunkCols + h, &v[h]);
+          ptx::tmem_ld_32x32b_x32(taddr + ch_col + h, &v[h]);
         ptx::tmem_ld_wait();
         if (ch == T::kChunks - 1) {
           // Accumulator fully read: hand the TMEM buffer back to the MMA issuer.
@@ -374,7 +382,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if constexpr (kFused) {
           // v := act(alpha * v + bias[col] + beta * R[row, col]) in fp32; every lane of the warp
           // reads the same bias words (one broadcast transaction per load), and its own row of R.
-          const uint32_t cc = col0 + ch * T::kChunkCols;
+          const uint32_t cc = col0 + ch_col;
           const uint32_t r = row0 + lane;
           float add[kFp32PerChunk];
           if (p.bias != nullptr && cc + kFp32PerChunk <= p.N &&
@@ -448,7 +456,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          const uint32_t cc = col0 + ch * T::kChunkCols;
+          const uint32_t cc = col0 + ch_col;
           if (row0 < p.M && cc < p.N) {
             for (uint32_t d = 0; d < p.n_dests; ++d)
               ptx::tma_store_2d(&tm_c.map[d], stg0 + sbuf * T::kBufBytes, (int32_t)cc, (int32_t)row0);

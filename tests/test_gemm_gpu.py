@@ -53,7 +53,10 @@ def cfgs():
             "pair_n256": GemmConfig(2, 256, 0, 0, 0), "pair_n128": GemmConfig(2, 128, 0, 0, 0),
             "pair_2sub_n256": GemmConfig(2, 256, 0, 0, 0, 2), "pair_2sub_n128": GemmConfig(2, 128, 0, 0, 0, 2),
             "pair_2sub_n224": GemmConfig(2, 224, 0, 0, 0, 2), "pair_2sub_n192": GemmConfig(2, 192, 0, 0, 0, 2),
-            "pair_2sub_n160": GemmConfig(2, 160, 0, 0, 0, 2)}
+            "pair_2sub_n160": GemmConfig(2, 160, 0, 0, 0, 2),
+            # widths ending in half a store box (the last box overlaps its neighbour)
+            "pair_2sub_n240": GemmConfig(2, 240, 0, 0, 0, 2), "pair_2sub_n208": GemmConfig(2, 208, 0, 0, 0, 2),
+            "pair_2sub_n176": GemmConfig(2, 176, 0, 0, 0, 2)}
 
 
 # ------------------------------------------------------------ reference shape
@@ -183,7 +186,8 @@ def test_fp8_e4m3(ctx, oracle_mod, M, N, K):
     ctx.status()
     check_norm(oracle_mod, out, want, "fp8 auto")
     for name, cfg in cfgs().items():
-        if name in ("pair_n128", "pair_2sub_n128", "pair_2sub_n224", "pair_2sub_n192", "pair_2sub_n160"):
+        if name in ("pair_n128", "pair_2sub_n128", "pair_2sub_n192", "pair_2sub_n160", "pair_2sub_n208",
+                    "pair_2sub_n176"):
             continue  # no such fp8 kernels
         out = ctx.gemm_tn(Aq.cuda(), Bq.cuda(), alpha=sa * sb, config=cfg)
         ctx.status()

@@ -58,7 +58,8 @@ typedef struct PatinaGemmConfig {
   int32_t m_sub;     /* 128-row accumulator sub-tiles per CTA: 1 or 2;
                         tile height = 128 * cta_group * m_sub */
   int32_t stream_k;  /* skinny path (M <= 128, bf16 out): 0 = library decides, 1 = force,
-                        -1 = never */
+                        -1 = never; 2 = force, and sum shared tiles in the follow-up kernel;
+                        3 = force, and let the last CTA to reach a tile sum it */
 } PatinaGemmConfig;
 
 /* What a call would launch; computed on the host without touching a device. */

@@ -420,12 +420,26 @@ cudaError_t launch_sk_kernel(const SkPlan& sp, cudaStream_t stream, const CUtens
     *attr_set = true;
   }
   fn<<<sp.grid, 192, smem, stream>>>(tm_w, tm_x, p);
-  return cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && p.split_reduce) {
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(sp.tiles * (p.m_pad / 16u), 1, 1);
+    lc.blockDim = dim3(128, 1, 1);
+    lc.dynamicSmemBytes = 0;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    e = cudaLaunchKernelEx(&lc, streamk_reduce_kernel, p, (uint32_t)sp.grid);
+  }
+  return e;
 }
 
 int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t lda, const void* B,
                    int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, int reduce_mode = 0) {
   const SkPlan sp = make_sk_plan(in_type, M, N, K, ctx->num_sms);
   // scratch: grow-only; counters start (and are left) at zero
   if (ctx->cap_sk_partials < sp.partial_bytes) {
@@ -472,13 +486,19 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.ldc = ldc;
   p.partials = ctx->d_sk_partials;
   p.counters = ctx->d_sk_counters;
+  // Wide X (more than 16 rows): a shared tile's partials are 16 KB and more per contributor; one
+  // finishing CTA per tile pulling them through its own SM was measured at 15 us for M = 128, so
+  // the sum moves to a second small kernel that every SM takes part in.
+  p.split_reduce = (sp.m_pad > 16u && sp.grid > 1u) ? 1u : 0u;
+  if (reduce_mode == 2) p.split_reduce = 1u;  // explicit request (PatinaGemmConfig::stream_k = 2 / 3)
+  if (reduce_mode == 3) p.split_reduce = 0u;
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
   cudaError_t e = (in_type == kBF16)
                       ? launch_sk_kernel<kBF16>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[0])
                       : launch_sk_kernel<kE4M3>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[1]);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "stream-K launch");
-  ctx->launches += 1;
+  ctx->launches += p.split_reduce ? 2 : 1;
   return PATINA_GEMM_OK;
 }
 
@@ -513,7 +533,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   if (n_extra == 0 && epi == nullptr &&
       (want_sk > 0 || (want_sk == 0 && !explicit_tile &&
                        streamk_preferred(in_type, out_type, M, N, K, ctx->num_sms))))
-    return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream);
+    return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream, want_sk);
   PatinaGemmPlan plan;
   const KernelEntry* k = nullptr;
   rc = make_plan(in_type, out_type, M, N, K, cfg, ctx->num_sms, &plan, &k, &err, epi != nullptr);

@@ -46,6 +46,8 @@ struct StreamKParams {
   int64_t ldc;
   float* partials;         // [tiles][max_contrib][m_pad / 4][128 rows][4] fp32
   uint32_t* counters;      // [tiles], zero between launches
+  uint32_t split_reduce;   // 1: shared tiles are only published here and summed by
+                           // streamk_reduce_kernel, launched right after on the same stream
   uint32_t* status;
   uint64_t wait_limit_ns;
 };
@@ -129,6 +131,14 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   w.limit_ns = p.wait_limit_ns;
   w.has_peer = false;
 
+  // Producer state lives outside the role branch: thread 0 starts the first ring pass before
+  // the CTA-wide set-up barrier, so that TMEM allocation and the barrier hide behind DRAM latency.
+  uint32_t prod_s = 0, prod_ph = 0;
+  uint64_t prod_u = u_begin;
+  uint32_t prod_t = (uint32_t)(u_begin / p.k_blocks);
+  uint32_t prod_kb = (uint32_t)(u_begin - (uint64_t)prod_t * p.k_blocks);
+  // W is read exactly once: keep it from displacing X (re-read by every CTA) in L2.
+  uint64_t stream_once = 0, keep = 0;
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_w);
     ptx::prefetch_tensormap(&tm_x);
@@ -143,6 +153,20 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     *abort_ptr = 0u;
     *last_ptr = 0u;
     ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+    stream_once = ptx::l2_policy_evict_first();
+    keep = ptx::l2_policy_evict_last();
+    // First pass through the ring: every stage is free, no wait needed.
+    while (prod_u < u_end && prod_ph == 0u) {
+      const uint32_t sw = ring + prod_s * kSkStageStride;
+      const int32_t k0 = (int32_t)(prod_kb * kBlockKElems);
+      ptx::mbar_arrive_expect_tx(full_bar + 8u * prod_s, kWBytes + x_bytes);
+      ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * prod_s, k0, (int32_t)(prod_t * kSkTileRows), stream_once);
+      ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * prod_s, k0, 0, keep);
+      ++prod_u;
+      if (++prod_s == kStages) { prod_s = 0; prod_ph = 1u; }
+      if (++prod_kb == p.k_blocks) { prod_kb = 0; ++prod_t; }
+    }
   }
   if (warp_idx == 1) {
     ptx::tmem_alloc<1>(tmem_slot, kSkTmemCols);
@@ -152,18 +176,18 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Let the follow-up reduce kernel's blocks take their places now; they wait for this grid to
+  // complete before touching memory.
+  if (p.split_reduce) ptx::launch_dependents();
 
   // ------------------------------------------------------------ TMA producer
   if (warp_idx == 0) {
     if (lane == 0) {
-      uint32_t s = 0, ph = 0;
+      uint32_t s = prod_s, ph = prod_ph;
       bool ok = true;
-      // W is read exactly once: keep it from displacing X (re-read by every CTA) in L2.
-      const uint64_t stream_once = ptx::l2_policy_evict_first();
-      const uint64_t keep = ptx::l2_policy_evict_last();
-      uint64_t u = u_begin;
-      uint32_t t = (uint32_t)(u_begin / p.k_blocks);
-      uint32_t kb = (uint32_t)(u_begin - (uint64_t)t * p.k_blocks);
+      uint64_t u = prod_u;
+      uint32_t t = prod_t;
+      uint32_t kb = prod_kb;
       while (u < u_end && ok) {
         const uint64_t left = u_end - u;
         const uint32_t group = left < p.burst ? (uint32_t)left : p.burst;
@@ -277,70 +301,78 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                      make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
                                  __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3])));
           }
-          __threadfence();
+          if (!p.split_reduce) __threadfence();
         }
-        ptx::named_bar_sync(1, 128);
-        if (epi_tid == 0) {
-          bool last = false;
-          if (!dead && *abort_ptr == 0u) {
-            const uint32_t seen = atomicAdd(p.counters + t, 1u);
-            last = (seen == contribs - 1u);
-            if (last) p.counters[t] = 0u;  // everybody has arrived: leave it clean for the next launch
+        if (p.split_reduce) {
+          // The sum over contributors is the follow-up kernel's job (all SMs share it; a
+          // single finishing CTA would have to pull every contributor's tile through one SM).
+          is_last = false;
+        } else {
+          ptx::named_bar_sync(1, 128);
+          if (epi_tid == 0) {
+            bool last = false;
+            if (!dead && *abort_ptr == 0u) {
+              const uint32_t seen = atomicAdd(p.counters + t, 1u);
+              last = (seen == contribs - 1u);
+              if (last) p.counters[t] = 0u;  // everybody has arrived: leave it clean for the next launch
+            }
+            *last_ptr = last ? 1u : 0u;
           }
-          *last_ptr = last ? 1u : 0u;
+          ptx::named_bar_sync(1, 128);
+          is_last = !dead && (*last_ptr != 0u);
+          if (is_last) __threadfence();
         }
-        ptx::named_bar_sync(1, 128);
-        is_last = !dead && (*last_ptr != 0u);
-        if (is_last) __threadfence();
       }
       if (is_last) {
         // 2. sum the contributors in their fixed order (this CTA's part comes from TMEM), scale,
-        //    round to bf16 and store C[m][n]. Up to 64 values of m at a time, contributor
-        //    outermost, so that one contributor's 16 loads are in flight together.
+        //    round to bf16 and store C[m][n]. Sixteen values of m at a time; the partials of up
+        //    to eight contributors (32 loads of 16 bytes per thread) are requested before any is
+        //    used, so a tile shared by many CTAs costs one or two trips to L2, not one per CTA.
         const float4* slot0 = reinterpret_cast<const float4*>(
                                   p.partials + (size_t)t * p.max_contrib * ((size_t)p.m_pad * 128u)) +
                               q * 32u + lane;
         const size_t slot_quads = (size_t)p.m_pad * 32u;  // float4 words per slot
-        for (uint32_t mb = 0; mb < p.m_pad; mb += 64u) {
-          const uint32_t nq = (p.m_pad - mb) >= 64u ? 16u : (p.m_pad - mb) / 4u;  // quads in this batch
-          float acc[64];
+        for (uint32_t m0 = 0; m0 < p.m_pad; m0 += 16u) {
+          uint32_t own[16];
+          ptx::tmem_ld_32x32b_x16(taddr + m0, own);
+          ptx::tmem_ld_wait();
+          float acc[16];
 #pragma unroll
-          for (uint32_t i = 0; i < 64; ++i) acc[i] = 0.0f;
-          for (uint32_t j = 0; j < contribs; ++j) {
-            float x[64];
-            if (j == my_j) {
+          for (uint32_t i = 0; i < 16; ++i) acc[i] = 0.0f;
+          for (uint32_t j0 = 0; j0 < contribs; j0 += 8u) {
+            float4 x[8][4];
 #pragma unroll
-              for (uint32_t c16 = 0; c16 < 4; ++c16) {
-                if (c16 * 4u < nq) {
-                  uint32_t v[16];
-                  ptx::tmem_ld_32x32b_x16(taddr + mb + c16 * 16u, v);
-                  ptx::tmem_ld_wait();
+            for (uint32_t jj = 0; jj < 8; ++jj) {
+              const uint32_t j = j0 + jj;
+              if (j < contribs && j != my_j) {
+                const float4* other = slot0 + (size_t)j * slot_quads + (size_t)(m0 / 4u) * 128u;
 #pragma unroll
-                  for (uint32_t i = 0; i < 16; ++i) x[c16 * 16u + i] = __uint_as_float(v[i]);
-                }
-              }
-            } else {
-              const float4* other = slot0 + (size_t)j * slot_quads + (size_t)(mb / 4u) * 128u;
-#pragma unroll
-              for (uint32_t g = 0; g < 16; ++g) {
-                if (g < nq) {
-                  const float4 w4 = __ldcg(other + (size_t)g * 128u);
-                  x[4 * g] = w4.x;
-                  x[4 * g + 1] = w4.y;
-                  x[4 * g + 2] = w4.z;
-                  x[4 * g + 3] = w4.w;
-                }
+                for (uint32_t g = 0; g < 4; ++g) x[jj][g] = __ldcg(other + (size_t)g * 128u);
               }
             }
 #pragma unroll
-            for (uint32_t i = 0; i < 64; ++i)
-              if (i < nq * 4u) acc[i] = (j == 0u) ? x[i] : acc[i] + x[i];
+            for (uint32_t jj = 0; jj < 8; ++jj) {
+              const uint32_t j = j0 + jj;
+              if (j < contribs) {
+                const bool mine = (j == my_j);
+#pragma unroll
+                for (uint32_t g = 0; g < 4; ++g) {
+                  const float a0 = mine ? __uint_as_float(own[4 * g]) : x[jj][g].x;
+                  const float a1 = mine ? __uint_as_float(own[4 * g + 1]) : x[jj][g].y;
+                  const float a2 = mine ? __uint_as_float(own[4 * g + 2]) : x[jj][g].z;
+                  const float a3 = mine ? __uint_as_float(own[4 * g + 3]) : x[jj][g].w;
+                  acc[4 * g] = (j == 0u) ? a0 : acc[4 * g] + a0;
+                  acc[4 * g + 1] = (j == 0u) ? a1 : acc[4 * g + 1] + a1;
+                  acc[4 * g + 2] = (j == 0u) ? a2 : acc[4 * g + 2] + a2;
+                  acc[4 * g + 3] = (j == 0u) ? a3 : acc[4 * g + 3] + a3;
+                }
+              }
+            }
           }
           if (n < p.N) {
 #pragma unroll
-            for (uint32_t i = 0; i < 64; ++i)
-              if (i < nq * 4u && mb + i < p.M)
-                p.C[(size_t)(mb + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
+            for (uint32_t i = 0; i < 16; ++i)
+              if (m0 + i < p.M) p.C[(size_t)(m0 + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
           }
         }
       }
@@ -366,6 +398,59 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (warp_idx == 1) ptx::tmem_dealloc<1>(tmem_base, kSkTmemCols);
+}
+
+// Second half of a split-reduce launch: sums the partial tiles that gemm_streamk_kernel
+// published, in contributor order (so the result does not depend on timing), scales, rounds to
+// bf16 and writes C. One block per (tile of 128 columns of C, 16 rows of C); thread = column.
+// Tiles that one CTA computed whole were written by that CTA and are skipped.
+__global__ void __launch_bounds__(128)
+streamk_reduce_kernel(const StreamKParams p, const uint32_t parts) {
+  const uint32_t chunks = p.m_pad / 16u;
+  const uint32_t t = blockIdx.x / chunks;
+  const uint32_t m0 = (blockIdx.x - t * chunks) * 16u;
+  const uint64_t tile_u0 = (uint64_t)t * p.k_blocks;
+  const uint32_t first_cta = streamk_owner(tile_u0, p.units, parts);
+  const uint32_t contribs = streamk_owner(tile_u0 + p.k_blocks - 1, p.units, parts) - first_cta + 1u;
+  if (contribs < 2u) return;
+  ptx::grid_dependency_wait();  // the partial tiles are complete and visible from here on
+  const uint32_t n = t * kSkTileRows + threadIdx.x;
+  const float4* slot0 = reinterpret_cast<const float4*>(
+                            p.partials + (size_t)t * p.max_contrib * ((size_t)p.m_pad * 128u)) +
+                        (size_t)(m0 / 4u) * 128u + threadIdx.x;
+  const size_t slot_quads = (size_t)p.m_pad * 32u;
+  float acc[16];
+#pragma unroll
+  for (uint32_t i = 0; i < 16; ++i) acc[i] = 0.0f;
+  for (uint32_t j0 = 0; j0 < contribs; j0 += 8u) {
+    float4 x[8][4];
+#pragma unroll
+    for (uint32_t jj = 0; jj < 8; ++jj) {
+      if (j0 + jj < contribs) {
+#pragma unroll
+        for (uint32_t g = 0; g < 4; ++g)
+          x[jj][g] = __ldcg(slot0 + (size_t)(j0 + jj) * slot_quads + (size_t)g * 128u);
+      }
+    }
+#pragma unroll
+    for (uint32_t jj = 0; jj < 8; ++jj) {
+      if (j0 + jj < contribs) {
+        const bool first = (j0 + jj == 0u);
+#pragma unroll
+        for (uint32_t g = 0; g < 4; ++g) {
+          acc[4 * g] = first ? x[jj][g].x : acc[4 * g] + x[jj][g].x;
+          acc[4 * g + 1] = first ? x[jj][g].y : acc[4 * g + 1] + x[jj][g].y;
+          acc[4 * g + 2] = first ? x[jj][g].z : acc[4 * g + 2] + x[jj][g].z;
+          acc[4 * g + 3] = first ? x[jj][g].w : acc[4 * g + 3] + x[jj][g].w;
+        }
+      }
+    }
+  }
+  if (n < p.N) {
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i)
+      if (m0 + i < p.M) p.C[(size_t)(m0 + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
+  }
 }
 
 }  // namespace patina

@@ -191,6 +191,19 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may become resident
+// while its predecessor still runs: the predecessor's blocks announce that with
+// launch_dependents (or by exiting), and the dependent kernel blocks in grid_dependency_wait
+// until the predecessor has completed and its memory writes are visible. Without the launch
+// attribute both instructions do nothing.
+__device__ __forceinline__ void launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ----------------------------------------------------------------- tcgen05
 template <int kCtaGroup>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t cols) {

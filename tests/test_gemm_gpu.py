@@ -221,7 +221,8 @@ def test_streamk_matches_oracle_and_large_tile_kernel(ctx, oracle_mod, M, N, K):
 
 def test_streamk_decode_shapes_full_size(ctx, oracle_mod):
     """The decode-shaped configurations at full size (N=28672, K=8192, M in {16, 64, 128}):
-    one launch each (stream-K for M = 16, the large-tile kernel above that); 128 sampled columns of C against the
+    one launch each, or two where the stream-K kernel hands the sum over contributors to its
+    follow-up kernel; 128 sampled columns of C against the
     oracle (computed as rows of B x A^T), and fp8 inputs on the same path."""
     from patina_b200 import inputs
     N, K = 28672, 8192
@@ -232,7 +233,7 @@ def test_streamk_decode_shapes_full_size(ctx, oracle_mod):
         before = ctx.launch_count
         out = ctx.gemm_tn(A.cuda(), B.cuda())
         ctx.status()
-        assert ctx.launch_count == before + 1
+        assert 1 <= ctx.launch_count - before <= 2
         ref_t = oracle_mod.ref_gemm_tn(widen(oracle_mod, B), widen(oracle_mod, A), rows=cols)  # [cols, M]
         want = oracle_mod.scale_round_bf16(ref_t.T.copy(), 1.0)
         check_norm(oracle_mod, out[:, torch.from_numpy(cols).cuda()], want, f"decode M={M}")

@@ -264,18 +264,48 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, graph_steps=0):
+        """Times `steps` calls of fn. graph_steps = G > 0: G consecutive steps are captured once
+        into a CUDA graph and the timed region replays it steps / G times, so that a kernel of
+        a few tens of microseconds is timed at the rate the GPU can run it, not at the rate the
+        Python interpreter can call it. Returns (total ms, per-step ms list)."""
         for i in range(warmup):
             fn(i)
         barrier()
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-        evs[0].record()
-        for i in range(steps):
-            fn(i)
-            evs[i + 1].record()
-        barrier()
-        total_ms = evs[0].elapsed_time(evs[-1])
-        per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+        count0 = ctx.launch_count
+        if graph_steps > 0:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(graph_steps):
+                        fn(i)
+                captured = ctx.launch_count - count0   # the library counts what it enqueues
+                graph.replay()          # untimed: instantiation and upload
+                side.synchronize()
+                barrier()
+                replays = steps // graph_steps
+                evs = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+                evs[0].record()
+                for r in range(replays):
+                    graph.replay()
+                    evs[r + 1].record()
+                side.synchronize()
+            barrier()
+            total_ms = evs[0].elapsed_time(evs[-1])
+            per = [evs[r].elapsed_time(evs[r + 1]) / graph_steps for r in range(replays)]
+            timed.launches = captured * replays
+        else:
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            evs[0].record()
+            for i in range(steps):
+                fn(i)
+                evs[i + 1].record()
+            barrier()
+            total_ms = evs[0].elapsed_time(evs[-1])
+            per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+            timed.launches = ctx.launch_count - count0
         if world > 1:
             t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -288,7 +318,6 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    launches0 = ctx.launch_count
     if args.fused_epilogue and not fp8:
         mode = args.fused_epilogue
         bias_d = torch.randn(N, generator=torch.Generator().manual_seed(1)).cuda() if "bias" in mode else None
@@ -298,8 +327,14 @@ def run_ours(args):
                                                 residual=res_d, activation=act)
     else:
         step = lambda i: ctx.gemm_tn(dA, dBs[i % len(dBs)], out=dC, alpha=alpha)
-    total_ms, per = timed(step, args.steps, args.warmup)
-    launches = ctx.launch_count - launches0 - args.warmup
+    # A step shorter than ~150 us is launch-bound from Python: replay it from a CUDA graph.
+    est_us = max(flops_per_gpu / 1.4e15, bytes_per_gpu / 6.0e12) * 1e6
+    graph_steps = 0
+    if args.graph != 0 and (args.graph > 0 or est_us < 150.0):
+        want = args.graph if args.graph > 0 else 50
+        graph_steps = max(g for g in range(1, min(want, args.steps) + 1) if args.steps % g == 0)
+    total_ms, per = timed(step, args.steps, args.warmup, graph_steps)
+    launches = timed.launches
     clocks = sampler.stop() if rank == 0 else None
     ctx.status()
     ms_per_step = total_ms / args.steps
@@ -394,6 +429,8 @@ def run_ours(args):
                    "l2": (f"{wl['rotate']} weight buffers of {N * K * ebytes / 1e6:.0f} MB in rotation"
                           if wl["rotate"] > 1 else
                           f"inputs ({(M * K + N * K) * ebytes / 1e6:.0f} MB) vs L2 126 MB; no flush between steps"),
+                   "launch": (f"CUDA graph of {graph_steps} steps, replayed {args.steps // graph_steps} times"
+                              if graph_steps else "one library call per step"),
                    "kernel": "library's automatic choice (tcgen05 large-tile or stream-K kernel)" +
                              (f"; fused epilogue: {args.fused_epilogue}" if args.fused_epilogue and not fp8 else "")},
         "per_gpu_tflops": round(value / world, 2),
@@ -463,6 +500,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bf16_tn_8192")
+    ap.add_argument("--graph", type=int, default=-1,
+                    help="steps per captured CUDA graph; 0 = one library call per step; "
+                         "-1 (default) = graph only when a step is estimated under 150 us")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--fused-allgather", action="store_true",

@@ -67,6 +67,12 @@ for _m in (16, 64, 128):
         "N split over the GPUs; 3 weight buffers in rotation (each larger than L2)",
         bound="hbm", scaling="strong", rotate=3)
 
+for _m in (16, 64, 128):
+    WORKLOADS[f"skinny_m{_m}_n3584"] = _wl(
+        _m, 3584, 8192, "llm", f"one GPU's share of the decode-shaped GEMM split over 8 GPUs: M={_m}, "
+        "N=28672/8=3584, K=8192 (memory-bound, 59 MB of weights); 12 weight buffers in rotation",
+        bound="hbm", scaling="strong", rotate=12)
+
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture;
 # see profiles/. None until a capture of that workload exists.
 NCU_DRAM_TRAFFIC_BYTES = {

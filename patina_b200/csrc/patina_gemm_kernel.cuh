@@ -361,15 +361,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * T::kAccCols + ms * BN;
       constexpr uint32_t kFp32PerChunk = T::kChunkCols;            // accumulator words per chunk
       constexpr uint32_t kPieces = T::kRowBytes / 16u;             // 16-byte pieces per staged row
-#pragma unroll 1
-      for (uint32_t ch = 0; ch < T::kChunks; ++ch) {
-        uint32_t v[kFp32PerChunk];
-        const uint32_t ch_col = (T::kOverlapLastChunk && ch == T::kChunks - 1)
-                                    ? (uint32_t)BN - T::kChunkCols : ch * T::kChunkCols;
+      // Chunk ch + 1 is requested from TMEM before chunk ch is converted and stored, so the
+      // load's latency (about 170 cycles measured) hides behind the previous chunk's work.
+      auto chunk_col = [](uint32_t ch) -> uint32_t {
+        return (T::kOverlapLastChunk && ch == T::kChunks - 1) ? (uint32_t)BN - T::kChunkCols
+                                                               : ch * T::kChunkCols;
+      };
+      auto request = [&](uint32_t ch, uint32_t* v) {
+        const uint32_t c0 = chunk_col(ch);
 #pragma unroll
-        for (uint32_t h = 0; h < kFp32PerChunk; h += 32u)
-          ptx::tmem_ld_32x32b_x32(taddr + ch_col + h, &v[h]);
-        ptx::tmem_ld_wait();
+        for (uint32_t h = 0; h < kFp32PerChunk; h += 32u) ptx::tmem_ld_32x32b_x32(taddr + c0 + h, &v[h]);
+      };
+      auto finish = [&](uint32_t ch, uint32_t* v) {
+        const uint32_t ch_col = chunk_col(ch);
         if (ch == T::kChunks - 1) {
           // Accumulator fully read: hand the TMEM buffer back to the MMA issuer.
           ptx::tc_fence_before_sync();
@@ -464,6 +468,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           ptx::tma_store_commit();
         }
         sbuf ^= 1u;
+      };
+      uint32_t va[kFp32PerChunk], vb[kFp32PerChunk];
+      request(0, va);
+#pragma unroll 1
+      for (uint32_t ch = 0; ch < T::kChunks; ch += 2u) {
+        ptx::tmem_ld_wait();
+        if (ch + 1u < T::kChunks) request(ch + 1u, vb);
+        finish(ch, va);
+        if (ch + 1u < T::kChunks) {
+          ptx::tmem_ld_wait();
+          if (ch + 2u < T::kChunks) request(ch + 2u, va);
+          finish(ch + 1u, vb);
+        }
       }
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();

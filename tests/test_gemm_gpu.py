@@ -281,6 +281,61 @@ def test_fused_epilogue(ctx, oracle_mod, activation):
                    "in-place accumulate")
 
 
+def test_stream_k_reduce_modes_agree(ctx, oracle_mod):
+    """The sum over the CTAs that share a tile can run inside the stream-K kernel (the last CTA
+    to reach a tile adds the others' parts) or in the follow-up kernel; both add in the same
+    contributor order, so they must agree bit for bit, for skinny and for wide X."""
+    from patina_b200 import inputs, GemmConfig
+    for M, N, K in [(16, 1024, 4096), (40, 904, 2120), (128, 1536, 8192)]:
+        A, B = inputs.make_operands("llm", M, N, K, seed=M + N)
+        dA, dB = A.cuda(), B.cuda()
+        follow_up = ctx.gemm_tn(dA, dB, config=GemmConfig(0, 0, 0, 0, 0, 0, 2))
+        in_kernel = ctx.gemm_tn(dA, dB, config=GemmConfig(0, 0, 0, 0, 0, 0, 3))
+        ctx.status()
+        assert torch.equal(follow_up, in_kernel), (M, N, K)
+        check_norm(oracle_mod, follow_up, expect_bf16(oracle_mod, A, B), f"stream-K {M}x{N}x{K}")
+
+
+def test_calls_can_be_captured_in_a_cuda_graph(ctx, oracle_mod):
+    """The calls only enqueue work, so after one eager call each (first calls set function
+    attributes and grow scratch memory) they can be captured into a CUDA graph; replaying the
+    graph on new operand values must give what eager calls give. Covers the large-tile kernel,
+    the stream-K kernel alone and the stream-K kernel with its dependent reduce kernel."""
+    from patina_b200 import inputs
+    shapes = [(512, 520, 264), (16, 1024, 8192), (96, 1024, 8192)]   # the last two take stream-K
+    ops, outs = [], []
+    for i, (M, N, K) in enumerate(shapes):
+        A, B = inputs.make_operands("llm", M, N, K, seed=50 + i)
+        ops.append((A.cuda(), B.cuda()))
+        outs.append(torch.empty((M, (N + 7) // 8 * 8), dtype=torch.bfloat16, device="cuda")[:, :N])
+    for (dA, dB), out in zip(ops, outs):
+        ctx.gemm_tn(dA, dB, out=out)           # eager first call
+    ctx.status()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for (dA, dB), out in zip(ops, outs):
+                ctx.gemm_tn(dA, dB, out=out)
+        for round_ in range(2):
+            for i, (dA, dB) in enumerate(ops):  # new values in the captured buffers
+                A2, B2 = inputs.make_operands("llm", *shapes[i], seed=70 + 10 * round_ + i)
+                dA.copy_(A2.cuda()); dB.copy_(B2.cuda())
+            for out in outs:
+                out.fill_(float("nan"))
+            graph.replay()
+            side.synchronize()
+            replayed = [o.clone() for o in outs]
+            for (dA, dB), out, got in zip(ops, outs, replayed):
+                eager = ctx.gemm_tn(dA, dB)
+                ctx.status()
+                assert torch.equal(got, eager)
+    torch.cuda.current_stream().wait_stream(side)
+    A2, B2 = inputs.make_operands("llm", *shapes[2], seed=70 + 10 + 2)
+    check_norm(oracle_mod, replayed[2], expect_bf16(oracle_mod, A2, B2), "graph replay vs oracle")
+
+
 def test_scatter_to_several_destinations_on_one_gpu(ctx, oracle_mod):
     """patina_gemm_bf16_tn_scatter with three destinations that all live on this GPU: each must
     receive exactly what the single-destination call produces (on a multi-GPU node the extra

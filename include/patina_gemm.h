@@ -149,6 +149,25 @@ int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t l
                                 int64_t ldb, void* const* C_dests, int n_dests, int64_t ldc,
                                 int64_t M, int64_t N, int64_t K, float alpha, void* stream);
 
+/* Grouped GEMM (no counterpart in the reference, whose kernel runs one 128 x 128 problem; this
+ * is its runtime `k_tiles` parameter, crates/patina/tests/golden/v2_gemm_pipelined.ptx:29, taken
+ * one step further: the tile list itself is a runtime value). One launch computes
+ *     C_g[M_g, N] = alpha * A_g[M_g, K] * B_g[N, K]^T     for g = 0 .. n_groups-1
+ * for groups that share N and K, e.g. the experts of a mixture-of-experts layer:
+ *   A  [total_rows, lda]   the groups' rows one after another (bf16, K-contiguous)
+ *   B  [n_groups * N, ldb] group g's weights are rows g*N .. (g+1)*N-1
+ *   C  [total_rows, ldc]   rows in the same order as A
+ *   group_rows             DEVICE array of n_groups int32: M_g (negative counts as 0); the call
+ *                          never reads it on the host, so it may be the output of a routing
+ *                          kernel that is still running on `stream`
+ * Rows of C from sum(M_g) up to total_rows are left untouched; if the sum exceeds total_rows the
+ * excess is dropped. n_groups <= 128 per call. `config` may be NULL; only cta_group, m_sub,
+ * group_m and max_ctas are looked at (tile height 128 * cta_group * m_sub, width 256). */
+int patina_gemm_bf16_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                int64_t ldb, void* C, int64_t ldc, const int32_t* group_rows,
+                                int n_groups, int64_t total_rows, int64_t N, int64_t K, float alpha,
+                                const PatinaGemmConfig* config, void* stream);
+
 /* Buffers for the scatter above (no counterpart in the reference). peer_alloc gives device
  * memory of this context's GPU plus a 64-byte handle that another PROCESS on the node passes
  * to peer_open (with its own context) to get a pointer its GPU can write through NVLink.

@@ -86,6 +86,19 @@ const KernelEntry kKernels[] = {
 };
 constexpr int kNumKernels = sizeof(kKernels) / sizeof(kKernels[0]);
 
+// Grouped launches (bf16 -> bf16): the same kernel, compiled with the group tables.
+#define PATINA_GROUPED(G, MS, BN, S)                                                          \
+  { G, MS, BN, S, kBF16, kOutBF16, gemm_tn_kernel<G, MS, BN, S, kBF16, kOutBF16, false, true>, \
+    nullptr, GemmTraits<G, MS, BN, S, kBF16, kOutBF16>::kSmemBytes + kGroupTableBytes }
+const KernelEntry kGroupedKernels[] = {
+    PATINA_GROUPED(2, 2, 256, 4),  // 512 x 256 per pair: groups of many hundred rows
+    PATINA_GROUPED(2, 1, 256, 6),  // 256 x 256 per pair
+    PATINA_GROUPED(1, 1, 256, 4),  // 128 x 256: small groups lose least to their ragged last block
+};
+constexpr int kNumGroupedKernels = sizeof(kGroupedKernels) / sizeof(kGroupedKernels[0]);
+static_assert(GemmTraits<2, 2, 256, 4, kBF16, kOutBF16>::kSmemBytes + kGroupTableBytes <= kMaxDynSmem,
+              "group tables do not fit behind the largest kernel's shared memory");
+
 bool type_pair_supported(int in_type, int out_type) {
   for (int i = 0; i < kNumKernels; ++i)
     if (kKernels[i].in_type == in_type && kKernels[i].out_type == out_type) return true;
@@ -272,6 +285,8 @@ struct PatinaGemmContext {
   EncodeTiledFn encode = nullptr;
   std::vector<std::pair<TensorMapKey, CUtensorMap>> tmaps;  // small most-recent-first cache
   bool smem_attr_set[kNumKernels] = {};
+  bool grouped_attr_set[kNumGroupedKernels] = {};
+  int grouped_max_clusters[kNumGroupedKernels] = {};
   int max_clusters[kNumKernels] = {};  // co-resident clusters per kernel (pairs only)
   // scratch of the stream-K path: fp32 partial tiles and per-tile arrival counters
   float* d_sk_partials = nullptr;
@@ -641,6 +656,141 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   return PATINA_GEMM_OK;
 }
 
+// One launch for n_groups GEMMs that share N and K: A and C hold the groups' rows one after
+// another, B one [N, K] block per group, the row counts live in device memory.
+int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B, int64_t ldb,
+                   void* C, int64_t ldc, const int32_t* group_rows, int n_groups, int64_t total_rows,
+                   int64_t N, int64_t K, float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  if (n_groups < 0 || n_groups > (int)kMaxGroups)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
+                     fmt("n_groups=%d: a grouped launch takes 0..%u groups", n_groups, kMaxGroups));
+  if (n_groups > 0 && !group_rows)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "group_rows is null");
+  if ((int64_t)n_groups * N > 0x7fffffffLL)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "n_groups * N exceeds 2^31-1");
+  std::string err;
+  // A is [total_rows, K]; B is [n_groups * N, K]; C is [total_rows, N]
+  int rc = validate_args(kBF16, kOutBF16, A, lda, B, ldb, C, ldc, total_rows, N, K, &err);
+  if (rc != PATINA_GEMM_OK) return set_error(ctx, rc, err);
+  if (total_rows == 0 || N == 0 || n_groups == 0) return PATINA_GEMM_OK;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok) return set_error(ctx, PATINA_GEMM_ERR_CUDA, "cudaSetDevice failed");
+  if (K == 0) {
+    cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 2, 0, (size_t)N * 2, (size_t)total_rows, stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemset2DAsync");
+    return PATINA_GEMM_OK;
+  }
+  // The row counts are on the device, so the tile shape follows the average group: a tall tile
+  // wastes up to a tile of rows at every group's end.
+  const int64_t avg = total_rows / n_groups;
+  int want_group = avg >= 1024 ? 2 : avg >= 256 ? 2 : 1;
+  int want_msub = avg >= 1024 ? 2 : 1;
+  if (cfg && cfg->cta_group != 0) want_group = cfg->cta_group;
+  if (cfg && cfg->m_sub != 0) want_msub = cfg->m_sub;
+  if (ctx->num_sms < 2) want_group = 1;
+  const KernelEntry* k = nullptr;
+  int ki = -1;
+  for (int i = 0; i < kNumGroupedKernels; ++i)
+    if (kGroupedKernels[i].cta_group == want_group && kGroupedKernels[i].m_sub == want_msub) {
+      k = &kGroupedKernels[i];
+      ki = i;
+    }
+  if (!k)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
+                     fmt("no grouped kernel for cta_group=%d m_sub=%d", want_group, want_msub));
+
+  const uint32_t kelems = kBlockKBytes / 2;
+  const uint32_t tile_m = 128u * k->cta_group * k->m_sub;
+  const uint32_t tiles_n = ceil_div(N, k->block_n);
+  // every group may end with one partly filled row block
+  const uint64_t max_tiles = ((uint64_t)(total_rows / tile_m) + (uint64_t)n_groups) * tiles_n;
+  CUtensorMap tm_a, tm_b;
+  CStoreMaps tm_c;
+  rc = get_tensor_map(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)K,
+                      (uint64_t)lda, kCtaRows, kelems, &tm_a);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)n_groups * (uint64_t)N,
+                      (uint64_t)K, (uint64_t)ldb, (uint32_t)(k->block_n / k->cta_group), kelems, &tm_b);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)N,
+                      (uint64_t)ldc, kStoreBoxRows, staging_row_bytes((uint32_t)k->m_sub, 2) / 2,
+                      &tm_c.map[0]);
+  if (rc != PATINA_GEMM_OK) return rc;
+  for (int d = 1; d < kMaxDests; ++d) tm_c.map[d] = tm_c.map[0];
+
+  if (!ctx->grouped_attr_set[ki]) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k->fn),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->smem_bytes);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(smem, grouped)");
+    ctx->grouped_attr_set[ki] = true;
+  }
+  uint32_t slots = (uint32_t)(ctx->num_sms / k->cta_group);
+  if (k->cta_group > 1) {
+    if (ctx->grouped_max_clusters[ki] == 0) {
+      cudaLaunchConfig_t qc{};
+      qc.gridDim = dim3((unsigned)slots * k->cta_group, 1, 1);
+      qc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
+      qc.dynamicSmemBytes = k->smem_bytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = (unsigned)k->cta_group;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      qc.attrs = qa;
+      qc.numAttrs = 1;
+      int n = 0;
+      cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(k->fn), &qc);
+      if (qe != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = (int)slots;
+      }
+      ctx->grouped_max_clusters[ki] = n;
+    }
+    if ((uint32_t)ctx->grouped_max_clusters[ki] < slots) slots = (uint32_t)ctx->grouped_max_clusters[ki];
+  }
+  if (cfg && cfg->max_ctas > 0 && (uint32_t)(cfg->max_ctas / k->cta_group) < slots)
+    slots = (uint32_t)(cfg->max_ctas / k->cta_group);
+  if (slots == 0) slots = 1;
+  const uint32_t clusters = max_tiles < slots ? (uint32_t)max_tiles : slots;
+
+  GemmParams p{};
+  p.M = (uint32_t)total_rows;
+  p.N = (uint32_t)N;
+  p.K = (uint32_t)K;
+  p.tiles_m = 0;
+  p.tiles_n = tiles_n;
+  p.num_tiles = 0;  // the kernel derives it from the group sizes
+  p.k_blocks = ceil_div(K, kelems);
+  p.group_m = (cfg && cfg->group_m > 0) ? (uint32_t)cfg->group_m : 8u;
+  p.alpha = alpha;
+  p.n_dests = 1;
+  p.group_rows = group_rows;
+  p.n_groups = (uint32_t)n_groups;
+  p.c_base = C;
+  p.ldc = ldc;
+  p.status = ctx->d_status;
+  p.wait_limit_ns = ctx->wait_limit_ns;
+
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(clusters * k->cta_group, 1, 1);
+  lc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
+  lc.dynamicSmemBytes = k->smem_bytes;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)k->cta_group;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = (k->cta_group > 1) ? 1 : 0;
+  drain_stale_error("grouped launch");
+  cudaError_t e = cudaLaunchKernelEx(&lc, k->fn, tm_a, tm_b, tm_c, p);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaLaunchKernelEx(grouped)");
+  ctx->launches += 1;
+  return PATINA_GEMM_OK;
+}
+
 int grow(PatinaGemmContext* ctx, void** p, size_t* cap, size_t need) {
   if (*cap >= need) return PATINA_GEMM_OK;
   if (*p) cudaFree(*p);
@@ -830,6 +980,14 @@ int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t l
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "n_dests must be 1..8 and C_dests non-null");
   return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C_dests[0], ldc, M, N, K, alpha, nullptr,
                      static_cast<cudaStream_t>(stream), C_dests + 1, n_dests - 1);
+}
+
+int patina_gemm_bf16_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                int64_t ldb, void* C, int64_t ldc, const int32_t* group_rows,
+                                int n_groups, int64_t total_rows, int64_t N, int64_t K, float alpha,
+                                const PatinaGemmConfig* config, void* stream) {
+  return launch_grouped(ctx, A, lda, B, ldb, C, ldc, group_rows, n_groups, total_rows, N, K, alpha,
+                        config, static_cast<cudaStream_t>(stream));
 }
 
 // ---- buffers that other processes on the node can write ------------------------------------

@@ -58,9 +58,18 @@ struct GemmParams {
   float beta;
   uint32_t activation;     // Activation
   uint32_t n_dests;        // destinations of C (1..kMaxDests)
+  // grouped launch (kernels instantiated with kGrouped): A and C hold the groups' rows one
+  // after another, B holds one [N, K] block per group; M above is the total row count
+  const int32_t* group_rows;  // device array, rows of A and C per group
+  uint32_t n_groups;          // <= kMaxGroups
+  void* c_base;               // C itself, for the rows of a box that straddles a group's end
+  int64_t ldc;
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
 };
+
+constexpr uint32_t kMaxGroups = 128;
+constexpr uint32_t kGroupTableBytes = 2u * (kMaxGroups + 1u) * 4u + 8u;  // row and tile prefix sums
 
 enum Activation : uint32_t { kActNone = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
 
@@ -179,7 +188,8 @@ struct GemmTraits {
   static_assert((2 * kStages + 4) * 8 + 8 <= kBarrierRegionBytes, "barrier region too small");
 };
 
-template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused = false>
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused = false,
+          bool kGrouped = false>
 __global__ void __launch_bounds__(64 + 128 * kMSub, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CStoreMaps tm_c, const GemmParams p) {
@@ -189,6 +199,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   constexpr uint32_t kEpiWarps = T::kEpiWarps;
   // The fused epilogue may read C itself as the residual, so no column may be produced twice.
   static_assert(!(kFused && T::kOverlapLastChunk), "fused epilogue needs whole store boxes");
+  static_assert(!(kFused && kGrouped), "the grouped kernel has the plain epilogue only");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -201,6 +212,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const uint32_t tempty_bar = tfull_bar + 16u;         // [2]
   const uint32_t tmem_slot = tempty_bar + 16u;         // u32
   const uint32_t abort_slot = tmem_slot + 4u;          // u32
+  // grouped launch: prefix sums over the groups, [n_groups + 1] each, behind the barrier region
+  uint32_t* const grp_row_begin = reinterpret_cast<uint32_t*>(
+      smem_raw + (bars + kBarrierRegionBytes - ptx::smem_u32(smem_raw)));
+  uint32_t* const grp_tile_begin = grp_row_begin + (kMaxGroups + 1u);
   uint8_t* const smem_generic = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   volatile uint32_t* const tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
       smem_generic + (tmem_slot - smem_base));
@@ -237,6 +252,28 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     *abort_ptr = 0u;
     ptx::fence_mbar_init();
   }
+  if constexpr (kGrouped) {
+    // Every CTA derives the same tables from the device-resident group sizes: first row and
+    // first tile of every group (a group's tiles: its row blocks x all column blocks).
+    for (uint32_t g = threadIdx.x; g < p.n_groups; g += blockDim.x) {
+      const int32_t r = __ldg(p.group_rows + g);
+      grp_row_begin[g + 1u] = r > 0 ? (uint32_t)r : 0u;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t row = 0, tile = 0;
+      grp_row_begin[0] = 0u;
+      grp_tile_begin[0] = 0u;
+      for (uint32_t g = 0; g < p.n_groups; ++g) {
+        uint32_t r = grp_row_begin[g + 1u];
+        if (r > p.M - row) r = p.M - row;  // never past the end of A and C
+        row += r;
+        tile += ((r + T::kTileM - 1u) / T::kTileM) * p.tiles_n;
+        grp_row_begin[g + 1u] = row;
+        grp_tile_begin[g + 1u] = tile;
+      }
+    }
+  }
   if (warp_idx == 1) {
     ptx::tmem_alloc<kCtaGroup>(tmem_slot, T::kTmemCols);
     ptx::tmem_relinquish<kCtaGroup>();
@@ -250,17 +287,52 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  const uint32_t num_tiles = kGrouped ? grp_tile_begin[p.n_groups] : p.num_tiles;
+  // Where tile t lies. Plain launch: one problem. Grouped launch: the group is found by moving
+  // a cursor forward (tile indices only grow), rows are offset by the group's first row and
+  // the rows of B by the group's block of N rows.
+  struct TileSpot {
+    uint32_t m, n;        // block coordinates inside the (group's) problem
+    uint32_t row_base;    // first row of the problem in A and C
+    uint32_t row_end;     // one past its last row
+    uint32_t b_row_base;  // first row of the problem in B
+  };
+  auto locate = [&](uint32_t t, uint32_t& g) -> TileSpot {
+    TileSpot sp;
+    if constexpr (kGrouped) {
+      while (g + 1u < p.n_groups && t >= grp_tile_begin[g + 1u]) ++g;
+      const uint32_t rows = grp_row_begin[g + 1u] - grp_row_begin[g];
+      const TileCoord c = tile_coord(t - grp_tile_begin[g], (rows + T::kTileM - 1u) / T::kTileM,
+                                     p.tiles_n, p.group_m);
+      sp.m = c.m;
+      sp.n = c.n;
+      sp.row_base = grp_row_begin[g];
+      sp.row_end = grp_row_begin[g + 1u];
+      sp.b_row_base = g * p.N;
+    } else {
+      const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+      sp.m = c.m;
+      sp.n = c.n;
+      sp.row_base = 0u;
+      sp.row_end = p.M;
+      sp.b_row_base = 0u;
+    }
+    return sp;
+  };
 
   // ------------------------------------------------------------ TMA producer
   if (warp_idx == 0) {
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
-      for (uint32_t t = cluster_id; t < p.num_tiles; t += num_clusters) {
-        const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
-        // Sub-tile s of this CTA covers rows a_row + s * (128 * kCtaGroup).
-        const int32_t a_row = (int32_t)(c.m * T::kTileM + cta_rank * kCtaRows);
-        const int32_t b_row = (int32_t)(c.n * BN + cta_rank * T::kBRows);
+      uint32_t grp = 0;
+      for (uint32_t t = cluster_id; t < num_tiles; t += num_clusters) {
+        const TileSpot c = locate(t, grp);
+        // Sub-tile s of this CTA covers rows a_row + s * (128 * kCtaGroup). In a grouped launch
+        // the last row block of a group also loads rows of the next group (or zeros past the
+        // end): they only feed accumulator rows that are never stored.
+        const int32_t a_row = (int32_t)(c.row_base + c.m * T::kTileM + cta_rank * kCtaRows);
+        const int32_t b_row = (int32_t)(c.b_row_base + c.n * BN + cta_rank * T::kBRows);
         bool ok = true;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
@@ -297,7 +369,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint32_t peer_tfull = kPair ? ptx::mapa(tfull_bar, 1) : 0u;
       uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
-      for (uint32_t t = cluster_id; t < p.num_tiles && ok; t += num_clusters, ++it) {
+      for (uint32_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
         ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
         if (!ok) break;
@@ -348,15 +420,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t row_sw = (T::kRowBytes == 128u) ? (lane & 7u) : ((lane >> 1) & 3u);
     uint32_t it = 0, sbuf = 0;
     bool ok = true;
-    for (uint32_t t = cluster_id; t < p.num_tiles && ok; t += num_clusters, ++it) {
-      const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+    uint32_t grp = 0;
+    for (uint32_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+      const TileSpot c = locate(t, grp);
       const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
       ok = bounded_wait<kPair>(tfull_bar + 8u * buf, acc_ph, w, kTimeoutEpilogueTmemFull, t);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const uint32_t row0 = c.m * T::kTileM + ms * (kCtaRows * kCtaGroup) + cta_rank * kCtaRows +
-                            q * kStoreBoxRows;
+      const uint32_t row0 = c.row_base + c.m * T::kTileM + ms * (kCtaRows * kCtaGroup) +
+                            cta_rank * kCtaRows + q * kStoreBoxRows;
+      // A grouped launch must not write past its group: a box beyond the group's last row is
+      // dropped, one that straddles it is written row by row from the registers.
+      const bool box_outside = kGrouped && row0 >= c.row_end;
+      const bool box_straddles = kGrouped && !box_outside && row0 + kStoreBoxRows > c.row_end;
       const uint32_t col0 = c.n * BN;
       const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * T::kAccCols + ms * BN;
       constexpr uint32_t kFp32PerChunk = T::kChunkCols;            // accumulator words per chunk
@@ -429,6 +506,39 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             v[i] = __float_as_uint(apply_activation(__uint_as_float(v[i]) * p.alpha + add[i], p.activation));
         }
         const float out_scale = kFused ? 1.0f : p.alpha;
+        if constexpr (kGrouped) {
+          static_assert(!kGrouped || kOut == kOutBF16, "grouped launches write bf16");
+          if (box_outside) return;
+          if (box_straddles) {
+            // Each lane holds one row of the box: lanes whose row belongs to the group write
+            // their kChunkCols columns themselves, 16 bytes at a time.
+            const uint32_t r = row0 + lane;
+            const uint32_t cc = col0 + ch_col;
+            if (r < c.row_end) {
+              __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c_base) + (size_t)r * (size_t)p.ldc + cc;
+#pragma unroll
+              for (uint32_t j = 0; j < kPieces; ++j) {
+                uint32_t w[4];
+#pragma unroll
+                for (uint32_t e2 = 0; e2 < 4; ++e2) {
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(
+                      __uint_as_float(v[8 * j + 2 * e2]) * out_scale,
+                      __uint_as_float(v[8 * j + 2 * e2 + 1]) * out_scale);
+                  w[e2] = (uint32_t)__bfloat16_as_ushort(h.x) | ((uint32_t)__bfloat16_as_ushort(h.y) << 16);
+                }
+                if (cc + 8u * j + 8u <= p.N) {
+                  *reinterpret_cast<uint4*>(crow + 8u * j) = make_uint4(w[0], w[1], w[2], w[3]);
+                } else {
+#pragma unroll
+                  for (uint32_t e1 = 0; e1 < 8; ++e1)
+                    if (cc + 8u * j + e1 < p.N)
+                      crow[8u * j + e1] = __ushort_as_bfloat16((unsigned short)(w[e1 >> 1] >> (16u * (e1 & 1u))));
+                }
+              }
+            }
+            return;
+          }
+        }
         // The staging buffer about to be rewritten must have been read by its store.
         if (lane == 0) ptx::tma_store_wait_read<T::kStageBufs - 1>();
         __syncwarp();

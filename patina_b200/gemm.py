@@ -206,6 +206,40 @@ class GemmContext:
         if rc != _l.OK:
             self._raise(rc)
 
+    def gemm_bf16_tn_grouped(self, A, B, group_rows, out=None, alpha=1.0, config=None):
+        """One launch for the groups of a ragged batch: out[rows of group g] = alpha *
+        A[rows of group g] @ B[g]^T. A: [total_rows, K] bf16 with the groups' rows one after
+        another; B: [n_groups, N, K] (or [n_groups * N, K]) bf16; group_rows: int32 CUDA tensor
+        of n_groups row counts (it stays on the device: nothing here synchronises)."""
+        if not (A.is_cuda and B.is_cuda and group_rows.is_cuda):
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "A, B and group_rows must be CUDA tensors (no CPU path)")
+        if A.dtype != torch.bfloat16 or B.dtype != torch.bfloat16 or group_rows.dtype != torch.int32:
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "A and B must be bf16, group_rows int32")
+        n_groups = int(group_rows.numel())
+        total_rows, K = A.shape
+        if B.dim() == 3:
+            if not B.is_contiguous():
+                raise PatinaGemmError(_l.ERR_INVALID_ARG, "a 3-D B must be contiguous")
+            N = B.shape[1]
+            B2 = B.view(B.shape[0] * N, B.shape[2])
+        else:
+            B2 = B
+            N = B.shape[0] // max(n_groups, 1)
+        if B2.shape[0] != n_groups * N or B2.shape[1] != K or not group_rows.is_contiguous():
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "B must hold one [N, K] block per group")
+        if out is None:
+            out = torch.empty((total_rows, N), dtype=torch.bfloat16, device=A.device)
+        lda = A.stride(0) if total_rows > 1 else max(K, 1)
+        ldb = B2.stride(0) if B2.shape[0] > 1 else max(K, 1)
+        ldc = out.stride(0) if total_rows > 1 else max(N, 1)
+        rc = self._lib.patina_gemm_bf16_tn_grouped(
+            self._h, A.data_ptr(), lda, B2.data_ptr(), ldb, out.data_ptr(), ldc, group_rows.data_ptr(),
+            n_groups, total_rows, N, K, float(alpha),
+            C.byref(config) if config is not None else None, _stream_ptr(self.device))
+        if rc != _l.OK:
+            self._raise(rc)
+        return out
+
     # ------------------------------------------------------------- peer buffers
     def peer_alloc(self, nbytes: int) -> tuple[int, bytes]:
         """Device memory other processes of the node can map: (pointer, 64-byte handle)."""

@@ -40,9 +40,9 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
 
-def _wl(M, N, K, dist, desc, dtype="bf16", bound="tensor", scaling="weak", rotate=1):
+def _wl(M, N, K, dist, desc, dtype="bf16", bound="tensor", scaling="weak", rotate=1, groups=0):
     return {"M": M, "N": N, "K": K, "dist": dist, "desc": desc, "dtype": dtype, "bound": bound,
-            "scaling": scaling, "rotate": rotate}
+            "scaling": scaling, "rotate": rotate, "groups": groups}
 
 
 # scaling "weak": every GPU gets N columns (N-column shards of an N*gpus-wide problem);
@@ -72,6 +72,18 @@ for _m in (16, 64, 128):
         _m, 3584, 8192, "llm", f"one GPU's share of the decode-shaped GEMM split over 8 GPUs: M={_m}, "
         "N=28672/8=3584, K=8192 (memory-bound, 59 MB of weights); 12 weight buffers in rotation",
         bound="hbm", scaling="strong", rotate=12)
+
+# Ragged groups through one grouped launch: 16384 token rows routed unevenly to 8 experts that
+# each own a [N, K] weight block (the up-projection of a mixture-of-experts layer).
+WORKLOADS["moe_grouped_8x14336x4096"] = _wl(
+    16384, 14336, 4096, "llm", "grouped bf16 TN GEMM: 8 groups sharing N=14336, K=4096; 16384 rows split "
+    "unevenly (seeded multinomial) over the groups; activations N(0,1), weights N(0,0.02); each "
+    "group's N split over the GPUs", scaling="strong", groups=8)
+
+WORKLOADS["moe_grouped_64x2048x4096"] = _wl(
+    8192, 2048, 4096, "llm", "grouped bf16 TN GEMM: 64 small groups sharing N=2048, K=4096; 8192 rows "
+    "split unevenly (seeded multinomial) over the groups; each group's N split over the GPUs",
+    scaling="strong", groups=64)
 
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture;
 # see profiles/. None until a capture of that workload exists.
@@ -242,6 +254,7 @@ def run_ours(args):
         n_total = wl["N"] * world
     fp8 = wl["dtype"] == "e4m3"
     ebytes = 1 if fp8 else 2
+    G = wl["groups"]
     ctx = patina_b200.GemmContext(local_rank)
     # This rank's column shard: its own seed, so shards differ like real weight shards do;
     # A (activations) is replicated: every rank draws it from rank 0's seed.
@@ -256,7 +269,7 @@ def run_ours(args):
         del A32, B32
     else:
         A_h, _ = inputs.make_operands(wl["dist"], M, 1, K, seed=inputs.DEFAULT_SEED, pin=True)
-        _, B_h = inputs.make_operands(wl["dist"], 1, N, K, seed=inputs.DEFAULT_SEED + rank, pin=True)
+        _, B_h = inputs.make_operands(wl["dist"], 1, max(G, 1) * N, K, seed=inputs.DEFAULT_SEED + rank, pin=True)
     C_h = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
     dA = A_h.cuda(non_blocking=True)
     dBs = [B_h.cuda(non_blocking=True)]
@@ -320,7 +333,14 @@ def run_ours(args):
 
     flops_per_gpu = 2.0 * M * N * K
     flops_total = 2.0 * M * n_total * K
-    bytes_per_gpu = (M * K + N * K) * ebytes + M * N * 2
+    bytes_per_gpu = (M * K + max(G, 1) * N * K) * ebytes + M * N * 2
+    rows_h = d_rows = None
+    if G:
+        import numpy as np
+        rng = np.random.default_rng(inputs.DEFAULT_SEED)
+        share = rng.dirichlet(np.full(G, 2.0))           # uneven routing, the same on every rank
+        rows_h = torch.from_numpy(rng.multinomial(M, share).astype(np.int32)).pin_memory()
+        d_rows = rows_h.cuda()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -331,6 +351,8 @@ def run_ours(args):
         act = "gelu" if "gelu" in mode else ("relu" if "relu" in mode else "none")
         step = lambda i: ctx.gemm_bf16_tn_fused(dA, dBs[i % len(dBs)], out=dC, alpha=alpha, bias=bias_d,
                                                 residual=res_d, activation=act)
+    elif G:
+        step = lambda i: ctx.gemm_bf16_tn_grouped(dA, dBs[i % len(dBs)], d_rows, out=dC, alpha=alpha)
     else:
         step = lambda i: ctx.gemm_tn(dA, dBs[i % len(dBs)], out=dC, alpha=alpha)
     # A step shorter than ~150 us is launch-bound from Python: replay it from a CUDA graph.
@@ -368,16 +390,41 @@ def run_ours(args):
         barrier()
         shared.close()
 
+    separate_ms = None
+    if G:
+        # the same work as one plain call per group (what a caller without the grouped entry does)
+        bounds = [0] + list(torch.cumsum(rows_h, 0).tolist())
+        B3 = dBs[0].view(G, N, K)
+
+        def separate(i):
+            for g in range(G):
+                if bounds[g + 1] > bounds[g]:
+                    ctx.gemm_tn(dA[bounds[g]:bounds[g + 1]], B3[g], out=dC[bounds[g]:bounds[g + 1]], alpha=alpha)
+        s_steps = min(args.steps, 100)
+        s_total, _ = timed(separate, s_steps, 3)
+        separate_ms = s_total / s_steps
+
     # end to end: host buffers in, host buffer out, every step
     e2e_steps = min(args.steps, 200)
     if args.no_e2e:
         e2e_total_ms = float("nan")
+    elif G:
+        # weights stay resident (as in serving); activations and the routing counts come from
+        # pinned host memory every step and the result goes back
+        def e2e_step(i):
+            dA.copy_(A_h, non_blocking=True)
+            d_rows.copy_(rows_h, non_blocking=True)
+            ctx.gemm_bf16_tn_grouped(dA, dBs[0], d_rows, out=dC, alpha=alpha)
+            C_h.copy_(dC, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e2e_total_ms, _ = timed(e2e_step, e2e_steps, min(args.warmup, 3))
+        ctx.status()
     else:
         e2e_total_ms, _ = timed(lambda i: ctx.gemm_host(A_h, B_h, C_h, alpha=alpha), e2e_steps,
                                 min(args.warmup, 3))
         ctx.status()
     e2e_value = flops_total / (e2e_total_ms / e2e_steps * 1e-3) / 1e12
-    h2d = (M * K + N * K) * ebytes
+    h2d = (M * K + N * K) * ebytes if not G else M * K * ebytes + 4 * G
     d2h = M * N * 2
 
     if rank != 0:
@@ -453,6 +500,12 @@ def run_ours(args):
                      "algorithmic_flops_per_launch": flops_per_gpu,
                      "algorithmic_bytes_per_launch": bytes_per_gpu, **extra},
     }
+    if G:
+        out["config"]["groups"] = G
+        out["config"]["group_rows"] = rows_h.tolist()
+        out["separate_calls"] = {"ms_per_step": round(separate_ms, 5),
+                                 "tflops": round(flops_total / (separate_ms * 1e-3) / 1e12, 2),
+                                 "note": "one plain call per group, same kernels; not part of `value`"}
     if gather_ms is not None:
         out["allgather"] = {"ms_per_step": round(gather_ms, 4), "bytes_received_per_gpu": M * (n_total - N) * 2,
                             "gemm_plus_allgather_tflops": round(flops_total / ((ms_per_step + gather_ms) * 1e-3) / 1e12, 2),

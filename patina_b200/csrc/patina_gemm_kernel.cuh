@@ -319,6 +319,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     return sp;
   };
+  // Sub-tiles of a tile that hold rows of the problem. In a grouped launch the last row block
+  // of a group often needs only the first of its two 128-row (256 per pair) sub-tiles: the
+  // second is then neither loaded nor multiplied.
+  auto live_subtiles = [&](const TileSpot& c) -> uint32_t {
+    if constexpr (kGrouped && kMSub == 2) {
+      return (c.row_base + c.m * T::kTileM + kCtaRows * kCtaGroup >= c.row_end) ? 1u : 2u;
+    } else {
+      return (uint32_t)kMSub;
+    }
+  };
 
   // ------------------------------------------------------------ TMA producer
   if (warp_idx == 0) {
@@ -333,6 +343,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // end): they only feed accumulator rows that are never stored.
         const int32_t a_row = (int32_t)(c.row_base + c.m * T::kTileM + cta_rank * kCtaRows);
         const int32_t b_row = (int32_t)(c.b_row_base + c.n * BN + cta_rank * T::kBRows);
+        const uint32_t n_sub = live_subtiles(c);
+        const uint32_t stage_tx = n_sub * T::kASubBytes + T::kBBytes;  // bytes this CTA loads per stage
         bool ok = true;
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
@@ -341,17 +353,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           const uint32_t sb = sa + T::kABytes;
           const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
           if constexpr (kPair) {
-            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, 2u * T::kStageBytes);
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, 2u * stage_tx);
 #pragma unroll
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-              ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
+              if (ms < n_sub)
+                ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
                                     a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
           } else {
-            ptx::mbar_arrive_expect_tx(full_bar + 8u * s, T::kStageBytes);
+            ptx::mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
 #pragma unroll
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-              ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * s, k0,
+              if (ms < n_sub)
+                ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * s, k0,
                                a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d(sb, &tm_b, full_bar + 8u * s, k0, b_row);
           }
@@ -367,9 +381,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint32_t idesc_v = idesc(kIn, kCtaRows * kCtaGroup, BN);
       const uint32_t peer_empty = kPair ? ptx::mapa(empty_bar, 1) : 0u;
       const uint32_t peer_tfull = kPair ? ptx::mapa(tfull_bar, 1) : 0u;
-      uint32_t s = 0, ph = 0, it = 0;
+      uint32_t s = 0, ph = 0, it = 0, grp = 0;
       bool ok = true;
       for (uint32_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+        const uint32_t n_sub = live_subtiles(locate(t, grp));
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
         ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
         if (!ok) break;
@@ -386,9 +401,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
 #pragma unroll
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
-              const uint64_t da = smem_desc_sw128_kmajor(sa + ms * T::kASubBytes);
-              ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db + adv, idesc_v,
-                                          (kb | k) != 0u);
+              if (ms < n_sub) {
+                const uint64_t da = smem_desc_sw128_kmajor(sa + ms * T::kASubBytes);
+                ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db + adv, idesc_v,
+                                            (kb | k) != 0u);
+              }
             }
           }
           ptx::umma_commit<kCtaGroup>(empty_bar + 8u * s);

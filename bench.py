@@ -82,8 +82,9 @@ WORKLOADS["moe_grouped_8x14336x4096"] = _wl(
 
 WORKLOADS["moe_grouped_64x2048x4096"] = _wl(
     8192, 2048, 4096, "llm", "grouped bf16 TN GEMM: 64 small groups sharing N=2048, K=4096; 8192 rows "
-    "split unevenly (seeded multinomial) over the groups; each group's N split over the GPUs",
-    scaling="strong", groups=64)
+    "split unevenly (seeded multinomial) over the groups (1.07 GB of weights for 0.14 TFLOP: "
+    "memory-bound); each group's N split over the GPUs",
+    bound="hbm", scaling="strong", groups=64)
 
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture;
 # see profiles/. None until a capture of that workload exists.

@@ -137,6 +137,18 @@ int patina_gemm_bf16_tn_fused(PatinaGemmContext* ctx, const void* A, int64_t lda
                               int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                               float alpha, const PatinaGemmEpilogue* epi, void* stream);
 
+/* The fused epilogue with an fp8 result (no counterpart in the reference): what a quantised
+ * layer stack needs from the GEMM that feeds its next fp8 GEMM.
+ *     y = act(alpha * A * B^T + bias + beta * R)          (fp32, as above)
+ *     C[M, ldc] (e4m3, one byte per element) = saturate_e4m3(round_to_nearest_even(out_scale * y))
+ *     *amax = max(*amax, max |y|)  over the M x N outputs (device float, atomic; may be NULL;
+ *             the caller zeroes it when a new scale window starts)
+ * ldc must be a multiple of 16 (bytes = elements); epi may be NULL (plain GEMM, quantised). */
+int patina_gemm_bf16_tn_fused_fp8out(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                     int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                                     float alpha, const PatinaGemmEpilogue* epi, float out_scale,
+                                     float* amax, void* stream);
+
 /* Column-shard scatter (no counterpart in the reference, which is single-GPU): the same bf16
  * GEMM, but every finished tile of C is stored to n_dests (1..8) destinations that share M, N
  * and ldc. On a multi-GPU node each GPU passes, for every GPU g, the address of ITS column block

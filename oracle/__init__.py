@@ -158,10 +158,9 @@ def scale_round_bf16(ref: np.ndarray, alpha: float = 1.0) -> np.ndarray:
     return out
 
 
-def fused_epilogue_bf16(ref: np.ndarray, alpha=1.0, bias=None, residual=None, beta=1.0,
-                        activation="none") -> np.ndarray:
-    """bf16(act(alpha * ref + bias[n] + beta * residual[m, n])) widened to float32, all of it in
-    double before the single rounding: the expected output of the fused-epilogue entry point.
+def fused_epilogue_f64(ref: np.ndarray, alpha=1.0, bias=None, residual=None, beta=1.0,
+                       activation="none") -> np.ndarray:
+    """act(alpha * ref + bias[n] + beta * residual[m, n]) in double, before any rounding.
     (The reference's kernel has no epilogue arithmetic; this extends its double-precision check.)"""
     import math
     x = alpha * np.asarray(ref, dtype=np.float64)
@@ -178,7 +177,23 @@ def fused_epilogue_bf16(ref: np.ndarray, alpha=1.0, bias=None, residual=None, be
         x = x / (1.0 + np.exp(-x))
     elif activation != "none":
         raise ValueError(activation)
-    return scale_round_bf16(x, 1.0)
+    return x
+
+
+def fused_epilogue_bf16(ref: np.ndarray, alpha=1.0, bias=None, residual=None, beta=1.0,
+                        activation="none") -> np.ndarray:
+    """bf16 of the double-precision epilogue, widened to float32: the expected output of the
+    fused-epilogue entry point (one rounding at the very end)."""
+    return scale_round_bf16(fused_epilogue_f64(ref, alpha, bias, residual, beta, activation), 1.0)
+
+
+def fused_epilogue_e4m3(ref: np.ndarray, out_scale: float, alpha=1.0, bias=None, residual=None,
+                        beta=1.0, activation="none"):
+    """The fp8-output epilogue: (e4m3 codes of out_scale * y rounded to nearest even and
+    saturated, max|y|, y) with y the double-precision epilogue."""
+    y = fused_epilogue_f64(ref, alpha, bias, residual, beta, activation)
+    codes = f32_to_e4m3_bits((y * out_scale).astype(np.float32))
+    return codes, float(np.abs(y).max()) if y.size else 0.0, y
 
 
 # --------------------------------------------------------------- comparisons

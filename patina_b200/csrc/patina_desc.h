@@ -23,11 +23,11 @@
 namespace patina {
 
 enum InputType : int { kF16 = 0, kBF16 = 1, kE4M3 = 2 };
-enum OutputType : int { kOutBF16 = 0, kOutF32 = 1 };
+enum OutputType : int { kOutBF16 = 0, kOutF32 = 1, kOutE4M3 = 2 };
 enum SwizzleMode : int { kSwizzleNone = 0, kSwizzle128B = 2 };  // descriptor layout-type codes
 
 PATINA_HD constexpr uint32_t input_bytes(int t) { return t == kE4M3 ? 1u : 2u; }
-PATINA_HD constexpr uint32_t output_bytes(int t) { return t == kOutF32 ? 4u : 2u; }
+PATINA_HD constexpr uint32_t output_bytes(int t) { return t == kOutF32 ? 4u : t == kOutE4M3 ? 1u : 2u; }
 
 // ---- shared-memory matrix descriptor (tcgen05, "version 1") --------------
 //   [ 0,14) start address  >> 4      [16,30) leading-dim byte offset >> 4
@@ -118,10 +118,11 @@ constexpr uint32_t kMaxDynSmem = 232448;    // 227 KB
 // Epilogue staging: every epilogue warp owns two buffers of 32 rows, double-buffered so that
 // filling one overlaps the TMA store reading the other. With four epilogue warps a row
 // segment is 128 bytes (128-byte swizzle); with eight warps (m_sub = 2) it is 64 bytes
-// (64-byte swizzle), which keeps the total at 32 KB.
+// (64-byte swizzle), which keeps the total at 32 KB. One-byte outputs also stage 64-byte rows
+// (64 columns per box, the same register count per chunk as a 128-byte row of bf16).
 PATINA_HD constexpr uint32_t staging_bufs(uint32_t) { return 2u; }
 PATINA_HD constexpr uint32_t staging_row_bytes(uint32_t m_sub, uint32_t out_bytes) {
-  return (m_sub == 2 && out_bytes == 2) ? 64u : 128u;
+  return ((m_sub == 2 && out_bytes == 2) || out_bytes == 1) ? 64u : 128u;
 }
 PATINA_HD constexpr uint32_t staging_buf_bytes(uint32_t m_sub, uint32_t out_bytes) {
   return kStoreBoxRows * staging_row_bytes(m_sub, out_bytes);

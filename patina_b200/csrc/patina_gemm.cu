@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdarg>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -56,6 +57,11 @@ struct KernelEntry {
     gemm_tn_kernel<G, MS, BN, S, IN, OUT, true>, GemmTraits<G, MS, BN, S, IN, OUT>::kSmemBytes }
 
 // Listed best-first per type pair: an explicit request takes the first match.
+#define PATINA_KERNEL_Q(G, MS, BN, S)                                           \
+  { G, MS, BN, S, kBF16, kOutE4M3, gemm_tn_kernel<G, MS, BN, S, kBF16, kOutE4M3, true>, \
+    gemm_tn_kernel<G, MS, BN, S, kBF16, kOutE4M3, true>,                         \
+    GemmTraits<G, MS, BN, S, kBF16, kOutE4M3>::kSmemBytes }
+
 const KernelEntry kKernels[] = {
     // bf16 -> bf16
     PATINA_KERNEL_F(2, 2, 256, 4, kBF16, kOutBF16),  // 512 x 256 per pair, accumulators fill TMEM
@@ -79,6 +85,10 @@ const KernelEntry kKernels[] = {
     PATINA_KERNEL(2, 1, 256, 6, kE4M3, kOutBF16),
     PATINA_KERNEL(1, 1, 256, 4, kE4M3, kOutBF16),
     PATINA_KERNEL(1, 1, 128, 6, kE4M3, kOutBF16),
+    // bf16 -> e4m3 (scaled, with amax): fused epilogue only, so both slots hold that kernel
+    PATINA_KERNEL_Q(2, 1, 256, 6),
+    PATINA_KERNEL_Q(1, 1, 256, 4),
+    PATINA_KERNEL_Q(1, 1, 128, 6),
     // f16 -> f32 (the reference kernel's types)
     PATINA_KERNEL(2, 1, 256, 6, kF16, kOutF32),
     PATINA_KERNEL(1, 1, 256, 4, kF16, kOutF32),
@@ -521,7 +531,8 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
                 const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                 float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream,
                 void* const* extra_dests = nullptr, int n_extra = 0,
-                const PatinaGemmEpilogue* epi = nullptr) {
+                const PatinaGemmEpilogue* epi = nullptr, float out_scale = 1.0f,
+                float* amax = nullptr) {
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   std::string err;
   int rc = validate_args(in_type, out_type, A, lda, B, ldb, C, ldc, M, N, K, &err);
@@ -566,8 +577,9 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   if (rc != PATINA_GEMM_OK) return rc;
   for (int d = 0; d <= n_extra; ++d) {
     rc = get_tensor_map(ctx, d == 0 ? C : extra_dests[d - 1],
-                        out_type == kOutF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                        out_type == kOutF32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                        : out_type == kOutE4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                               : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                         ob, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kStoreBoxRows,
                         staging_row_bytes((uint32_t)k->m_sub, ob) / ob, &tm_c.map[d]);
     if (rc != PATINA_GEMM_OK) return rc;
@@ -634,6 +646,11 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     p.activation = (uint32_t)epi->activation;
   }
   p.n_dests = (uint32_t)(1 + n_extra);
+  p.c_dests[0] = C;
+  for (int d = 0; d < n_extra; ++d) p.c_dests[d + 1] = extra_dests[d];
+  p.ldc = ldc;
+  p.out_scale = out_scale;
+  p.amax = amax;
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
 
@@ -767,7 +784,7 @@ int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const voi
   p.n_dests = 1;
   p.group_rows = group_rows;
   p.n_groups = (uint32_t)n_groups;
-  p.c_base = C;
+  p.c_dests[0] = C;
   p.ldc = ldc;
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
@@ -942,10 +959,7 @@ int patina_gemm_f16_tn_f32out(PatinaGemmContext* ctx, const void* A, int64_t lda
                      static_cast<cudaStream_t>(stream));
 }
 
-int patina_gemm_bf16_tn_fused(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
-                              int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
-                              float alpha, const PatinaGemmEpilogue* epi, void* stream) {
-  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+static int check_epilogue(PatinaGemmContext* ctx, const PatinaGemmEpilogue* epi, int64_t N, int64_t K) {
   if (!epi) return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "epilogue description is null");
   if (epi->activation < 0 || epi->activation > 3)
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "unknown activation");
@@ -957,6 +971,34 @@ int patina_gemm_bf16_tn_fused(PatinaGemmContext* ctx, const void* A, int64_t lda
                        "residual must be 16-byte aligned with ldr >= N and a row pitch multiple of 16 bytes");
   }
   if (K == 0) return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "fused epilogue needs K > 0");
+  return PATINA_GEMM_OK;
+}
+
+int patina_gemm_bf16_tn_fused_fp8out(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                     int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                                     float alpha, const PatinaGemmEpilogue* epi, float out_scale,
+                                     float* amax, void* stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  const PatinaGemmEpilogue none{};
+  if (!epi) epi = &none;
+  int rc = check_epilogue(ctx, epi, N, K);
+  if (rc != PATINA_GEMM_OK) return rc;
+  if (!(out_scale > 0.0f) || !std::isfinite(out_scale))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "out_scale must be positive and finite");
+  if (amax && (reinterpret_cast<uintptr_t>(amax) & 3u))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "amax is not 4-byte aligned");
+  return launch_gemm(ctx, kBF16, kOutE4M3, A, lda, B, ldb, C, ldc, M, N, K, alpha, nullptr,
+                     static_cast<cudaStream_t>(stream), nullptr, 0, epi, out_scale, amax);
+}
+
+int patina_gemm_bf16_tn_fused(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                              int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                              float alpha, const PatinaGemmEpilogue* epi, void* stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  {
+    const int rc = check_epilogue(ctx, epi, N, K);
+    if (rc != PATINA_GEMM_OK) return rc;
+  }
   // A transcendental per output is too much work for the epilogue of the TMEM-filling tile,
   // which runs between two mainloops: take the double-buffered 256 x 256 pair tile, whose
   // epilogue overlaps the next tile's mainloop (measured at 8192 x 14336 x 4096 with bias + GELU:

@@ -30,6 +30,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "patina_desc.h"
 #include "patina_ptx.cuh"
@@ -57,12 +58,20 @@ struct GemmParams {
   int64_t ldr;
   float beta;
   uint32_t activation;     // Activation
+  // e4m3 output (kernels instantiated with kOutE4M3): C = e4m3_sat(out_scale * act(...)); the
+  // largest |act(...)| of the launch is folded into *amax with an atomic max (may be null)
+  float out_scale;
+  float* amax;
   uint32_t n_dests;        // destinations of C (1..kMaxDests)
   // grouped launch (kernels instantiated with kGrouped): A and C hold the groups' rows one
   // after another, B holds one [N, K] block per group; M above is the total row count
   const int32_t* group_rows;  // device array, rows of A and C per group
   uint32_t n_groups;          // <= kMaxGroups
-  void* c_base;               // C itself, for the rows of a box that straddles a group's end
+  // C itself (every destination), for boxes the TMA store cannot clip: TMA stores clip at
+  // 16-byte granularity, so a box that crosses column N when N * element size is not a
+  // multiple of 16 bytes, and (grouped launch) a box that crosses a group's last row, are
+  // written row by row from the registers instead.
+  void* c_dests[kMaxDests];
   int64_t ldc;
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
@@ -200,6 +209,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   // The fused epilogue may read C itself as the residual, so no column may be produced twice.
   static_assert(!(kFused && T::kOverlapLastChunk), "fused epilogue needs whole store boxes");
   static_assert(!(kFused && kGrouped), "the grouped kernel has the plain epilogue only");
+  static_assert(kOut != kOutE4M3 || kFused, "e4m3 output goes through the fused epilogue (scale, amax)");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -449,12 +459,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             cta_rank * kCtaRows + q * kStoreBoxRows;
       // A grouped launch must not write past its group: a box beyond the group's last row is
       // dropped, one that straddles it is written row by row from the registers.
-      const bool box_outside = kGrouped && row0 >= c.row_end;
+      const bool box_outside = row0 >= c.row_end;
       const bool box_straddles = kGrouped && !box_outside && row0 + kStoreBoxRows > c.row_end;
       const uint32_t col0 = c.n * BN;
       const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * T::kAccCols + ms * BN;
       constexpr uint32_t kFp32PerChunk = T::kChunkCols;            // accumulator words per chunk
       constexpr uint32_t kPieces = T::kRowBytes / 16u;             // 16-byte pieces per staged row
+      float tile_amax = 0.0f;   // e4m3 output: largest magnitude this thread produced in the tile
       // Chunk ch + 1 is requested from TMEM before chunk ch is converted and stored, so the
       // load's latency (about 170 cycles measured) hides behind the previous chunk's work.
       auto chunk_col = [](uint32_t ch) -> uint32_t {
@@ -521,35 +532,78 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
           for (uint32_t i = 0; i < kFp32PerChunk; ++i)
             v[i] = __float_as_uint(apply_activation(__uint_as_float(v[i]) * p.alpha + add[i], p.activation));
+          if constexpr (kOut == kOutE4M3) {
+            // rows past M carry act(bias) and must not count; columns past N are exactly zero
+            if (r < p.M) {
+#pragma unroll
+              for (uint32_t i = 0; i < kFp32PerChunk; ++i)
+                if (cc + i < p.N) tile_amax = fmaxf(tile_amax, fabsf(__uint_as_float(v[i])));
+            }
+          }
         }
-        const float out_scale = kFused ? 1.0f : p.alpha;
-        if constexpr (kGrouped) {
-          static_assert(!kGrouped || kOut == kOutBF16, "grouped launches write bf16");
-          if (box_outside) return;
-          if (box_straddles) {
-            // Each lane holds one row of the box: lanes whose row belongs to the group write
-            // their kChunkCols columns themselves, 16 bytes at a time.
+        const float out_scale = (kOut == kOutE4M3) ? p.out_scale : (kFused ? 1.0f : p.alpha);
+        static_assert(!kGrouped || kOut == kOutBF16, "grouped launches write bf16");
+        if (box_outside) return;
+        {
+          const uint32_t cc = col0 + ch_col;
+          constexpr uint32_t kOutBytes = output_bytes(kOut);
+          const bool ragged_n = cc < p.N && cc + T::kChunkCols > p.N && ((p.N * kOutBytes) & 15u) != 0u;
+          if (box_straddles || ragged_n) {
+            // Each lane holds one row of the box: lanes whose row exists write their columns
+            // themselves, 16 bytes at a time, element by element in the piece that crosses N.
             const uint32_t r = row0 + lane;
-            const uint32_t cc = col0 + ch_col;
             if (r < c.row_end) {
-              __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c_base) + (size_t)r * (size_t)p.ldc + cc;
+              constexpr uint32_t kPerPiece = 16u / kOutBytes;   // elements per 16-byte piece
+              for (uint32_t d = 0; d < p.n_dests; ++d) {
+                uint8_t* crow = static_cast<uint8_t*>(p.c_dests[d]) +
+                                ((size_t)r * (size_t)p.ldc + cc) * kOutBytes;
 #pragma unroll
-              for (uint32_t j = 0; j < kPieces; ++j) {
-                uint32_t w[4];
+                for (uint32_t j = 0; j < kPieces; ++j) {
+                  uint32_t w[4];
+                  if constexpr (kOut == kOutBF16) {
 #pragma unroll
-                for (uint32_t e2 = 0; e2 < 4; ++e2) {
-                  const __nv_bfloat162 h = __floats2bfloat162_rn(
-                      __uint_as_float(v[8 * j + 2 * e2]) * out_scale,
-                      __uint_as_float(v[8 * j + 2 * e2 + 1]) * out_scale);
-                  w[e2] = (uint32_t)__bfloat16_as_ushort(h.x) | ((uint32_t)__bfloat16_as_ushort(h.y) << 16);
-                }
-                if (cc + 8u * j + 8u <= p.N) {
-                  *reinterpret_cast<uint4*>(crow + 8u * j) = make_uint4(w[0], w[1], w[2], w[3]);
-                } else {
+                    for (uint32_t e2 = 0; e2 < 4; ++e2) {
+                      const __nv_bfloat162 h = __floats2bfloat162_rn(
+                          __uint_as_float(v[8 * j + 2 * e2]) * out_scale,
+                          __uint_as_float(v[8 * j + 2 * e2 + 1]) * out_scale);
+                      w[e2] = (uint32_t)__bfloat16_as_ushort(h.x) | ((uint32_t)__bfloat16_as_ushort(h.y) << 16);
+                    }
+                  } else if constexpr (kOut == kOutE4M3) {
 #pragma unroll
-                  for (uint32_t e1 = 0; e1 < 8; ++e1)
-                    if (cc + 8u * j + e1 < p.N)
-                      crow[8u * j + e1] = __ushort_as_bfloat16((unsigned short)(w[e1 >> 1] >> (16u * (e1 & 1u))));
+                    for (uint32_t e4 = 0; e4 < 4; ++e4) {
+                      const uint32_t i0 = 16 * j + 4 * e4;
+                      const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                          make_float2(__uint_as_float(v[i0]) * out_scale, __uint_as_float(v[i0 + 1]) * out_scale),
+                          __NV_SATFINITE, __NV_E4M3);
+                      const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                          make_float2(__uint_as_float(v[i0 + 2]) * out_scale,
+                                      __uint_as_float(v[i0 + 3]) * out_scale),
+                          __NV_SATFINITE, __NV_E4M3);
+                      w[e4] = lo | (hi << 16);
+                    }
+                  } else {
+#pragma unroll
+                    for (uint32_t e = 0; e < 4; ++e)
+                      w[e] = __float_as_uint(__uint_as_float(v[4 * j + e]) * out_scale);
+                  }
+                  const uint32_t c_first = cc + kPerPiece * j;
+                  if (c_first + kPerPiece <= p.N) {
+                    *reinterpret_cast<uint4*>(crow + 16u * j) = make_uint4(w[0], w[1], w[2], w[3]);
+                  } else {
+#pragma unroll
+                    for (uint32_t e = 0; e < kPerPiece; ++e) {
+                      if (c_first + e < p.N) {
+                        if constexpr (kOutBytes == 4u) {
+                          reinterpret_cast<uint32_t*>(crow + 16u * j)[e] = w[e];
+                        } else if constexpr (kOutBytes == 2u) {
+                          reinterpret_cast<uint16_t*>(crow + 16u * j)[e] =
+                              (uint16_t)(w[e >> 1] >> (16u * (e & 1u)));
+                        } else {
+                          (crow + 16u * j)[e] = (uint8_t)(w[e >> 2] >> (8u * (e & 3u)));
+                        }
+                      }
+                    }
+                  }
                 }
               }
             }
@@ -573,6 +627,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             w1 = pack(v[8 * j + 2], v[8 * j + 3]);
             w2 = pack(v[8 * j + 4], v[8 * j + 5]);
             w3 = pack(v[8 * j + 6], v[8 * j + 7]);
+          } else if constexpr (kOut == kOutE4M3) {
+            // sixteen values per 16-byte piece; round to nearest even, saturate to +-448
+            auto pack4 = [&](uint32_t i0) -> uint32_t {
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__uint_as_float(v[i0]) * out_scale, __uint_as_float(v[i0 + 1]) * out_scale),
+                  __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__uint_as_float(v[i0 + 2]) * out_scale, __uint_as_float(v[i0 + 3]) * out_scale),
+                  __NV_SATFINITE, __NV_E4M3);
+              return lo | (hi << 16);
+            };
+            w0 = pack4(16 * j + 0);
+            w1 = pack4(16 * j + 4);
+            w2 = pack4(16 * j + 8);
+            w3 = pack4(16 * j + 12);
           } else {
             w0 = __float_as_uint(__uint_as_float(v[4 * j + 0]) * out_scale);
             w1 = __float_as_uint(__uint_as_float(v[4 * j + 1]) * out_scale);
@@ -607,6 +676,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           ptx::tmem_ld_wait();
           if (ch + 2u < T::kChunks) request(ch + 2u, va);
           finish(ch + 1u, vb);
+        }
+      }
+      if constexpr (kOut == kOutE4M3) {
+        if (p.amax != nullptr) {
+          // magnitudes are non-negative floats: their bit patterns order like unsigned integers
+          const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(tile_amax));
+          if (lane == 0 && m != 0u) atomicMax(reinterpret_cast<unsigned int*>(p.amax), m);
         }
       }
     }

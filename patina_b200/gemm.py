@@ -167,14 +167,7 @@ class GemmContext:
             self._raise(rc)
         return out
 
-    def gemm_bf16_tn_fused(self, A, B, out=None, alpha=1.0, bias=None, residual=None, beta=1.0,
-                           activation="none"):
-        """out = act(alpha * A @ B^T + bias[n] + beta * residual[m, n]) in one kernel
-        (bias: float32 [N]; residual: bf16 [M, N]; activation: none | relu | gelu | silu)."""
-        M, K = A.shape
-        N = B.shape[0]
-        if out is None:
-            out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    def _epilogue(self, M, N, bias, residual, beta, activation):
         acts = {"none": _l.ACT_NONE, "relu": _l.ACT_RELU, "gelu": _l.ACT_GELU, "silu": _l.ACT_SILU}
         if activation not in acts:
             raise PatinaGemmError(_l.ERR_INVALID_ARG, f"unknown activation {activation!r}")
@@ -183,12 +176,44 @@ class GemmContext:
         if residual is not None and (residual.dtype != torch.bfloat16 or tuple(residual.shape) != (M, N)
                                      or residual.stride(1) != 1):
             raise PatinaGemmError(_l.ERR_INVALID_ARG, "residual must be bf16 [M, N], contiguous rows")
-        epi = _l.GemmEpilogue(bias.data_ptr() if bias is not None else None,
-                              residual.data_ptr() if residual is not None else None,
-                              residual.stride(0) if residual is not None else 0, float(beta), acts[activation])
+        return _l.GemmEpilogue(bias.data_ptr() if bias is not None else None,
+                               residual.data_ptr() if residual is not None else None,
+                               residual.stride(0) if residual is not None else 0, float(beta), acts[activation])
+
+    def gemm_bf16_tn_fused(self, A, B, out=None, alpha=1.0, bias=None, residual=None, beta=1.0,
+                           activation="none"):
+        """out = act(alpha * A @ B^T + bias[n] + beta * residual[m, n]) in one kernel
+        (bias: float32 [N]; residual: bf16 [M, N]; activation: none | relu | gelu | silu)."""
+        M, K = A.shape
+        N = B.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+        epi = self._epilogue(M, N, bias, residual, beta, activation)
         rc = self._lib.patina_gemm_bf16_tn_fused(self._h, A.data_ptr(), A.stride(0), B.data_ptr(),
                                                  B.stride(0), out.data_ptr(), out.stride(0), M, N, K,
                                                  float(alpha), C.byref(epi), _stream_ptr(self.device))
+        if rc != _l.OK:
+            self._raise(rc)
+        return out
+
+    def gemm_bf16_tn_fused_fp8out(self, A, B, out_scale: float, out=None, amax=None, alpha=1.0, bias=None,
+                                  residual=None, beta=1.0, activation="none"):
+        """out (float8_e4m3fn) = saturate(out_scale * act(alpha * A @ B^T + bias + beta * residual));
+        `amax`, a one-element float32 CUDA tensor, is raised to the largest |act(...)| seen."""
+        M, K = A.shape
+        N = B.shape[0]
+        if out is None:
+            ldc = (N + 15) // 16 * 16
+            out = torch.empty((M, ldc), dtype=torch.float8_e4m3fn, device=A.device)[:, :N]
+        if out.element_size() != 1 or tuple(out.shape) != (M, N) or out.stride(1) != 1:
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "out must be [M, N] float8_e4m3fn (or uint8), contiguous rows")
+        if amax is not None and (amax.dtype != torch.float32 or amax.numel() != 1 or not amax.is_cuda):
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "amax must be a one-element float32 CUDA tensor")
+        epi = self._epilogue(M, N, bias, residual, beta, activation)
+        rc = self._lib.patina_gemm_bf16_tn_fused_fp8out(
+            self._h, A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), out.data_ptr(),
+            out.stride(0) if M > 1 else max((N + 15) // 16 * 16, 16), M, N, K, float(alpha), C.byref(epi),
+            float(out_scale), amax.data_ptr() if amax is not None else None, _stream_ptr(self.device))
         if rc != _l.OK:
             self._raise(rc)
         return out

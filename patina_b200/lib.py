@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "lib
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED_ARCH, ERR_CUDA, ERR_TIMEOUT = 0, 1, 2, 3, 4
 IN_F16, IN_BF16, IN_E4M3 = 0, 1, 2
-OUT_BF16, OUT_F32 = 0, 1
+OUT_BF16, OUT_F32, OUT_E4M3 = 0, 1, 2
 
 # every symbol include/patina_gemm.h declares
 SYMBOLS = (
@@ -22,7 +22,7 @@ SYMBOLS = (
     "patina_gemm_plan", "patina_gemm_smem_desc", "patina_gemm_idesc",
     "patina_gemm_k_advance_units", "patina_gemm_tmem_lane_offset", "patina_gemm_tile_coord",
     "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_range",
-    "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_grouped",
+    "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped",
     "patina_gemm_peer_alloc",
     "patina_gemm_peer_open", "patina_gemm_peer_close", "patina_gemm_peer_free",
 )
@@ -111,6 +111,7 @@ def load() -> C.CDLL:
     L.patina_gemm_streamk_owner.argtypes = [C.c_uint64] * 3
     L.patina_gemm_streamk_owner.restype = C.c_uint32
     L.patina_gemm_bf16_tn_scatter.argtypes = [vp, vp, i64, vp, i64, C.POINTER(vp), i32, i64, i64, i64, i64, f32, vp]
+    L.patina_gemm_bf16_tn_fused_fp8out.argtypes = gemm_args + [f32, C.POINTER(GemmEpilogue), f32, vp, vp]
     L.patina_gemm_bf16_tn_grouped.argtypes = [vp, vp, i64, vp, i64, vp, i64, vp, i32, i64, i64, i64, f32,
                                               C.POINTER(GemmConfig), vp]
     L.patina_gemm_bf16_tn_fused.argtypes = gemm_args + [f32, C.POINTER(GemmEpilogue), vp]

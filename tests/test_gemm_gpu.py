@@ -113,11 +113,15 @@ def test_bf16_ragged_shapes(ctx, oracle_mod, M, N, K):
     A, B = inputs.make_operands("llm", M, N, K, seed=M * 7 + N)
     want = expect_bf16(oracle_mod, A, B, alpha=0.75)
     for name, cfg in cfgs().items():
-        ldc = (N + 7) // 8 * 8  # row pitch must be a multiple of 16 bytes
-        out = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :N]
+        ldc = (N + 7) // 8 * 8 + 8  # row pitch must be a multiple of 16 bytes
+        full = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")
+        out = full[:, :N]
         ctx.gemm_tn(A.cuda(), B.cuda(), out=out, alpha=0.75, config=cfg)
         ctx.status()
         check_norm(oracle_mod, out, want, f"{name} {M}x{N}x{K}")
+        # not one column behind N may be written, also when N is not a multiple of 8 columns
+        # (TMA stores clip in units of 16 bytes; the kernel writes such boxes itself)
+        assert bool(torch.isnan(full[:, N:]).all()), f"{name} {M}x{N}x{K}: columns behind N were written"
 
 
 def test_leading_dimensions_and_untouched_padding(ctx, oracle_mod):
@@ -334,6 +338,60 @@ def test_calls_can_be_captured_in_a_cuda_graph(ctx, oracle_mod):
     torch.cuda.current_stream().wait_stream(side)
     A2, B2 = inputs.make_operands("llm", *shapes[2], seed=70 + 10 + 2)
     check_norm(oracle_mod, replayed[2], expect_bf16(oracle_mod, A2, B2), "graph replay vs oracle")
+
+
+@pytest.mark.parametrize("activation", ["none", "gelu"])
+def test_fused_epilogue_fp8_output(ctx, oracle_mod, activation):
+    """e4m3 result of the fused epilogue: C = sat_e4m3(rne(out_scale * y)), y as in the bf16 case,
+    plus the running amax. Rule (written out because one e4m3 step is 6-12 % of a value, far
+    above the bf16 tolerance): every code equals the oracle's (double-precision y, one rounding),
+    or is the neighbouring code where the exact out_scale * y lies within 5 % of a step of the
+    midpoint between the two (fp32 vs double accumulation may fall either side); at most 1 % of
+    the codes may differ; saturated values are +-448, never NaN; amax within 1e-4 relative."""
+    from patina_b200 import inputs
+    M, N, K = 520, 392, 264
+    A, B = inputs.make_operands("llm", M, N, K, seed=21)
+    g = torch.Generator().manual_seed(6)
+    bias = torch.randn(N, generator=g, dtype=torch.float32) * 0.1
+    res = (torch.randn((M, N), generator=g) * 0.2).to(torch.bfloat16)
+    ref = oracle_mod.ref_gemm_tn(widen(oracle_mod, A), widen(oracle_mod, B))
+    table = oracle_mod.e4m3_bits_to_f32(np.arange(256, dtype=np.uint8)).astype(np.float64)
+    dA, dB = A.cuda(), B.cuda()
+    ldc = (N + 31) // 16 * 16
+    for kw, scale_for in [(dict(bias=bias, residual=res, beta=0.5), 200.0), (dict(), 2000.0)]:
+        _, amax_ref, y = oracle_mod.fused_epilogue_e4m3(
+            ref, 1.0, alpha=1.5, bias=kw.get("bias").numpy() if "bias" in kw else None,
+            residual=widen(oracle_mod, kw["residual"]) if "residual" in kw else None,
+            beta=kw.get("beta", 1.0), activation=activation)
+        out_scale = scale_for / amax_ref          # 200: inside the range; 2000: part of it saturates
+        codes_ref = oracle_mod.f32_to_e4m3_bits((y * out_scale).astype(np.float32))
+        full = torch.full((M, ldc), 0x55, dtype=torch.uint8, device="cuda")
+        amax = torch.zeros(1, dtype=torch.float32, device="cuda")
+        dev_kw = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in kw.items()}
+        ctx.gemm_bf16_tn_fused_fp8out(dA, dB, out_scale, out=full[:, :N], amax=amax, alpha=1.5,
+                                      activation=activation, **dev_kw)
+        ctx.status()
+        got = full[:, :N].cpu().numpy()
+        assert bool((full[:, N:] == 0x55).all()), "padding columns were written"
+        assert not np.any((got & 0x7F) == 0x7F), "NaN code in the output"
+        diff = got != codes_ref
+        assert diff.mean() <= 0.01, f"{diff.mean():.4f} of the codes differ"
+        a, b, x = table[got[diff]], table[codes_ref[diff]], (y * out_scale)[diff]
+        step = np.abs(a - b)
+        order = np.sort(np.unique(table[np.isfinite(table)]))
+        adjacent = np.abs(np.searchsorted(order, a) - np.searchsorted(order, b)) == 1
+        assert bool(adjacent.all()), "a differing code is not the oracle's neighbour"
+        assert bool((np.abs(np.clip(x, -448, 448) - (a + b) / 2) <= 0.05 * step + 1e-6).all()), \
+            "a differing code is not explained by a value on a rounding boundary"
+        if scale_for > 448:
+            assert np.any(np.abs(table[got]) == 448.0), "expected saturated values"
+        assert abs(float(amax.item()) - amax_ref) <= 1e-4 * amax_ref
+        # a second call with a smaller result must leave the running maximum where it is
+        ctx.gemm_bf16_tn_fused_fp8out(dA, dB, out_scale, out=full[:, :N], amax=amax, alpha=0.5,
+                                      activation=activation, **dev_kw)
+        ctx.status()
+        if not kw:
+            assert abs(float(amax.item()) - amax_ref) <= 1e-4 * amax_ref
 
 
 def test_scatter_to_several_destinations_on_one_gpu(ctx, oracle_mod):

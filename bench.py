@@ -350,8 +350,15 @@ def run_ours(args):
         bias_d = torch.randn(N, generator=torch.Generator().manual_seed(1)).cuda() if "bias" in mode else None
         res_d = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda") if "res" in mode else None
         act = "gelu" if "gelu" in mode else ("relu" if "relu" in mode else "none")
-        step = lambda i: ctx.gemm_bf16_tn_fused(dA, dBs[i % len(dBs)], out=dC, alpha=alpha, bias=bias_d,
-                                                residual=res_d, activation=act)
+        if "fp8out" in mode:
+            dC8 = torch.empty((M, N), dtype=torch.float8_e4m3fn, device="cuda")
+            amax_d = torch.zeros(1, dtype=torch.float32, device="cuda")
+            step = lambda i: ctx.gemm_bf16_tn_fused_fp8out(dA, dBs[i % len(dBs)], 16.0, out=dC8, amax=amax_d,
+                                                           alpha=alpha, bias=bias_d, residual=res_d,
+                                                           activation=act)
+        else:
+            step = lambda i: ctx.gemm_bf16_tn_fused(dA, dBs[i % len(dBs)], out=dC, alpha=alpha, bias=bias_d,
+                                                    residual=res_d, activation=act)
     elif G:
         step = lambda i: ctx.gemm_bf16_tn_grouped(dA, dBs[i % len(dBs)], d_rows, out=dC, alpha=alpha)
     else:
@@ -568,7 +575,7 @@ def main():
     ap.add_argument("--fused-allgather", action="store_true",
                     help="N > 1: also time the GEMM whose epilogue stores its column block into every "
                          "GPU's full-width C (peer writes over NVLink instead of a collective)")
-    ap.add_argument("--fused-epilogue", default="", choices=["", "none", "bias", "relu", "gelu", "bias_gelu", "bias_res_gelu"],
+    ap.add_argument("--fused-epilogue", default="", choices=["", "none", "bias", "relu", "gelu", "bias_gelu", "bias_res_gelu", "fp8out", "bias_gelu_fp8out"],
                     help="time the bf16 GEMM with this epilogue fused in (patina_gemm_bf16_tn_fused) instead of the plain one")
     ap.add_argument("--allgather", action="store_true",
                     help="N > 1: also time the optional NCCL all-gather of the C column shards")

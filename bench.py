@@ -96,6 +96,9 @@ NCU_DRAM_TRAFFIC_BYTES = {
     "skinny_m64": 476_598_016,
     # profiles/gemm_tn_kernel_fp8_8192_pair512x256.md
     "fp8_tn_8192": 434_516_224,
+    # profiles/gemm_tn_kernel_grouped_bf16_moe.md
+    "moe_grouped_64x2048x4096": 1_176_533_696,
+    "moe_grouped_8x14336x4096": 2_069_426_128,
 }
 
 

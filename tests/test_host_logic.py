@@ -99,6 +99,36 @@ def test_plan_variants():
     assert (p.tile_m, p.tmem_cols, p.block) == (512, 512, 320)
 
 
+def test_planner_picks_match_what_was_measured_fastest():
+    """The planner's time model (tile speed x waves, a partly filled last wave costing less)
+    against shapes whose alternatives were timed on a B200: the pick must be the measured
+    winner. Tile widths in steps of 16 columns: every stage stays a whole number of 1 KB
+    swizzle atoms and the instruction's N a multiple of 16."""
+    picks = {
+        (8192, 8192, 8192): (2, 2, 256),      # 6.92 waves of 512 x 256
+        (4096, 4096, 4096): (2, 2, 240),      # 144 tiles = two waves of 74 pairs instead of 128 + idle
+        (8192, 3584, 8192): (2, 2, 208),      # 1/8 of a 28672-wide projection: 322 vs 331 (224) vs 359 us (256)
+        (8192, 1792, 4096): (2, 2, 208),
+        (8192, 14336, 4096): (2, 2, 240),
+        (8192, 4096, 4096): (2, 1, 256),      # 256 x 256 pair tiles fill 6.92 waves; 512 x 256 only 3.46
+        (8192, 512, 4096): (2, 1, 256),
+    }
+    for shape, want in picks.items():
+        p = L.plan(L.IN_BF16, L.OUT_BF16, *shape)
+        assert (p.cta_group, p.m_sub, p.block_n) == want, (shape, (p.cta_group, p.m_sub, p.block_n))
+        assert p.stage_bytes % 1024 == 0 and p.block_n % 16 == 0
+        assert p.expect_tx_bytes == p.cta_group * p.stage_bytes
+        assert p.smem_bytes <= 232448
+    # every width is reachable by an explicit request and keeps the same invariants
+    for bn in (256, 240, 224, 208, 192, 176, 160, 128):
+        p = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192, L.GemmConfig(2, bn, 0, 0, 0, 2))
+        assert p.block_n == bn and p.tiles_n == -(-8192 // bn) and p.stage_bytes == 2 * 16384 + bn // 2 * 128
+        assert p.tmem_cols == 512 and p.smem_bytes <= 232448
+    # e4m3 output (fused epilogue with scale and amax) has its own kernels
+    p = L.plan(L.IN_BF16, L.OUT_E4M3, 8192, 14336, 4096)
+    assert (p.cta_group, p.m_sub, p.block_n) == (2, 1, 256)
+
+
 def test_argument_validation(built_lib):
     ok = dict(in_type=L.IN_BF16, out_type=L.OUT_BF16, A=0x1000, lda=64, B=0x2000, ldb=64, Cp=0x3000,
               ldc=64, M=32, N=64, K=64)

@@ -527,6 +527,31 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   return PATINA_GEMM_OK;
 }
 
+// Clusters of this kernel that can be resident at once (cached per kernel). A persistent grid
+// must not exceed it, or the late clusters would start their tile lists after the others finish.
+int resident_clusters(const KernelEntry* k, int num_sms, int* cache) {
+  if (*cache != 0) return *cache;
+  cudaLaunchConfig_t qc{};
+  qc.gridDim = dim3((unsigned)(num_sms / k->cta_group) * k->cta_group, 1, 1);
+  qc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
+  qc.dynamicSmemBytes = k->smem_bytes;
+  cudaLaunchAttribute qa[1];
+  qa[0].id = cudaLaunchAttributeClusterDimension;
+  qa[0].val.clusterDim.x = (unsigned)k->cta_group;
+  qa[0].val.clusterDim.y = 1;
+  qa[0].val.clusterDim.z = 1;
+  qc.attrs = qa;
+  qc.numAttrs = 1;
+  int n = 0;
+  cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(k->fn), &qc);
+  if (qe != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = num_sms / k->cta_group;
+  }
+  *cache = n;
+  return n;
+}
+
 int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A, int64_t lda,
                 const void* B, int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                 float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream,
@@ -599,29 +624,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   }
 
   if (k->cta_group > 1) {
-    // A persistent grid must not exceed what can be resident at once, or the
-    // late clusters would start their tile lists after the others finish.
-    if (ctx->max_clusters[ki] == 0) {
-      cudaLaunchConfig_t qc{};
-      qc.gridDim = dim3((unsigned)(ctx->num_sms / k->cta_group) * k->cta_group, 1, 1);
-      qc.blockDim = dim3(plan.block, 1, 1);
-      qc.dynamicSmemBytes = k->smem_bytes;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = (unsigned)k->cta_group;
-      qa[0].val.clusterDim.y = 1;
-      qa[0].val.clusterDim.z = 1;
-      qc.attrs = qa;
-      qc.numAttrs = 1;
-      int n = 0;
-      cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(k->fn), &qc);
-      if (qe != cudaSuccess || n <= 0) {
-        cudaGetLastError();
-        n = ctx->num_sms / k->cta_group;
-      }
-      ctx->max_clusters[ki] = n;
-    }
-    const uint32_t cap = (uint32_t)ctx->max_clusters[ki] * k->cta_group;
+    const uint32_t cap = (uint32_t)resident_clusters(k, ctx->num_sms, &ctx->max_clusters[ki]) * k->cta_group;
     if (plan.grid > cap) plan.grid = cap;
   }
 
@@ -744,27 +747,8 @@ int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const voi
   }
   uint32_t slots = (uint32_t)(ctx->num_sms / k->cta_group);
   if (k->cta_group > 1) {
-    if (ctx->grouped_max_clusters[ki] == 0) {
-      cudaLaunchConfig_t qc{};
-      qc.gridDim = dim3((unsigned)slots * k->cta_group, 1, 1);
-      qc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
-      qc.dynamicSmemBytes = k->smem_bytes;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = (unsigned)k->cta_group;
-      qa[0].val.clusterDim.y = 1;
-      qa[0].val.clusterDim.z = 1;
-      qc.attrs = qa;
-      qc.numAttrs = 1;
-      int n = 0;
-      cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(k->fn), &qc);
-      if (qe != cudaSuccess || n <= 0) {
-        cudaGetLastError();
-        n = (int)slots;
-      }
-      ctx->grouped_max_clusters[ki] = n;
-    }
-    if ((uint32_t)ctx->grouped_max_clusters[ki] < slots) slots = (uint32_t)ctx->grouped_max_clusters[ki];
+    const uint32_t cap = (uint32_t)resident_clusters(k, ctx->num_sms, &ctx->grouped_max_clusters[ki]);
+    if (cap < slots) slots = cap;
   }
   if (cfg && cfg->max_ctas > 0 && (uint32_t)(cfg->max_ctas / k->cta_group) < slots)
     slots = (uint32_t)(cfg->max_ctas / k->cta_group);

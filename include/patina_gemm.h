@@ -180,6 +180,15 @@ int patina_gemm_bf16_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_t l
                                 int n_groups, int64_t total_rows, int64_t N, int64_t K, float alpha,
                                 const PatinaGemmConfig* config, void* stream);
 
+/* The same for e4m3 inputs with bf16 output: C_g = scale_a * group_scale_b[g] * (A_g * B_g^T).
+ * group_scale_b is a DEVICE array of n_groups floats (each group's weight scale), or NULL for
+ * a common factor of 1. */
+int patina_gemm_fp8e4m3_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                   int64_t ldb, void* C, int64_t ldc, const int32_t* group_rows,
+                                   int n_groups, int64_t total_rows, int64_t N, int64_t K, float scale_a,
+                                   const float* group_scale_b, const PatinaGemmConfig* config,
+                                   void* stream);
+
 /* Buffers for the scatter above (no counterpart in the reference). peer_alloc gives device
  * memory of this context's GPU plus a 64-byte handle that another PROCESS on the node passes
  * to peer_open (with its own context) to get a pointer its GPU can write through NVLink.

@@ -97,13 +97,16 @@ const KernelEntry kKernels[] = {
 constexpr int kNumKernels = sizeof(kKernels) / sizeof(kKernels[0]);
 
 // Grouped launches (bf16 -> bf16): the same kernel, compiled with the group tables.
-#define PATINA_GROUPED(G, MS, BN, S)                                                          \
-  { G, MS, BN, S, kBF16, kOutBF16, gemm_tn_kernel<G, MS, BN, S, kBF16, kOutBF16, false, true>, \
-    nullptr, GemmTraits<G, MS, BN, S, kBF16, kOutBF16>::kSmemBytes + kGroupTableBytes }
+#define PATINA_GROUPED(G, MS, BN, S, IN)                                                 \
+  { G, MS, BN, S, IN, kOutBF16, gemm_tn_kernel<G, MS, BN, S, IN, kOutBF16, false, true>, \
+    nullptr, GemmTraits<G, MS, BN, S, IN, kOutBF16>::kSmemBytes + kGroupTableBytes }
 const KernelEntry kGroupedKernels[] = {
-    PATINA_GROUPED(2, 2, 256, 4),  // 512 x 256 per pair: groups of many hundred rows
-    PATINA_GROUPED(2, 1, 256, 6),  // 256 x 256 per pair
-    PATINA_GROUPED(1, 1, 256, 4),  // 128 x 256: small groups lose least to their ragged last block
+    PATINA_GROUPED(2, 2, 256, 4, kBF16),  // 512 x 256 per pair: groups of many hundred rows
+    PATINA_GROUPED(2, 1, 256, 6, kBF16),  // 256 x 256 per pair
+    PATINA_GROUPED(1, 1, 256, 4, kBF16),  // 128 x 256: small groups lose least to their ragged last block
+    PATINA_GROUPED(2, 2, 256, 4, kE4M3),
+    PATINA_GROUPED(2, 1, 256, 6, kE4M3),
+    PATINA_GROUPED(1, 1, 256, 4, kE4M3),
 };
 constexpr int kNumGroupedKernels = sizeof(kGroupedKernels) / sizeof(kGroupedKernels[0]);
 static_assert(GemmTraits<2, 2, 256, 4, kBF16, kOutBF16>::kSmemBytes + kGroupTableBytes <= kMaxDynSmem,
@@ -678,9 +681,10 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
 
 // One launch for n_groups GEMMs that share N and K: A and C hold the groups' rows one after
 // another, B one [N, K] block per group, the row counts live in device memory.
-int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B, int64_t ldb,
-                   void* C, int64_t ldc, const int32_t* group_rows, int n_groups, int64_t total_rows,
-                   int64_t N, int64_t K, float alpha, const PatinaGemmConfig* cfg, cudaStream_t stream) {
+int launch_grouped(PatinaGemmContext* ctx, int in_type, const void* A, int64_t lda, const void* B,
+                   int64_t ldb, void* C, int64_t ldc, const int32_t* group_rows, int n_groups,
+                   int64_t total_rows, int64_t N, int64_t K, float alpha, const float* group_alpha,
+                   const PatinaGemmConfig* cfg, cudaStream_t stream) {
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   if (n_groups < 0 || n_groups > (int)kMaxGroups)
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
@@ -691,8 +695,10 @@ int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const voi
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "n_groups * N exceeds 2^31-1");
   std::string err;
   // A is [total_rows, K]; B is [n_groups * N, K]; C is [total_rows, N]
-  int rc = validate_args(kBF16, kOutBF16, A, lda, B, ldb, C, ldc, total_rows, N, K, &err);
+  int rc = validate_args(in_type, kOutBF16, A, lda, B, ldb, C, ldc, total_rows, N, K, &err);
   if (rc != PATINA_GEMM_OK) return set_error(ctx, rc, err);
+  if (group_alpha && (reinterpret_cast<uintptr_t>(group_alpha) & 3u))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "the per-group factors are not 4-byte aligned");
   if (total_rows == 0 || N == 0 || n_groups == 0) return PATINA_GEMM_OK;
   DeviceGuard guard(ctx->device);
   if (!guard.ok) return set_error(ctx, PATINA_GEMM_ERR_CUDA, "cudaSetDevice failed");
@@ -712,7 +718,8 @@ int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const voi
   const KernelEntry* k = nullptr;
   int ki = -1;
   for (int i = 0; i < kNumGroupedKernels; ++i)
-    if (kGroupedKernels[i].cta_group == want_group && kGroupedKernels[i].m_sub == want_msub) {
+    if (kGroupedKernels[i].in_type == in_type && kGroupedKernels[i].cta_group == want_group &&
+        kGroupedKernels[i].m_sub == want_msub) {
       k = &kGroupedKernels[i];
       ki = i;
     }
@@ -720,17 +727,18 @@ int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const voi
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
                      fmt("no grouped kernel for cta_group=%d m_sub=%d", want_group, want_msub));
 
-  const uint32_t kelems = kBlockKBytes / 2;
+  const uint32_t ib = input_bytes(in_type);
+  const uint32_t kelems = kBlockKBytes / ib;
   const uint32_t tile_m = 128u * k->cta_group * k->m_sub;
   const uint32_t tiles_n = ceil_div(N, k->block_n);
   // every group may end with one partly filled row block
   const uint64_t max_tiles = ((uint64_t)(total_rows / tile_m) + (uint64_t)n_groups) * tiles_n;
   CUtensorMap tm_a, tm_b;
   CStoreMaps tm_c;
-  rc = get_tensor_map(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)K,
+  rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)total_rows, (uint64_t)K,
                       (uint64_t)lda, kCtaRows, kelems, &tm_a);
   if (rc != PATINA_GEMM_OK) return rc;
-  rc = get_tensor_map(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)n_groups * (uint64_t)N,
+  rc = get_tensor_map(ctx, B, tmap_in_type(in_type), ib, (uint64_t)n_groups * (uint64_t)N,
                       (uint64_t)K, (uint64_t)ldb, (uint32_t)(k->block_n / k->cta_group), kelems, &tm_b);
   if (rc != PATINA_GEMM_OK) return rc;
   rc = get_tensor_map(ctx, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)N,
@@ -767,6 +775,7 @@ int launch_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const voi
   p.alpha = alpha;
   p.n_dests = 1;
   p.group_rows = group_rows;
+  p.group_alpha = group_alpha;
   p.n_groups = (uint32_t)n_groups;
   p.c_dests[0] = C;
   p.ldc = ldc;
@@ -1012,8 +1021,17 @@ int patina_gemm_bf16_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_t l
                                 int64_t ldb, void* C, int64_t ldc, const int32_t* group_rows,
                                 int n_groups, int64_t total_rows, int64_t N, int64_t K, float alpha,
                                 const PatinaGemmConfig* config, void* stream) {
-  return launch_grouped(ctx, A, lda, B, ldb, C, ldc, group_rows, n_groups, total_rows, N, K, alpha,
-                        config, static_cast<cudaStream_t>(stream));
+  return launch_grouped(ctx, kBF16, A, lda, B, ldb, C, ldc, group_rows, n_groups, total_rows, N, K,
+                        alpha, nullptr, config, static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_fp8e4m3_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B,
+                                   int64_t ldb, void* C, int64_t ldc, const int32_t* group_rows,
+                                   int n_groups, int64_t total_rows, int64_t N, int64_t K, float scale_a,
+                                   const float* group_scale_b, const PatinaGemmConfig* config,
+                                   void* stream) {
+  return launch_grouped(ctx, kE4M3, A, lda, B, ldb, C, ldc, group_rows, n_groups, total_rows, N, K,
+                        scale_a, group_scale_b, config, static_cast<cudaStream_t>(stream));
 }
 
 // ---- buffers that other processes on the node can write ------------------------------------

@@ -66,6 +66,8 @@ struct GemmParams {
   // grouped launch (kernels instantiated with kGrouped): A and C hold the groups' rows one
   // after another, B holds one [N, K] block per group; M above is the total row count
   const int32_t* group_rows;  // device array, rows of A and C per group
+  const float* group_alpha;   // device array, one more factor per group (e.g. an expert's weight
+                              // scale for fp8 inputs), or null
   uint32_t n_groups;          // <= kMaxGroups
   // C itself (every destination), for boxes the TMA store cannot clip: TMA stores clip at
   // 16-byte granularity, so a box that crosses column N when N * element size is not a
@@ -459,6 +461,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             cta_rank * kCtaRows + q * kStoreBoxRows;
       // A grouped launch must not write past its group: a box beyond the group's last row is
       // dropped, one that straddles it is written row by row from the registers.
+      float tile_alpha = p.alpha;
+      if constexpr (kGrouped) {
+        if (p.group_alpha != nullptr) tile_alpha *= __ldg(p.group_alpha + grp);
+      }
       const bool box_outside = row0 >= c.row_end;
       const bool box_straddles = kGrouped && !box_outside && row0 + kStoreBoxRows > c.row_end;
       const uint32_t col0 = c.n * BN;
@@ -561,7 +567,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
           }
         }
-        const float out_scale = (kOut == kOutE4M3) ? p.out_scale : (kFused ? 1.0f : p.alpha);
+        const float out_scale = (kOut == kOutE4M3) ? p.out_scale : (kFused ? 1.0f : tile_alpha);
         static_assert(!kGrouped || kOut == kOutBF16, "grouped launches write bf16");
         if (box_outside) return;
         {

@@ -231,15 +231,11 @@ class GemmContext:
         if rc != _l.OK:
             self._raise(rc)
 
-    def gemm_bf16_tn_grouped(self, A, B, group_rows, out=None, alpha=1.0, config=None):
-        """One launch for the groups of a ragged batch: out[rows of group g] = alpha *
-        A[rows of group g] @ B[g]^T. A: [total_rows, K] bf16 with the groups' rows one after
-        another; B: [n_groups, N, K] (or [n_groups * N, K]) bf16; group_rows: int32 CUDA tensor
-        of n_groups row counts (it stays on the device: nothing here synchronises)."""
+    def _grouped(self, A, B, group_rows, out, in_dtypes):
         if not (A.is_cuda and B.is_cuda and group_rows.is_cuda):
             raise PatinaGemmError(_l.ERR_INVALID_ARG, "A, B and group_rows must be CUDA tensors (no CPU path)")
-        if A.dtype != torch.bfloat16 or B.dtype != torch.bfloat16 or group_rows.dtype != torch.int32:
-            raise PatinaGemmError(_l.ERR_INVALID_ARG, "A and B must be bf16, group_rows int32")
+        if A.dtype not in in_dtypes or B.dtype != A.dtype or group_rows.dtype != torch.int32:
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, f"A and B must be {in_dtypes[0]}, group_rows int32")
         n_groups = int(group_rows.numel())
         total_rows, K = A.shape
         if B.dim() == 3:
@@ -257,9 +253,32 @@ class GemmContext:
         lda = A.stride(0) if total_rows > 1 else max(K, 1)
         ldb = B2.stride(0) if B2.shape[0] > 1 else max(K, 1)
         ldc = out.stride(0) if total_rows > 1 else max(N, 1)
+        return B2, out, (A.data_ptr(), lda, B2.data_ptr(), ldb, out.data_ptr(), ldc, group_rows.data_ptr(),
+                         n_groups, total_rows, N, K)
+
+    def gemm_bf16_tn_grouped(self, A, B, group_rows, out=None, alpha=1.0, config=None):
+        """One launch for the groups of a ragged batch: out[rows of group g] = alpha *
+        A[rows of group g] @ B[g]^T. A: [total_rows, K] bf16 with the groups' rows one after
+        another; B: [n_groups, N, K] (or [n_groups * N, K]) bf16; group_rows: int32 CUDA tensor
+        of n_groups row counts (it stays on the device: nothing here synchronises)."""
+        _, out, args = self._grouped(A, B, group_rows, out, (torch.bfloat16,))
         rc = self._lib.patina_gemm_bf16_tn_grouped(
-            self._h, A.data_ptr(), lda, B2.data_ptr(), ldb, out.data_ptr(), ldc, group_rows.data_ptr(),
-            n_groups, total_rows, N, K, float(alpha),
+            self._h, *args, float(alpha), C.byref(config) if config is not None else None,
+            _stream_ptr(self.device))
+        if rc != _l.OK:
+            self._raise(rc)
+        return out
+
+    def gemm_fp8e4m3_tn_grouped(self, Aq, Bq, group_rows, scale_a: float, group_scale_b=None, out=None,
+                                config=None):
+        """The grouped launch for float8_e4m3fn operands, bf16 result: out[group g] = scale_a *
+        group_scale_b[g] * Aq[group g] @ Bq[g]^T (group_scale_b: float32 CUDA tensor or None)."""
+        if group_scale_b is not None and (group_scale_b.dtype != torch.float32 or not group_scale_b.is_cuda
+                                          or group_scale_b.numel() != group_rows.numel()):
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "group_scale_b must be a float32 CUDA tensor, one per group")
+        _, out, args = self._grouped(Aq, Bq, group_rows, out, (torch.float8_e4m3fn, torch.uint8))
+        rc = self._lib.patina_gemm_fp8e4m3_tn_grouped(
+            self._h, *args, float(scale_a), group_scale_b.data_ptr() if group_scale_b is not None else None,
             C.byref(config) if config is not None else None, _stream_ptr(self.device))
         if rc != _l.OK:
             self._raise(rc)

@@ -22,7 +22,7 @@ SYMBOLS = (
     "patina_gemm_plan", "patina_gemm_smem_desc", "patina_gemm_idesc",
     "patina_gemm_k_advance_units", "patina_gemm_tmem_lane_offset", "patina_gemm_tile_coord",
     "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_range",
-    "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped",
+    "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped", "patina_gemm_fp8e4m3_tn_grouped",
     "patina_gemm_peer_alloc",
     "patina_gemm_peer_open", "patina_gemm_peer_close", "patina_gemm_peer_free",
 )
@@ -114,6 +114,8 @@ def load() -> C.CDLL:
     L.patina_gemm_bf16_tn_fused_fp8out.argtypes = gemm_args + [f32, C.POINTER(GemmEpilogue), f32, vp, vp]
     L.patina_gemm_bf16_tn_grouped.argtypes = [vp, vp, i64, vp, i64, vp, i64, vp, i32, i64, i64, i64, f32,
                                               C.POINTER(GemmConfig), vp]
+    L.patina_gemm_fp8e4m3_tn_grouped.argtypes = [vp, vp, i64, vp, i64, vp, i64, vp, i32, i64, i64, i64, f32,
+                                                 vp, C.POINTER(GemmConfig), vp]
     L.patina_gemm_bf16_tn_fused.argtypes = gemm_args + [f32, C.POINTER(GemmEpilogue), vp]
     L.patina_gemm_peer_alloc.argtypes = [vp, C.c_size_t, C.POINTER(vp), C.c_char_p]
     L.patina_gemm_peer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]

@@ -117,6 +117,35 @@ def test_grouped_counts_beyond_the_buffer_are_dropped(ctx, oracle_mod):
     assert bool((guard[total:] == 3.0).all())
 
 
+def test_grouped_fp8_with_a_scale_per_group(ctx, oracle_mod):
+    """e4m3 operands, one weight scale per group: C_g = sa * sb[g] * (A_g B_g^T), against the
+    oracle on the dequantised operands (the bound of the fp8 configurations: elementwise
+    1e-2 * max|C_ref|, relative Frobenius 1e-3 after bf16 rounding of the reference)."""
+    from patina_b200 import inputs
+    rows, N, K = [200, 3, 0, 321], 392, 336
+    total = sum(rows)
+    Aq, sa, _, _ = inputs.make_fp8_operands(total, 8, K)
+    Bqs, sbs = [], []
+    for g in range(len(rows)):
+        _, _, Bq, sb = inputs.make_fp8_operands(8, N, K, seed=40 + g)
+        Bqs.append(Bq)
+        sbs.append(sb * (1.0 + g))            # clearly different factors per group
+    Bq = torch.stack(Bqs)
+    d_rows = torch.tensor(rows, dtype=torch.int32, device="cuda")
+    d_sb = torch.tensor(sbs, dtype=torch.float32, device="cuda")
+    w8 = lambda t: oracle_mod.e4m3_bits_to_f32(t.view(torch.uint8).numpy())
+    for name, cfg in configs().items():
+        out = ctx.gemm_fp8e4m3_tn_grouped(Aq.cuda(), Bq.cuda(), d_rows, sa, d_sb, config=cfg)
+        ctx.status()
+        r0 = 0
+        for g, r in enumerate(rows):
+            if r:
+                ref = oracle_mod.ref_gemm_tn(w8(Aq[r0:r0 + r]), w8(Bq[g]))
+                check_norm(oracle_mod, out[r0:r0 + r], oracle_mod.scale_round_bf16(ref, sa * sbs[g]),
+                           f"{name} fp8 group {g}")
+            r0 += r
+
+
 def test_grouped_invalid_arguments(ctx):
     import patina_b200
     A = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")

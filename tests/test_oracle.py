@@ -160,3 +160,23 @@ def test_fused_epilogue_reference(oracle_mod):
         assert np.mean(got != exp) < 0.02
     with pytest.raises(ValueError):
         oracle_mod.fused_epilogue_bf16(ref, activation="tanh")
+
+
+def test_fp8_output_epilogue_restatement(oracle_mod):
+    """oracle.fused_epilogue_e4m3 (the expected output of the fp8-output entry point): its codes
+    are the round-to-nearest-even, saturating e4m3 of out_scale * y, checked against torch's own
+    float8_e4m3fn conversion where that is defined (|x| <= 448), and against +-448 beyond."""
+    import torch
+    rng = np.random.default_rng(12)
+    ref = rng.normal(size=(37, 53)) * 3.0
+    bias = rng.normal(size=53).astype(np.float32)
+    codes, amax, y = oracle_mod.fused_epilogue_e4m3(ref, 40.0, alpha=1.5, bias=bias, activation="relu")
+    want_y = np.maximum(1.5 * ref + bias.astype(np.float64)[None, :], 0.0)
+    assert np.allclose(y, want_y, rtol=0, atol=0)
+    assert amax == float(np.abs(want_y).max())
+    x = (want_y * 40.0).astype(np.float32)
+    inside = np.abs(x) <= 448.0
+    t = torch.from_numpy(x).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(codes[inside], t[inside])
+    assert inside.sum() < x.size, "the case should also exercise saturation"
+    assert np.all(codes[~inside & (x > 0)] == 0x7E) and np.all(codes[~inside & (x < 0)] == 0xFE)

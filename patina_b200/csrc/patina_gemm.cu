@@ -309,7 +309,7 @@ struct PatinaGemmContext {
   uint32_t sk_burst = 4;
   // copy streams and events of patina_gemm_host's pipelined form
   cudaStream_t s_in = nullptr, s_out = nullptr;
-  cudaEvent_t ev[3 + 2 * 8] = {};
+  cudaEvent_t ev[kHostEvents] = {};
   // device staging for patina_gemm_host
   void* d_a = nullptr;
   void* d_b = nullptr;

@@ -35,10 +35,6 @@
 #include "patina_desc.h"
 #include "patina_ptx.cuh"
 
-#ifndef PATINA_L2_HINTS
-#define PATINA_L2_HINTS 0   // 0: no hints; 1: A evict-last, B evict-first; 2: A evict-last only
-#endif
-
 namespace patina {
 
 // Where a finished sub-tile of C is stored: one tensor map per destination. One destination is
@@ -351,14 +347,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
-#if PATINA_L2_HINTS
-      // Inside a band of group_m tile rows, the rows of A are reused by every wave while a
-      // panel of B is used by the tiles of one wave only.
-      const uint64_t pol_a = ptx::l2_policy_evict_last();
-#if PATINA_L2_HINTS == 1
-      const uint64_t pol_b = ptx::l2_policy_evict_first();
-#endif
-#endif
       uint32_t grp = 0;
       for (uint32_t t = cluster_id; t < num_tiles; t += num_clusters) {
         const TileSpot c = locate(t, grp);
@@ -380,20 +368,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, 2u * stage_tx);
 #pragma unroll
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-              if (ms < n_sub) {
-#if PATINA_L2_HINTS
-                ptx::tma_load_2d_pair_hint(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
-                                           a_row + (int32_t)(ms * kCtaRows * kCtaGroup), pol_a);
-#else
+              if (ms < n_sub)
                 ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
-                                      a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
-#endif
-              }
-#if PATINA_L2_HINTS == 1
-            ptx::tma_load_2d_pair_hint(sb, &tm_b, leader_full + 8u * s, k0, b_row, pol_b);
-#else
+                                    a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
-#endif
           } else {
             ptx::mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
 #pragma unroll

@@ -23,7 +23,8 @@
  * Alignment rules (TMA): A, B, C base addresses 16-byte aligned;
  * lda, ldb, ldc times the element size a multiple of 16 bytes; lda,ldb >= K,
  * ldc >= N. M, N, K are otherwise free (ragged edges are zero-filled on load
- * and clipped on store). M == 0 or N == 0 is a no-op; K == 0 stores zeros.
+ * and clipped on store: no element of C outside [M, N] is written, whatever
+ * N's remainder). M == 0 or N == 0 is a no-op; K == 0 stores zeros.
  */
 #ifndef PATINA_GEMM_H
 #define PATINA_GEMM_H
@@ -46,12 +47,13 @@ enum {
 };
 
 enum { PATINA_IN_F16 = 0, PATINA_IN_BF16 = 1, PATINA_IN_E4M3 = 2 };
-enum { PATINA_OUT_BF16 = 0, PATINA_OUT_F32 = 1 };
+enum { PATINA_OUT_BF16 = 0, PATINA_OUT_F32 = 1, PATINA_OUT_E4M3 = 2 /* fused epilogue only */ };
 
 /* Tile configuration. Zero in any field means "choose for me". */
 typedef struct PatinaGemmConfig {
   int32_t cta_group; /* 1 = one CTA per tile; 2 = CTA pair (tcgen05 cta_group::2) */
-  int32_t block_n;   /* tile width: 128 or 256 */
+  int32_t block_n;   /* tile width: 128 ... 256 in steps of 16 for pair tiles with m_sub = 2,
+                        128 or 256 otherwise */
   int32_t stages;    /* shared-memory ring depth */
   int32_t group_m;   /* scheduler band height in tiles */
   int32_t max_ctas;  /* cap on persistent CTAs (0 = number of SMs) */

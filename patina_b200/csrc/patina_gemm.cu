@@ -128,7 +128,7 @@ uint32_t ceil_div(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); 
 //    L2 bandwidth and power, not by any one SM;
 //  * for the same reason a partly filled last wave is cheaper than a full one: with half the
 //    clusters active each tile ran 29 % faster, so a wave filled to f costs about 0.55 + 0.45 f.
-double config_score(const KernelEntry& k, int64_t M, int64_t N, int num_sms) {
+double config_score(const KernelEntry& k, int64_t M, int64_t N, int64_t K, int num_sms) {
   const int64_t tile_m = 128 * k.cta_group * k.m_sub;
   const uint64_t tiles = (uint64_t)ceil_div(M, tile_m) * ceil_div(N, k.block_n);
   const uint64_t slots = (uint64_t)(num_sms / k.cta_group);
@@ -145,6 +145,12 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int num_sms) {
     if (k.in_type == kE4M3) speed *= 0.97;  // twice the MMA rate: the smaller tile falls back further
   } else {
     speed = k.block_n >= 256 ? 0.895 : 0.62;
+    // A single wave over a short K is mostly set-up, first loads and the epilogue, and a lone
+    // CTA has less of that than a pair (cluster launch, cross-CTA barriers): measured at
+    // 8192 x 512 x 4096, 128 single-CTA tiles take 25.6 us, 64 pair tiles 27.9 us (2048^3: 15.3
+    // vs 17.4 us); at K = 6144 the pair is ahead again (41.8 vs 44.0 us).
+    const uint64_t k_blocks = (uint64_t)ceil_div(K, kBlockKBytes / input_bytes(k.in_type));
+    if (waves == 1 && k_blocks <= 80 && k.block_n >= 256) speed *= 1.12;
   }
   const double tile_cost = (double)tile_m * (double)k.block_n / speed;  // per-tile time, area units
   const double time = tile_cost * ((double)(waves - 1) + 0.55 + 0.45 * last_fill);
@@ -191,7 +197,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (c.stages != 0 && k.stages != c.stages) continue;
       if (k.cta_group == 2 && num_sms < 2) continue;
       if (need_fused && !k.fn_fused) continue;
-      const double s = config_score(k, M, N, num_sms);
+      const double s = config_score(k, M, N, K, num_sms);
       if (s > best_score) {
         best_score = s;
         best = &k;

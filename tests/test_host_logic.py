@@ -111,7 +111,9 @@ def test_planner_picks_match_what_was_measured_fastest():
         (8192, 1792, 4096): (2, 2, 208),
         (8192, 14336, 4096): (2, 2, 240),
         (8192, 4096, 4096): (2, 1, 256),      # 256 x 256 pair tiles fill 6.92 waves; 512 x 256 only 3.46
-        (8192, 512, 4096): (2, 1, 256),
+        (8192, 512, 4096): (1, 1, 256),       # one wave, short K: 128 lone CTAs 25.6 us, 64 pairs 27.9 us
+        (8192, 512, 6144): (2, 1, 256),       # longer K: the pair is ahead again (41.8 vs 44.0 us)
+        (2048, 2048, 2048): (1, 1, 256),      # 15.3 vs 17.4 us
     }
     for shape, want in picks.items():
         p = L.plan(L.IN_BF16, L.OUT_BF16, *shape)

@@ -67,6 +67,10 @@ for _m in (16, 64, 128):
         "N split over the GPUs; 3 weight buffers in rotation (each larger than L2)",
         bound="hbm", scaling="strong", rotate=3)
 
+# One GPU's share of the widest projection when it is split over 8 GPUs, as a 1-GPU workload
+WORKLOADS["llm_proj_shard_3584x8192"] = _wl(
+    8192, 3584, 8192, "llm", "one GPU's share of the 28672 x 8192 projection split over 8 GPUs: bf16 TN "
+    "GEMM M=8192, N=3584, K=8192, activations N(0,1), weights N(0,0.02)", scaling="strong")
 for _m in (16, 64, 128):
     WORKLOADS[f"skinny_m{_m}_n3584"] = _wl(
         _m, 3584, 8192, "llm", f"one GPU's share of the decode-shaped GEMM split over 8 GPUs: M={_m}, "

@@ -145,16 +145,20 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int64_t K, int n
     if (k.in_type == kE4M3) speed *= 0.97;  // twice the MMA rate: the smaller tile falls back further
   } else {
     speed = k.block_n >= 256 ? 0.895 : 0.62;
-    // A single wave over a short K is mostly set-up, first loads and the epilogue, and a lone
-    // CTA has less of that than a pair (cluster launch, cross-CTA barriers): measured at
-    // 8192 x 512 x 4096, 128 single-CTA tiles take 25.6 us, 64 pair tiles 27.9 us (2048^3: 15.3
-    // vs 17.4 us); at K = 6144 the pair is ahead again (41.8 vs 44.0 us).
-    const uint64_t k_blocks = (uint64_t)ceil_div(K, kBlockKBytes / input_bytes(k.in_type));
-    if (waves == 1 && k_blocks <= 80 && k.block_n >= 256) speed *= 1.12;
   }
-  const double tile_cost = (double)tile_m * (double)k.block_n / speed;  // per-tile time, area units
-  const double time = tile_cost * ((double)(waves - 1) + 0.55 + 0.45 * last_fill);
-  return (double)M * (double)N / (time * (double)slots);
+  // Time in units of "one SM's share of one output element over one k-block at full speed";
+  // measured: 81 000 - 83 000 of them per microsecond at bf16 (a 128 x 256 tile's k-block takes
+  // 0.45 us on a lone CTA, a 256 x 256 tile's 0.41 us on a pair).
+  const double k_blocks = (double)ceil_div(K, kBlockKBytes / input_bytes(k.in_type));
+  const double per_sm_tile = (double)tile_m * (double)k.block_n / (speed * (double)k.cta_group);
+  const double mainloop = per_sm_tile * k_blocks * ((double)(waves - 1) + 0.55 + 0.45 * last_fill);
+  // What a launch costs besides: set-up, the first loads' latency, the last epilogue, teardown.
+  // A pair pays about 2 us more (cluster launch, barriers across the two CTAs): at
+  // 8192 x 512 x 4096 128 lone CTAs take 25.6 us and 64 pairs 27.9 us, at 2048^3 15.3 vs 17.4 us,
+  // at 1024^3 9.1 vs 11.0 us; from K = 6144 on the pair's faster mainloop wins again (41.8 vs
+  // 44.0 us).
+  const double fixed = (k.cta_group == 2 ? 8.0 : 6.0) * 82000.0;
+  return 1.0e12 / (mainloop + fixed);
 }
 
 int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
@@ -412,33 +416,39 @@ bool streamk_supported(int in_type, int out_type, int64_t M) {
   return out_type == kOutBF16 && (in_type == kBF16 || in_type == kE4M3) && M >= 1 && M <= 128;
 }
 
+constexpr uint64_t kSkMinUnits = 8;
+
 SkPlan make_sk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms) {
   SkPlan s{};
   s.m_pad = (uint32_t)((M + 15) / 16 * 16);
   s.tiles = ceil_div(N, kSkTileRows);
   s.k_blocks = ceil_div(K, kBlockKBytes / input_bytes(in_type));
   s.units = (uint64_t)s.tiles * s.k_blocks;
-  s.grid = (uint32_t)((uint64_t)num_sms < s.units ? (uint64_t)num_sms : s.units);
+  // every CTA gets at least kSkMinUnits units, so that its set-up is paid for by some streaming
+  const uint64_t want = (s.units + kSkMinUnits - 1) / kSkMinUnits;
+  s.grid = (uint32_t)((uint64_t)num_sms < want ? (uint64_t)num_sms : want);
   s.max_contrib = streamk_max_contrib(s.units, s.grid, s.k_blocks);
   s.partial_bytes = (uint64_t)s.tiles * s.max_contrib * s.m_pad * 128ull * sizeof(float);
   s.counter_bytes = (uint64_t)s.tiles * sizeof(uint32_t);
   return s;
 }
 
-// Heuristic for the automatic choice: skinny M, and enough (tile, k-block) units that cutting
-// K across CTAs pays (otherwise the large-tile kernel's 128-wide tiles already fill the GPU).
+// The automatic choice between the two kernels for M <= 128.
+//  * Many weight tiles (N = 28672, K = 8192): stream-K leads for M <= 32 (75.3 vs 77 us at
+//    M = 16); from M = 64 on the X slab is as large as the W slab and the large-tile kernel,
+//    which loads one X slab per 256 rows of W, is ahead -- as long as it has a tile for most SMs.
+//  * Few weight tiles (a narrow shard, or the reference's own 128 x 128 x K shape) leave the
+//    large-tile kernel on a handful of SMs, each pulling its whole K through one SM's L2 port:
+//    128 x 128 x 8192 takes 45 us there and 10 us when K is cut across CTAs (128 x 1024 x 4096:
+//    22 vs 9.6 us; 32 x 2048 x 2048: 12.8 vs 8.6 us). Only a short K (16 k-blocks: 8.6 vs 9.2 us)
+//    is not worth cutting.
 bool streamk_preferred(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
   if (!streamk_supported(in_type, out_type, M)) return false;
-  // Measured at N = 28672, K = 8192: stream-K leads for M <= 32 (5.8 vs 5.6 TB/s at M = 16);
-  // from M = 64 on the X slab is as large as the W slab and the large-tile kernel, which loads
-  // one X slab per 256 rows of W, is ahead (5.7-5.8 TB/s) -- as long as it has a tile for most
-  // SMs. A narrow shard (N / 8 = 3584 columns is 14 tiles of 256) leaves it starved: 14 CTAs
-  // cannot pull the HBM bandwidth, and cutting K across all SMs wins again.
   const SkPlan s = make_sk_plan(in_type, M, N, K, num_sms);
-  if (s.units < 4ull * (uint64_t)num_sms) return false;
-  if (M <= 32) return true;
+  if (M <= 32 && s.units >= 4ull * (uint64_t)num_sms) return true;
   const uint64_t large_tiles = (uint64_t)ceil_div(N, 256);  // one 128-row tile covers all of M
-  return large_tiles * 10 < (uint64_t)num_sms * 7;
+  const bool starved = large_tiles * 10 < (uint64_t)num_sms * 7;
+  return starved && s.k_blocks >= 24;
 }
 
 template <int kIn>

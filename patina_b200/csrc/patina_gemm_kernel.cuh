@@ -708,7 +708,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
       }
     }
-    if (lane == 0) ptx::tma_store_wait_all<0>();
+    // The staging buffers must have been read before the CTA gives its shared memory back; the
+    // writes themselves are complete, as every write of a grid, when the grid completes.
+    if (lane == 0) ptx::tma_store_wait_read<0>();
   }
 
   // ---------------------------------------------------------------- teardown

@@ -85,6 +85,29 @@ def test_run_gemm_mirror(oracle_mod, golden):
         patina_b200.run_gemm(48, np.zeros((128, 48), np.float32), np.zeros((128, 48), np.float32))
 
 
+@pytest.mark.parametrize("M,N,K", [(100, 130, 96), (300, 261, 200), (128, 127, 64)])
+def test_f16_f32out_ragged_shapes(ctx, oracle_mod, M, N, K):
+    """The reference's types (f16 in, f32 out) on shapes its kernel cannot run: ragged M, N, K, the
+    reference's own pass rule against its CPU GEMM restated, every kernel of that type pair; N is
+    not a multiple of 4 columns, so the last store box of a row is written from the registers,
+    and not one column behind N may change."""
+    from patina_b200 import GemmConfig
+    g = torch.Generator().manual_seed(M + N)
+    A = (torch.rand((M, K), generator=g) - 0.5).to(torch.float16)
+    B = (torch.rand((N, K), generator=g) - 0.5).to(torch.float16)
+    w = lambda t: oracle_mod.f16_bits_to_f32(t.view(torch.int16).numpy().view(np.uint16))
+    ref = oracle_mod.ref_gemm_tn(w(A), w(B))
+    ldc = (N + 3) // 4 * 4 + 4
+    for name, cfg in {"auto": None, "1cta_n128": GemmConfig(1, 128, 0, 0, 0), "1cta_n256": GemmConfig(1, 256, 0, 0, 0),
+                      "pair_n256": GemmConfig(2, 256, 0, 0, 0)}.items():
+        full = torch.full((M, ldc), float("nan"), dtype=torch.float32, device="cuda")
+        ctx.gemm_tn(A.cuda(), B.cuda(), out=full[:, :N], config=cfg)
+        ctx.status()
+        bad, max_abs, max_rel, _ = oracle_mod.compare_legacy(full[:, :N].cpu().numpy(), ref)
+        assert bad == 0, f"{name}: {bad} mismatches, max abs {max_abs:.3e}, max rel {max_rel:.3e}"
+        assert bool(torch.isnan(full[:, N:]).all()), f"{name}: columns behind N were written"
+
+
 # ------------------------------------------------------------------ bf16 cases
 def test_bf16_1024_cubed_all_configs(ctx, oracle_mod):
     """The 1024^3 check case: U(-1,1) operands, full compare, every tile configuration."""

@@ -56,7 +56,8 @@ def expected_blocks(oracle_mod, A, B, rows, alpha=1.0):
 
 @pytest.mark.parametrize("rows,N,K", [([300, 0, 1, 129, 512, 37, 5], 520, 264),
                                       ([31, 33, 32, 64, 1], 256, 72),
-                                      ([1000, 600], 776, 520)])
+                                      ([1000, 600], 776, 520),
+                                      ([70, 33, 200], 261, 72)])   # N not a multiple of 8 columns
 def test_grouped_matches_oracle(ctx, oracle_mod, rows, N, K):
     """Every group against the oracle, on every tile height; rows behind the last group and
     the padding columns of C keep their contents; empty and one-row groups; group ends that

@@ -96,7 +96,7 @@ NCU_DRAM_TRAFFIC_BYTES = {
     # profiles/gemm_tn_kernel_bf16_8192_pair512x256.md: 821.4 MB read + 121.4 MB written
     "bf16_tn_8192": 942_766_080,
     # profiles/gemm_streamk_kernel_bf16_m16_n28672_k8192.md
-    "skinny_m16": 476_167_680,
+    "skinny_m16": 476_803_840,
     "skinny_m64": 476_598_016,
     # profiles/gemm_tn_kernel_fp8_8192_pair512x256.md
     "fp8_tn_8192": 434_516_224,

@@ -67,6 +67,12 @@ for _m in (16, 64, 128):
         "N split over the GPUs; 3 weight buffers in rotation (each larger than L2)",
         bound="hbm", scaling="strong", rotate=3)
 
+for _m in (16, 64):
+    WORKLOADS[f"skinny_fp8_m{_m}"] = _wl(
+        _m, 28672, 8192, "unit_normal", f"decode-shaped fp8 e4m3 TN GEMM M={_m}, N=28672, K=8192, per-tensor "
+        "scales, bf16 out (memory-bound: 235 MB of weights); N split over the GPUs; 4 weight buffers in "
+        "rotation", dtype="e4m3", bound="hbm", scaling="strong", rotate=4)
+
 # One GPU's share of the widest projection when it is split over 8 GPUs, as a 1-GPU workload
 WORKLOADS["llm_proj_shard_3584x8192"] = _wl(
     8192, 3584, 8192, "llm", "one GPU's share of the 28672 x 8192 projection split over 8 GPUs: bf16 TN "

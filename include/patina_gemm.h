@@ -264,6 +264,9 @@ int patina_gemm_streamk_plan(int in_type, int64_t M, int64_t N, int64_t K, int n
                              PatinaStreamKPlan* out);
 void patina_gemm_streamk_range(uint64_t cta, uint64_t units, uint64_t parts, uint64_t* begin,
                                uint64_t* end);
+/* 1 if a call without an explicit configuration would take the stream-K kernel for this
+ * problem on a device with num_sms SMs, 0 if the large-tile kernel (host-only; for tests). */
+int patina_gemm_streamk_chosen(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms);
 uint32_t patina_gemm_streamk_owner(uint64_t unit, uint64_t units, uint64_t parts);
 
 /* Derived encodings, exported so tests can pin them against the reference's

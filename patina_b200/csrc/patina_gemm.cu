@@ -1223,6 +1223,11 @@ int patina_gemm_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   return make_plan(in_type, out_type, M, N, K, cfg, num_sms, out, nullptr, nullptr);
 }
 
+int patina_gemm_streamk_chosen(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return 0;
+  return streamk_preferred(in_type, out_type, M, N, K, num_sms) ? 1 : 0;
+}
+
 int patina_gemm_streamk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms,
                              PatinaStreamKPlan* out) {
   if (!out || N <= 0 || K <= 0 || num_sms <= 0 || !streamk_supported(in_type, kOutBF16, M))

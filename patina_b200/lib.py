@@ -21,7 +21,7 @@ SYMBOLS = (
     "patina_gemm_f16_tn_f32out", "patina_gemm_ex", "patina_gemm_host", "patina_gemm_validate",
     "patina_gemm_plan", "patina_gemm_smem_desc", "patina_gemm_idesc",
     "patina_gemm_k_advance_units", "patina_gemm_tmem_lane_offset", "patina_gemm_tile_coord",
-    "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_range",
+    "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_chosen", "patina_gemm_streamk_range",
     "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped", "patina_gemm_fp8e4m3_tn_grouped",
     "patina_gemm_peer_alloc",
     "patina_gemm_peer_open", "patina_gemm_peer_close", "patina_gemm_peer_free",
@@ -106,6 +106,7 @@ def load() -> C.CDLL:
     L.patina_gemm_tile_coord.restype = None
     L.patina_gemm_version.restype = C.c_char_p
     L.patina_gemm_streamk_plan.argtypes = [i32, i64, i64, i64, i32, C.POINTER(StreamKPlan)]
+    L.patina_gemm_streamk_chosen.argtypes = [i32, i32, i64, i64, i64, i32]
     L.patina_gemm_streamk_range.argtypes = [C.c_uint64] * 3 + [C.POINTER(C.c_uint64)] * 2
     L.patina_gemm_streamk_range.restype = None
     L.patina_gemm_streamk_owner.argtypes = [C.c_uint64] * 3

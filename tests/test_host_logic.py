@@ -219,3 +219,21 @@ def test_streamk_plan_rejects_wide_m():
         L.streamk_plan(L.IN_BF16, 129, 4096, 4096)
     with pytest.raises(ValueError):
         L.streamk_plan(L.IN_F16, 16, 4096, 4096)
+
+
+def test_automatic_choice_between_the_two_kernels(built_lib):
+    """Which kernel a call without configuration takes for M <= 128, against the shapes that were
+    timed on a B200 (microseconds: stream-K / large-tile)."""
+    chosen = lambda M, N, K, t=L.IN_BF16, o=L.OUT_BF16: built_lib.patina_gemm_streamk_chosen(t, o, M, N, K, 148)
+    assert chosen(16, 28672, 8192) == 1        # 75.3 / 77
+    assert chosen(64, 28672, 8192) == 0        # 88 / 78: enough 256-wide tiles for most SMs
+    assert chosen(128, 28672, 8192) == 0       # 98 / 79
+    assert chosen(64, 3584, 8192) == 1         # 16.8 / 23 (an 8-way shard: 14 tiles of 256)
+    assert chosen(128, 3584, 8192) == 1        # 17.8 / 53
+    assert chosen(128, 128, 4096) == 1         # 9.4 / 22: one tile, deep K
+    assert chosen(64, 256, 8192) == 1          # 10.0 / 45
+    assert chosen(128, 2048, 1024) == 0        # 9.2 / 8.6: K too short to be worth cutting
+    assert chosen(16, 24, 40) == 0
+    assert chosen(129, 3584, 8192) == 0        # the stream-K kernel holds at most 128 rows of X
+    assert chosen(16, 28672, 8192, L.IN_E4M3) == 1
+    assert chosen(128, 128, 4096, L.IN_F16, L.OUT_F32) == 0   # f32 output: large-tile kernel only

@@ -436,6 +436,19 @@ def test_scatter_to_several_destinations_on_one_gpu(ctx, oracle_mod):
         assert torch.equal(w[:, o:o + N], single)
         assert bool((w[:, :o] == 9.0).all()) and bool((w[:, o + N:] == 9.0).all())
     check_norm(oracle_mod, single, expect_bf16(oracle_mod, A, B), "scatter reference")
+    # a width that is not a multiple of 8 columns: the last box of every row is written from the
+    # registers, once per destination, and must not touch the neighbouring columns either
+    N2 = 523
+    A2, B2 = inputs.make_operands("llm", M, N2, K, seed=78)
+    dA2, dB2 = A2.cuda(), B2.cuda()
+    single2 = ctx.gemm_tn(dA2, dB2, out=torch.empty((M, 528), dtype=torch.bfloat16, device="cuda")[:, :N2])
+    for w in wide:
+        w.fill_(9.0)
+    ctx.gemm_bf16_tn_scatter(dA2, dB2, ptrs, ldc)
+    ctx.status()
+    for w, o in zip(wide, offs):
+        assert torch.equal(w[:, o:o + N2], single2)
+        assert bool((w[:, :o] == 9.0).all()) and bool((w[:, o + N2:] == 9.0).all())
     with pytest.raises(patina_b200.PatinaGemmError, match="n_dests"):
         ctx.gemm_bf16_tn_scatter(dA, dB, ptrs * 3, ldc)            # nine destinations
     with pytest.raises(patina_b200.PatinaGemmError):

@@ -93,7 +93,11 @@ int patina_gemm_set_wait_limit_ns(PatinaGemmContext* ctx, uint64_t ns);
 
 /* Synchronise `stream` and report whether any kernel enqueued through this
  * context since the last call gave up on a wait (PATINA_GEMM_ERR_TIMEOUT).
- * Replaces the cuStreamSynchronize in gemm_check.cpp:297 / run.rs:375. */
+ * Replaces the cuStreamSynchronize in gemm_check.cpp:297 / run.rs:375.
+ * The context keeps ONE status record: with several streams on one context the report does not
+ * say which stream's kernel gave up. After a suspected expiry call this before the context is
+ * used again: it also clears the skinny path's arrival counters, which an abandoned launch can
+ * leave half-way (later skinny launches would otherwise finish tiles early or not at all). */
 int patina_gemm_status(PatinaGemmContext* ctx, void* stream);
 
 /* Kernels this context has launched so far. */
@@ -215,8 +219,9 @@ int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const vo
  * For callers that must not allocate device memory: code running inside an allocator's own
  * callback, a process whose device memory is fully carved up and audited at start-up, a loop
  * that cannot afford cudaMalloc's implicit device-wide synchronisation. The context API
- * allocates (status word, scratch that grows on demand); this call allocates nothing, ever:
- * no cudaMalloc, no cudaFree, no library routine that allocates.
+ * allocates (status word, scratch that grows on demand); this call allocates nothing after
+ * its first call on a device (see below): no cudaMalloc, no cudaFree, no allocating library
+ * routine, no host heap.
  *
  * It runs the skinny stream-K GEMM, bf16 in / bf16 out, C = alpha * A[M,K] * B[N,K]^T with
  * 1 <= M <= 128, on the CURRENT device, enqueued on `stream`, without synchronising. A, B, C
@@ -232,7 +237,17 @@ int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const vo
  * GPU therefore race: issue them on one stream, or otherwise order them.
  *
  * The first call on each device does a one-time set-up (device queries, a driver entry-point
- * lookup, the address of the scratch array); make that first call outside any stream capture.
+ * lookup, the address of the scratch array). With lazy module loading that first call is also
+ * when the driver loads the module and reserves the array on that GPU, so treat it as part of
+ * start-up: make one warm-up call per device before entering any region where allocation is
+ * forbidden, and outside any stream capture. From the second call on, nothing is allocated
+ * on the device or on the host heap, on success or on failure (diagnostics are formatted into
+ * err_buf). The set-up is published with release/acquire ordering, so concurrent first calls
+ * from several host threads are safe (they repeat the same work).
+ *
+ * Shared tiles are always summed by the last CTA to reach them (the follow-up reduce kernel of
+ * the context API is not used here), which is the slower choice for M > 16 on narrow problems
+ * (measured: about 15 us instead of 2 us for the sum at M = 128, N = 3584).
  * A device-side wait that runs out still ends the kernel after its bound, but this entry
  * point has no way to report it; use the context API when that report is needed.
  * err_buf (optional) receives a NUL-terminated diagnostic on failure. */

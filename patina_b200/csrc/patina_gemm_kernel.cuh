@@ -41,9 +41,12 @@ namespace patina {
 // the normal case; several are the column-shard scatter, where every GPU of a node writes its
 // column block into each GPU's full-width C (the other maps point into peer memory mapped
 // over NVLink; TMA *stores* there are plain peer writes, nothing is multicast or loaded).
+// A plain launch carries one map; only the scatter's instantiations carry kMaxDests of them
+// (a kilobyte of kernel parameters that every other launch would pay for in launch latency).
 constexpr int kMaxDests = 8;
+template <int kDests>
 struct CStoreMaps {
-  CUtensorMap map[kMaxDests];
+  CUtensorMap map[kDests];
 };
 
 struct GemmParams {
@@ -77,7 +80,26 @@ struct GemmParams {
   int64_t ldc;
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
+#ifdef PATINA_TRACE
+  unsigned long long* trace;  // [grid][32]: time stamps of a trace build (never in the shipped library)
+#endif
 };
+
+// Time stamps for a trace build (-DPATINA_TRACE): slot s of this CTA gets the global timer,
+// slot 16 + s the SM's cycle counter. The shipped library compiles these to nothing.
+#ifdef PATINA_TRACE
+#define PATINA_TRACE_AT(slot)                                                     \
+  do {                                                                            \
+    if (p.trace) {                                                                \
+      p.trace[(size_t)blockIdx.x * 32u + (slot)] = ptx::globaltimer_ns();         \
+      p.trace[(size_t)blockIdx.x * 32u + 16u + (slot)] = (unsigned long long)clock64(); \
+    }                                                                             \
+  } while (0)
+#else
+#define PATINA_TRACE_AT(slot) \
+  do {                        \
+  } while (0)
+#endif
 
 constexpr uint32_t kMaxGroups = 128;
 constexpr uint32_t kGroupTableBytes = 2u * (kMaxGroups + 1u) * 4u + 8u;  // row and tile prefix sums
@@ -200,10 +222,10 @@ struct GemmTraits {
 };
 
 template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused = false,
-          bool kGrouped = false>
+          bool kGrouped = false, int kDests = 1>
 __global__ void __launch_bounds__(64 + 128 * kMSub, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-               const __grid_constant__ CStoreMaps tm_c, const GemmParams p) {
+               const __grid_constant__ CStoreMaps<kDests> tm_c, const GemmParams p) {
   using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut>;
   constexpr bool kPair = (kCtaGroup == 2);
   constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
@@ -250,9 +272,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   // ---------------------------------------------------------------- prologue
   if (threadIdx.x == 0) {
+    PATINA_TRACE_AT(0);
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_b);
-    for (uint32_t d = 0; d < p.n_dests; ++d) ptx::prefetch_tensormap(&tm_c.map[d]);
+    for (uint32_t d = 0; d < (uint32_t)kDests && d < p.n_dests; ++d) ptx::prefetch_tensormap(&tm_c.map[d]);
     for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
       ptx::mbar_init(full_bar + 8u * s, 1);
       ptx::mbar_init(empty_bar + 8u * s, 1);
@@ -263,6 +286,32 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     *abort_ptr = 0u;
     ptx::fence_mbar_init();
+  }
+  // Single-CTA kernels: the producer lane (this same thread 0) issues the first pass through
+  // the ring right here, before TMEM allocation and the set-up barrier, so that those hide
+  // behind the first loads' latency. Every stage is free, so no wait is needed. (A pair's loads
+  // complete on the leader's barriers, which the partner may only use after the cluster-wide
+  // barrier below; a grouped launch needs its tables first.)
+  uint32_t pre_kb = 0;
+  if constexpr (!kPair && !kGrouped) {
+    if (threadIdx.x == 0 && cluster_id < p.num_tiles) {
+      ptx::fence_proxy_async_smem();
+      const TileCoord c0 = tile_coord(cluster_id, p.tiles_m, p.tiles_n, p.group_m);
+      const int32_t a_row = (int32_t)(c0.m * T::kTileM);
+      const int32_t b_row = (int32_t)(c0.n * BN);
+      const uint32_t n_pre = p.k_blocks < (uint32_t)kStages ? p.k_blocks : (uint32_t)kStages;
+      for (uint32_t kb = 0; kb < n_pre; ++kb) {
+        const uint32_t sa = ring + kb * T::kStageBytes;
+        const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
+        ptx::mbar_arrive_expect_tx(full_bar + 8u * kb, T::kStageBytes);
+#pragma unroll
+        for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
+          ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * kb, k0,
+                           a_row + (int32_t)(ms * kCtaRows));
+        ptx::tma_load_2d(sa + T::kABytes, &tm_b, full_bar + 8u * kb, k0, b_row);
+      }
+      pre_kb = n_pre;
+    }
   }
   if constexpr (kGrouped) {
     // Every CTA derives the same tables from the device-resident group sizes: first row and
@@ -298,6 +347,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     __syncthreads();
   }
   ptx::tc_fence_after_sync();
+  if (threadIdx.x == 0) PATINA_TRACE_AT(1);
   const uint32_t tmem_base = *tmem_slot_ptr;
   const uint32_t num_tiles = kGrouped ? grp_tile_begin[p.n_groups] : p.num_tiles;
   // Where tile t lies. Plain launch: one problem. Grouped launch: the group is found by moving
@@ -345,7 +395,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   // ------------------------------------------------------------ TMA producer
   if (warp_idx == 0) {
     if (lane == 0) {
-      uint32_t s = 0, ph = 0;
+      // (pre_kb k-blocks of the first tile are already in flight: see the prologue)
+      uint32_t s = pre_kb == (uint32_t)kStages ? 0u : pre_kb, ph = pre_kb == (uint32_t)kStages ? 1u : 0u;
+      uint32_t kb_first = pre_kb;
       const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
       uint32_t grp = 0;
       for (uint32_t t = cluster_id; t < num_tiles; t += num_clusters) {
@@ -358,7 +410,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t n_sub = live_subtiles(c);
         const uint32_t stage_tx = n_sub * T::kASubBytes + T::kBBytes;  // bytes this CTA loads per stage
         bool ok = true;
-        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+        for (uint32_t kb = kb_first; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
           if (!ok) break;
           const uint32_t sa = ring + s * T::kStageBytes;
@@ -383,6 +435,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
         }
+        kb_first = 0;
         if (!ok) break;
       }
     }
@@ -406,6 +459,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           ok = bounded_wait<kPair>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
           ptx::tc_fence_after_sync();
+          if (it == 0 && kb == 0) PATINA_TRACE_AT(2);
           const uint32_t sa = ring + s * T::kStageBytes;
           const uint64_t db = smem_desc_sw128_kmajor(sa + T::kABytes);
 #pragma unroll
@@ -427,6 +481,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (!ok) break;
         ptx::umma_commit<kCtaGroup>(tfull_bar + 8u * buf);
         if constexpr (kPair) ptx::umma_commit<kCtaGroup>(peer_tfull + 8u * buf);
+        PATINA_TRACE_AT(3);  // (overwritten per tile: the last tile's stamp stays)
       }
       // Every MMA must have retired before shared memory or TMEM is released:
       // wait for the last accumulator's completion here as well.
@@ -457,6 +512,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
+      if (warp_idx == 2 && lane == 0) PATINA_TRACE_AT(4);
       const uint32_t row0 = c.row_base + c.m * T::kTileM + ms * (kCtaRows * kCtaGroup) +
                             cta_rank * kCtaRows + q * kStoreBoxRows;
       // A grouped launch must not write past its group: a box beyond the group's last row is
@@ -684,8 +740,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
           const uint32_t cc = col0 + ch_col;
           if (row0 < p.M && cc < p.N) {
-            for (uint32_t d = 0; d < p.n_dests; ++d)
-              ptx::tma_store_2d(&tm_c.map[d], stg0 + sbuf * T::kBufBytes, (int32_t)cc, (int32_t)row0);
+            if constexpr (kDests == 1) {
+              ptx::tma_store_2d(&tm_c.map[0], stg0 + sbuf * T::kBufBytes, (int32_t)cc, (int32_t)row0);
+            } else {
+              for (uint32_t d = 0; d < p.n_dests; ++d)
+                ptx::tma_store_2d(&tm_c.map[d], stg0 + sbuf * T::kBufBytes, (int32_t)cc, (int32_t)row0);
+            }
           }
           ptx::tma_store_commit();
         }
@@ -710,7 +770,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     // The staging buffers must have been read before the CTA gives its shared memory back; the
     // writes themselves are complete, as every write of a grid, when the grid completes.
+    if (warp_idx == 2 && lane == 0) PATINA_TRACE_AT(5);
     if (lane == 0) ptx::tma_store_wait_read<0>();
+    if (warp_idx == 2 && lane == 0) PATINA_TRACE_AT(6);
   }
 
   // ---------------------------------------------------------------- teardown
@@ -731,6 +793,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   }
   ptx::tc_fence_after_sync();
   if (warp_idx == 1) ptx::tmem_dealloc<kCtaGroup>(tmem_base, T::kTmemCols);
+  if (threadIdx.x == 32) PATINA_TRACE_AT(7);
 }
 
 }  // namespace patina

@@ -86,6 +86,14 @@ PATINA_HD uint32_t streamk_max_contrib(uint64_t units, uint64_t parts, uint32_t 
   return (uint32_t)((k_blocks - 1) / min_len) + 2;
 }
 
+// True when at least one tile's k-blocks are split between CTAs (a CTA boundary that is not a
+// tile boundary). Without one every tile is computed whole and nothing needs summing.
+PATINA_HD bool streamk_any_shared_tile(uint64_t units, uint64_t parts, uint32_t k_blocks) {
+  for (uint64_t c = 1; c < parts; ++c)
+    if (streamk_range_start(c, units, parts) % k_blocks != 0) return true;
+  return false;
+}
+
 template <int kIn>
 __global__ void __launch_bounds__(192, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
@@ -412,8 +420,10 @@ streamk_reduce_kernel(const StreamKParams p, const uint32_t parts) {
   const uint64_t tile_u0 = (uint64_t)t * p.k_blocks;
   const uint32_t first_cta = streamk_owner(tile_u0, p.units, parts);
   const uint32_t contribs = streamk_owner(tile_u0 + p.k_blocks - 1, p.units, parts) - first_cta + 1u;
-  if (contribs < 2u) return;
+  // Every block waits, also one with nothing to sum: this grid must not complete before the GEMM
+  // grid has, or work enqueued behind it on the stream could read C too early.
   ptx::grid_dependency_wait();  // the partial tiles are complete and visible from here on
+  if (contribs < 2u) return;
   const uint32_t n = t * kSkTileRows + threadIdx.x;
   const float4* slot0 = reinterpret_cast<const float4*>(
                             p.partials + (size_t)t * p.max_contrib * ((size_t)p.m_pad * 128u)) +

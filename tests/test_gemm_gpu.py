@@ -56,7 +56,9 @@ def cfgs():
             "pair_2sub_n160": GemmConfig(2, 160, 0, 0, 0, 2),
             # widths ending in half a store box (the last box overlaps its neighbour)
             "pair_2sub_n240": GemmConfig(2, 240, 0, 0, 0, 2), "pair_2sub_n208": GemmConfig(2, 208, 0, 0, 0, 2),
-            "pair_2sub_n176": GemmConfig(2, 176, 0, 0, 0, 2)}
+            "pair_2sub_n176": GemmConfig(2, 176, 0, 0, 0, 2),
+            # narrow tiles for problems with few tiles
+            "pair_n64": GemmConfig(2, 64, 0, 0, 0), "1cta_n64": GemmConfig(1, 64, 0, 0, 0)}
 
 
 # ------------------------------------------------------------ reference shape
@@ -214,7 +216,7 @@ def test_fp8_e4m3(ctx, oracle_mod, M, N, K):
     check_norm(oracle_mod, out, want, "fp8 auto")
     for name, cfg in cfgs().items():
         if name in ("pair_n128", "pair_2sub_n128", "pair_2sub_n192", "pair_2sub_n160", "pair_2sub_n208",
-                    "pair_2sub_n176"):
+                    "pair_2sub_n176", "pair_n64", "1cta_n64"):
             continue  # no such fp8 kernels
         out = ctx.gemm_tn(Aq.cuda(), Bq.cuda(), alpha=sa * sb, config=cfg)
         ctx.status()
@@ -244,6 +246,54 @@ def test_streamk_matches_oracle_and_large_tile_kernel(ctx, oracle_mod, M, N, K):
     ctx.gemm_tn(dA, dB, out=tiled, alpha=1.5, config=GemmConfig(0, 0, 0, 0, 0, 0, -1))
     ctx.status()
     check_norm(oracle_mod, tiled, outs[0].float().cpu().numpy(), "large-tile vs stream-K")
+
+
+def test_streamk_whole_tiles_only_orders_the_stream(ctx, oracle_mod):
+    """A partition in which every CTA owns whole tiles (100 tiles x 8 k-blocks over 100 CTAs) with
+    a wide X, which would normally hand the sum to the follow-up kernel: nothing is shared, so no
+    second kernel may be launched, and work enqueued right behind the call on the same stream
+    must see the finished C."""
+    from patina_b200 import inputs, GemmConfig
+    M, N, K = 32, 12800, 512
+    A, B = inputs.make_operands("llm", M, N, K, seed=31)
+    dA, dB = A.cuda(), B.cuda()
+    want = expect_bf16(oracle_mod, A, B)
+    for mode in (1, 2):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        before = ctx.launch_count
+        ctx.gemm_tn(dA, dB, out=out, config=GemmConfig(0, 0, 0, 0, 0, 0, mode))
+        seen = out.clone()                       # a consumer on the same stream, no sync in between
+        assert ctx.launch_count - before == 1, "no tile is shared: the reduce kernel must not run"
+        ctx.status()
+        check_norm(oracle_mod, seen, want, f"consumer right behind the call (stream_k={mode})")
+
+
+def test_streamk_wait_expiry_is_reported_and_context_recovers(ctx, oracle_mod):
+    """The skinny kernel's bounded waits: with a 1 ns limit on a problem whose CTAs stream for
+    tens of microseconds each and share tiles, the launch is abandoned and status() says so;
+    status() also clears the arrival counters the abandoned launch left half-way, so the next
+    launches on the same context are right again (in-kernel sum and follow-up kernel)."""
+    import patina_b200
+    from patina_b200 import inputs, GemmConfig, lib as L
+    M, N, K = 16, 12800, 16384                 # 100 tiles x 256 k-blocks over 148 CTAs: shared tiles
+    A, B = inputs.make_operands("llm", M, N, K, seed=32)
+    dA, dB = A.cuda(), B.cuda()
+    ctx.set_wait_limit_ns(1)
+    try:
+        ctx.gemm_tn(dA, dB, config=GemmConfig(0, 0, 0, 0, 0, 0, 3))
+        with pytest.raises(patina_b200.PatinaGemmError) as ei:
+            ctx.status()
+        assert ei.value.code == L.ERR_TIMEOUT and "wait expired" in str(ei.value)
+    finally:
+        ctx.set_wait_limit_ns(2_000_000_000)
+    rng = np.random.default_rng(3)
+    cols = np.unique(np.concatenate([[0, 127, 128, N - 1], rng.integers(0, N, 60)])).astype(np.int64)
+    ref_t = oracle_mod.ref_gemm_tn(widen(oracle_mod, B), widen(oracle_mod, A), rows=cols)
+    want = oracle_mod.scale_round_bf16(ref_t.T.copy(), 1.0)
+    for mode in (3, 2):
+        out = ctx.gemm_tn(dA, dB, config=GemmConfig(0, 0, 0, 0, 0, 0, mode))
+        ctx.status()
+        check_norm(oracle_mod, out[:, torch.from_numpy(cols).cuda()], want, f"after recovery (stream_k={mode})")
 
 
 def test_streamk_decode_shapes_full_size(ctx, oracle_mod):

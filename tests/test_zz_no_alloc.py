@@ -9,7 +9,9 @@ inside the library and refuses problems that do not fit.
 Checked here, through the C ABI: its output equals the regular stream-K entry point's (same
 kernel, same partition, so bit for bit, which is inside the suite's tolerance) on two calls in
 a row with different operands -- the second call meets the first one's leftovers in the shared
-scratch; and oversize or out-of-range problems are refused with a message.
+scratch; device memory in use does not change across the calls after the first (the first
+call on a device is the documented warm-up: with lazy loading it is when the driver brings in
+the module and the array); and oversize or out-of-range problems are refused with a message.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
@@ -48,9 +50,16 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(oracle_mod):
         ctx.gemm_tn(dA, dB, out=want, alpha=alpha, config=GemmConfig(0, 0, 0, 0, 0, 0, 1))
         ctx.status()
         got = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :N]
+        if call == 0:
+            rc, msg = call_noalloc(lib, dA, dB, got, alpha)      # the warm-up call for this device
+            assert rc == L.OK, msg
+            got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc, msg = call_noalloc(lib, dA, dB, got, alpha)
         assert rc == L.OK, msg
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "device memory in use changed across the call"
         assert torch.equal(got, want), f"call {call}: differs from the regular entry point"
         # and both are right: the suite's tolerance against the oracle
         wa = oracle_mod.bf16_bits_to_f32(A.view(torch.int16).numpy().view(np.uint16))

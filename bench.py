@@ -13,6 +13,12 @@ scaling: per-GPU work is fixed).
 
 Prints ONE JSON line (rank 0). `value` times the kernel with operands resident
 in HBM; `e2e` times the public host-buffer call (H2D + GEMM + D2H every step).
+Whatever --steps is, the line also carries a short `burst` and a >= 1 s `sustained`
+measurement of the same workload (each with the SM clock sampled under it), at
+N = 1 short `configs` sub-records for the other benchmark configurations, and at
+every N a `strong` block: the per-shard step time of the fixed-size projection,
+fp8 and decode shapes split over the N ranks, from which strong scaling follows
+as T(1) / T(N) across the runs.
 `--impl reference` times the reference's own CPU GEMM (harness/gemm_check.cpp
 reference_gemm, compiled into oracle/_ref; the oracle port if that is absent)
 on the host cores, on bounded samples of the same workload.
@@ -50,6 +56,8 @@ def _wl(M, N, K, dist, desc, dtype="bf16", bound="tensor", scaling="weak", rotat
 WORKLOADS = {
     "bf16_tn_8192": _wl(8192, 8192, 8192, "normal_0p1",
                         "bf16 TN GEMM M=N=K=8192, N(0,1)*0.1, fp32 accumulate, bf16 out"),
+    "bf16_tn_1024": _wl(1024, 1024, 1024, "uniform",
+                        "bf16 TN GEMM M=N=K=1024, U(-1,1), fp32 accumulate, bf16 out (the CPU-checkable case)"),
     "bf16_tn_4096": _wl(4096, 4096, 4096, "normal_0p1",
                         "bf16 TN GEMM M=N=K=4096, N(0,1)*0.1, fp32 accumulate, bf16 out"),
     "fp8_tn_8192": _wl(8192, 8192, 8192, "unit_normal", "fp8 e4m3 TN GEMM M=N=K=8192, per-tensor scales "
@@ -427,6 +435,7 @@ def run_ours(args):
 
     # end to end: host buffers in, host buffer out, every step
     e2e_steps = min(args.steps, 200)
+    e2e_note = "patina_gemm_host: H2D of A and B, GEMM, D2H of C, pipelined over row blocks"
     if args.no_e2e:
         e2e_total_ms = float("nan")
     elif G:
@@ -440,6 +449,16 @@ def run_ours(args):
             torch.cuda.current_stream().synchronize()
         e2e_total_ms, _ = timed(e2e_step, e2e_steps, min(args.warmup, 3))
         ctx.status()
+    elif world > 1 and not fp8:
+        # Many GPUs: the replicated A crosses PCIe once per node (every rank uploads 1/world of
+        # it and an all-gather over NVLink completes it), each rank uploads its own B shard.
+        host_run = sharded.HostShardedGemm(ctx, M, N, K)
+        e2e_total_ms, _ = timed(lambda i: host_run(A_h, B_h, C_h, alpha=alpha), e2e_steps, min(args.warmup, 3))
+        ctx.status()
+        e2e_note = (f"per rank: 1/{world} of A and the whole B shard over PCIe, the rest of A over NVLink "
+                    f"(all-gather, {M * K * ebytes * (world - 1) // world} bytes received per rank)")
+        h2d_rank, d2h_rank = host_run.pcie_bytes()
+        del host_run
     else:
         e2e_total_ms, _ = timed(lambda i: ctx.gemm_host(A_h, B_h, C_h, alpha=alpha), e2e_steps,
                                 min(args.warmup, 3))
@@ -447,6 +466,146 @@ def run_ours(args):
     e2e_value = flops_total / (e2e_total_ms / e2e_steps * 1e-3) / 1e12
     h2d = (M * K + N * K) * ebytes if not G else M * K * ebytes + 4 * G
     d2h = M * N * 2
+    if world > 1 and not fp8 and not G and not args.no_e2e:
+        h2d, d2h = h2d_rank, d2h_rank
+
+    # ---- burst and sustained sub-measurements of the main workload, whatever --steps is
+    main_region_s = total_ms * 1e-3
+    sub = {}
+    if not (G or args.fused_epilogue or args.no_extras):
+        def clocked(steps, warmup, graph_steps=0):
+            smp = ClockSampler(local_rank)
+            if rank == 0:
+                smp.start()
+            t_ms, per_ms = timed(step, steps, warmup, graph_steps)
+            clk = smp.stop() if rank == 0 else None
+            return t_ms, per_ms, clk
+        if main_region_s >= 1.0:
+            sus_ms, sus_steps, sus_clk = total_ms, args.steps, clocks
+        else:
+            sus_steps = max(20, int(1.25e3 / max(ms_per_step, 1e-3)))
+            if graph_steps:
+                sus_steps = (sus_steps + graph_steps - 1) // graph_steps * graph_steps
+            sus_ms, _, sus_clk = clocked(sus_steps, 0, graph_steps)
+        if main_region_s <= 0.1:
+            bur_ms, bur_steps, bur_clk = total_ms, args.steps, clocks
+        else:
+            time.sleep(1.0)                       # let the part cool back to its idle clocks
+            bur_steps = graph_steps if graph_steps else 20
+            bur_ms, _, bur_clk = clocked(bur_steps, 3, graph_steps)
+
+        def sub_record(t_ms, n_steps, clk):
+            ms = t_ms / n_steps
+            return {"steps": n_steps, "ms_per_step": round(ms, 5), "timed_region_s": round(t_ms * 1e-3, 4),
+                    "per_gpu_tflops": round(flops_per_gpu / (ms * 1e-3) / 1e12, 2),
+                    "sm_mhz_median": clk.get("sm_mhz") if clk else None,
+                    "clock_samples": clk.get("samples") if clk else None,
+                    "reasons": clk.get("reasons") if clk else None}
+        sub["burst"] = sub_record(bur_ms, bur_steps, bur_clk)
+        sub["sustained"] = sub_record(sus_ms, sus_steps, sus_clk)
+
+    # ---- other configurations (N = 1) and the strong-scaling block (every N)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(peaks_path)) if os.path.isfile(peaks_path) else None
+    del dA, dBs, dC
+    torch.cuda.empty_cache()
+
+    def device_operands(w, m, n, k, seed):
+        """Operands of workload w drawn on the device (sub-records only time resident data)."""
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        da, db = inputs.DISTRIBUTIONS[w["dist"]]
+
+        def draw(spec, shape):
+            if spec[0] == "uniform":
+                return torch.rand(shape, generator=g, device="cuda") * (spec[2] - spec[1]) + spec[1]
+            return torch.randn(shape, generator=g, device="cuda") * spec[1]
+        a, b, al = draw(da, (m, k)), draw(db, (n, k)), 1.0
+        if w["dtype"] == "e4m3":
+            sa, sb = float(a.abs().max()) / 448.0, float(b.abs().max()) / 448.0
+            a = (a / sa).clamp_(-448, 448).to(torch.float8_e4m3fn)
+            b = (b / sb).clamp_(-448, 448).to(torch.float8_e4m3fn)
+            al = sa * sb
+        else:
+            a, b = a.to(torch.bfloat16), b.to(torch.bfloat16)
+        return a, b, al
+
+    def measure(name, budget_ms=40.0, gather=False):
+        """Step time of workload `name` on this run's ranks (its N split over them when its
+        scaling is strong), operands resident; max over ranks. Short steps replay from a graph."""
+        w = WORKLOADS[name]
+        m, k = w["M"], w["K"]
+        if w["scaling"] == "strong":
+            c0, c1 = sharded.column_shard(w["N"], world, rank)
+            n, nt = c1 - c0, w["N"]
+        else:
+            c0, n, nt = 0, w["N"], w["N"]
+        eb = 1 if w["dtype"] == "e4m3" else 2
+        a, b, al = device_operands(w, m, n, k, inputs.DEFAULT_SEED + 17 * rank)
+        bs = [b] + [b.clone() for _ in range(w["rotate"] - 1)]
+        c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        fl, by = 2.0 * m * n * k, (m * k + n * k) * eb + m * n * 2
+        est = max(fl / 1.4e15, by / 6.0e12) * 1e6
+        gs = 50 if est < 150.0 else 0
+        st = int(min(400, max(10, budget_ms * 1e3 / est)))
+        if gs:
+            st = max(gs, st // gs * gs)
+        fn = lambda i: ctx.gemm_tn(a, bs[i % len(bs)], out=c, alpha=al)
+        t_ms, per_ms = timed(fn, st, 3, gs)
+        ctx.status()
+        ms = t_ms / st
+        rec = {"M": m, "N_per_gpu": n, "N_total": nt, "K": k, "dtype": w["dtype"], "steps": st,
+               "launch": "graph" if gs else "calls", "ms_per_step": round(ms, 5),
+               "aggregate_tflops": round(2.0 * m * nt * k / (ms * 1e-3) / 1e12, 2)}
+        if w["bound"] == "hbm":
+            ach = by / (ms * 1e-3) / 1e9
+            pk = float(peaks["hbm_gbs"]) if peaks else FALLBACK_HBM_GBS
+            rec["roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk, "unit": "GB/s",
+                               "frac": round(ach / pk, 4), "algorithmic_bytes_per_launch": by}
+        else:
+            ach = fl / (ms * 1e-3) / 1e12
+            pk = (float(peaks["bf16_tflops"]) if peaks else FALLBACK_BF16_TFLOPS) * (2.0 if eb == 1 else 1.0)
+            rec["roofline"] = {"bound": "tensor", "achieved": round(ach, 1), "peak": pk, "unit": "TFLOP/s",
+                               "frac": round(ach / pk, 4), "algorithmic_flops_per_launch": fl,
+                               "peak_note": "measured bf16 burst" + (" x 2 (no fp8 peak was measured)" if eb == 1 else "")}
+        if gather and world > 1 and eb == 2:
+            # the optional gather of C, both ways, and whether they agree bit for bit
+            g_total, _ = timed(lambda i: sharded.all_gather_columns(c, nt), 10, 2)
+            rec["allgather_ms"] = round(g_total / 10, 4)
+            shared = sharded.SharedC(ctx, m, nt)
+            barrier()
+            ptrs = shared.column_block_ptrs(c0)
+            f_total, _ = timed(lambda i: ctx.gemm_bf16_tn_scatter(a, bs[0], ptrs, nt), 10, 2)
+            ctx.status()
+            rec["fused_gemm_allgather_ms"] = round(f_total / 10, 4)
+            ctx.gemm_tn(a, bs[0], out=c, alpha=al)
+            full = sharded.all_gather_columns(c, nt)
+            barrier()
+            same = torch.tensor([1.0 if torch.equal(full, shared.local) else 0.0], device="cuda")
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            rec["fused_equals_allgather"] = bool(same.item() == 1.0)
+            del full
+            barrier()
+            shared.close()
+        del a, b, bs, c
+        torch.cuda.empty_cache()
+        return rec
+
+    extras = {}
+    if not args.no_extras and not (G or args.fused_epilogue) and args.workload == "bf16_tn_8192":
+        if world == 1:
+            extras["configs"] = {nm: measure(nm) for nm in
+                                 ("bf16_tn_1024", "bf16_tn_4096", "fp8_tn_8192", "skinny_m16", "skinny_m64",
+                                  "skinny_m128")}
+        strong = {}
+        for nm in ("llm_proj_4096x4096", "llm_proj_14336x4096", "llm_proj_4096x14336", "llm_proj_28672x8192",
+                   "fp8_tn_16384", "skinny_m16", "skinny_m128"):
+            if world == 1 and nm in extras.get("configs", {}):
+                strong[nm] = extras["configs"][nm]
+            else:
+                strong[nm] = measure(nm, gather=(nm == "llm_proj_28672x8192"))
+        extras["strong"] = {"n_gpus": world, "note": "fixed problems, N columns split over the ranks; ms_per_step is "
+                            "the slowest rank's; strong scaling of a shape = its ms_per_step at 1 GPU / at N GPUs",
+                            "workloads": strong}
 
     if rank != 0:
         if world > 1:
@@ -456,8 +615,6 @@ def run_ours(args):
     # Denominators: measured on this pool (MEASURED_PEAKS.json). A timed region of a second or
     # more runs under the power cap like the "sustained" measurement; a shorter one is compared
     # with the (higher) burst figure.
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    peaks = json.load(open(peaks_path)) if os.path.isfile(peaks_path) else None
     region_s = total_ms * 1e-3
     kernel_ms = statistics.mean(per)
     extra = {}
@@ -510,7 +667,8 @@ def run_ours(args):
         "per_gpu_tflops": round(value / world, 2),
         "pct_of_nominal_peak": round(100.0 * value / world / nominal, 2),
         "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_total_ms / e2e_steps, 4)},
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_total_ms / e2e_steps, 4),
+                "bytes_are": "per rank (rank 0's)", "path": e2e_note},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": wl["bound"], "achieved": round(achieved, 2), "peak": peak, "unit": unit,
@@ -521,6 +679,8 @@ def run_ours(args):
                      "algorithmic_flops_per_launch": flops_per_gpu,
                      "algorithmic_bytes_per_launch": bytes_per_gpu, **extra},
     }
+    out.update(sub)
+    out.update(extras)
     if G:
         out["config"]["groups"] = G
         out["config"]["group_rows"] = rows_h.tolist()
@@ -585,6 +745,9 @@ def main():
                          "-1 (default) = graph only when a step is estimated under 150 us")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the burst / sustained sub-measurements, the other configurations and the "
+                         "strong-scaling block (profiling runs)")
     ap.add_argument("--fused-allgather", action="store_true",
                     help="N > 1: also time the GEMM whose epilogue stores its column block into every "
                          "GPU's full-width C (peer writes over NVLink instead of a collective)")

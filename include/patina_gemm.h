@@ -46,7 +46,8 @@ enum {
   PATINA_GEMM_ERR_TIMEOUT = 4           /* a bounded device-side wait expired */
 };
 
-enum { PATINA_IN_F16 = 0, PATINA_IN_BF16 = 1, PATINA_IN_E4M3 = 2 };
+enum { PATINA_IN_F16 = 0, PATINA_IN_BF16 = 1, PATINA_IN_E4M3 = 2,
+       PATINA_IN_MXE4M3 = 3 /* block-scaled: patina_gemm_mxfp8_tn only */ };
 enum { PATINA_OUT_BF16 = 0, PATINA_OUT_F32 = 1, PATINA_OUT_E4M3 = 2 /* fused epilogue only */ };
 
 /* Tile configuration. Zero in any field means "choose for me". */
@@ -195,6 +196,25 @@ int patina_gemm_fp8e4m3_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_
                                    const float* group_scale_b, const PatinaGemmConfig* config,
                                    void* stream);
 
+/* Block-scaled fp8 ("MXFP8"; no counterpart in the reference, whose kernel is f16 only,
+ * crates/patina/tests/golden/v2_gemm_pipelined.ptx:203,212): A and B hold e4m3 elements, and every
+ * 32 consecutive K elements of a row share one E8M0 scale (a byte e: the factor 2^(e - 127); 0xFF is
+ * NaN). The tensor core applies the scales (tcgen05.mma kind::mxf8f6f4.block_scale, scales in TMEM):
+ *     C[M,N] (bf16) = alpha * sum_k (A[m,k] * sa[m, k/32]) * (B[n,k] * sb[n, k/32])
+ * K must be a multiple of 32. The scales of a [rows, K] operand live in a buffer of
+ * patina_gemm_mx_scale_bytes(rows, K) bytes, in atoms of 512 bytes that cover 128 rows x 128 elements
+ * of K: atom index (row / 128) * ceil(K / 128) + k / 128, and inside the atom the scale of row r,
+ * 32-element block j is byte (r % 32) * 16 + ((r % 128) / 32) * 4 + (j % 4), the layout the tensor
+ * core's scale loads take (the "128x4 swizzled" layout other libraries use for MX scales).
+ * patina_gemm_mx_scale_offset gives the byte offset of one scale. The buffer is padded to whole
+ * atoms; padding bytes must be valid scales (anything but 0xFF), e.g. 127 (= 1.0). Scale buffers
+ * are device pointers, 16-byte aligned. `config` may be NULL; block_n is 256, 224, 192 or 128. */
+int patina_gemm_mxfp8_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* scales_a,
+                         const void* B, int64_t ldb, const void* scales_b, void* C, int64_t ldc, int64_t M,
+                         int64_t N, int64_t K, float alpha, const PatinaGemmConfig* config, void* stream);
+uint64_t patina_gemm_mx_scale_bytes(int64_t rows, int64_t K);
+uint64_t patina_gemm_mx_scale_offset(int64_t row, int64_t k_block32, int64_t K);
+
 /* Buffers for the scatter above (no counterpart in the reference). peer_alloc gives device
  * memory of this context's GPU plus a 64-byte handle that another PROCESS on the node passes
  * to peer_open (with its own context) to get a pointer its GPU can write through NVLink.
@@ -289,6 +309,8 @@ uint32_t patina_gemm_streamk_owner(uint64_t unit, uint64_t units, uint64_t parts
 uint64_t patina_gemm_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                int swizzle_code);
 uint32_t patina_gemm_idesc(int in_type, uint32_t umma_m, uint32_t umma_n);
+/* instruction descriptor of the block-scaled form (E8M0 scales, e4m3 operands) */
+uint32_t patina_gemm_idesc_mx(uint32_t umma_m, uint32_t umma_n, uint32_t a_sf_id, uint32_t b_sf_id);
 uint32_t patina_gemm_k_advance_units(uint32_t k_elems, int in_type);
 uint32_t patina_gemm_tmem_lane_offset(uint32_t warp_quarter);
 void patina_gemm_tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m,

@@ -150,6 +150,21 @@ def ref_gemm_tn(A: np.ndarray, B: np.ndarray, rows=None, threads: int = 0) -> np
     return out
 
 
+def mx_dequant(q_bits: np.ndarray, e: np.ndarray) -> np.ndarray:
+    """Block-scaled fp8 operand as exact float32 values: e4m3 element times 2^(e - 127), one E8M0
+    byte e per 32 consecutive K elements of a row (OCP Microscaling formats v1.0, MXFP8). The
+    reference has no block-scaled path; this extends its check: the dequantised operands go
+    through the same double-accumulating loop (harness/gemm_check.cpp:165-178)."""
+    q = e4m3_bits_to_f32(q_bits)
+    rows, K = q.shape
+    assert K % 32 == 0 and e.shape == (rows, K // 32) and e.dtype == np.uint8
+    assert not np.any(e == 0xFF), "0xFF is the E8M0 NaN"
+    scale = np.ldexp(np.float32(1.0), e.astype(np.int32) - 127).astype(np.float32)
+    out = (q.reshape(rows, K // 32, 32) * scale[:, :, None]).reshape(rows, K)
+    assert np.all(np.isfinite(out))
+    return np.ascontiguousarray(out, dtype=np.float32)
+
+
 def scale_round_bf16(ref: np.ndarray, alpha: float = 1.0) -> np.ndarray:
     """bf16(alpha * ref) (RNE), widened back to float32: the expected bf16 output."""
     ref = np.ascontiguousarray(ref, dtype=np.float64)

@@ -22,11 +22,14 @@
 
 namespace patina {
 
-enum InputType : int { kF16 = 0, kBF16 = 1, kE4M3 = 2 };
+// kMXE4M3: e4m3 elements with one E8M0 scale (a power of two) per 32 consecutive K elements of
+// every row ("MXFP8"); the tensor core applies the scales (tcgen05.mma kind::mxf8f6f4.block_scale).
+enum InputType : int { kF16 = 0, kBF16 = 1, kE4M3 = 2, kMXE4M3 = 3 };
 enum OutputType : int { kOutBF16 = 0, kOutF32 = 1, kOutE4M3 = 2 };
 enum SwizzleMode : int { kSwizzleNone = 0, kSwizzle128B = 2 };  // descriptor layout-type codes
 
-PATINA_HD constexpr uint32_t input_bytes(int t) { return t == kE4M3 ? 1u : 2u; }
+PATINA_HD constexpr uint32_t input_bytes(int t) { return (t == kE4M3 || t == kMXE4M3) ? 1u : 2u; }
+PATINA_HD constexpr bool is_block_scaled(int t) { return t == kMXE4M3; }
 PATINA_HD constexpr uint32_t output_bytes(int t) { return t == kOutF32 ? 4u : t == kOutE4M3 ? 1u : 2u; }
 
 // ---- shared-memory matrix descriptor (tcgen05, "version 1") --------------
@@ -65,6 +68,45 @@ PATINA_HD constexpr uint32_t k_advance_units_noswizzle(uint32_t k_elems, uint32_
 PATINA_HD constexpr uint32_t idesc(int input_type, uint32_t umma_m, uint32_t umma_n) {
   uint32_t fmt = (input_type == kBF16) ? 1u : 0u;  // f16 -> 0, e4m3 -> 0 (in its own kind)
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
+}
+
+// ---- block-scaled instruction descriptor (kind::mxf8f6f4.block_scale) ------
+//   [4,6) B scale-factor id   [7,10) A format (0 = e4m3)   [10,13) B format
+//   [15] A major, [16] B major (0 = K-major)   [17,23) N >> 3   [23] scale format (1 = E8M0)
+//   [24,29) M >> 4   [29,31) A scale-factor id
+// The scale-factor id says which byte of the operand's 32-bit scale column this instruction uses:
+// one column holds the scales of four consecutive 32-element k-blocks.
+PATINA_HD constexpr uint32_t idesc_mx(uint32_t umma_m, uint32_t umma_n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return ((b_sf_id & 3u) << 4) | ((umma_n >> 3) << 17) | (1u << 23) | ((umma_m >> 4) << 24) |
+         ((a_sf_id & 3u) << 29);
+}
+
+// ---- block scales in memory ---------------------------------------------------
+// The scales of a [rows, K] operand are stored in "atoms" of 512 bytes that cover 128 rows x
+// 128 elements of K (4 scales per row): atom (rows / 128, k / 128), the K index running fastest;
+// inside an atom the scale of row r, 32-element block j (0..3) is byte (r % 32) * 16 + (r / 32) * 4 + j.
+// That is 32 lines of 16 bytes: exactly what one tcgen05.cp.32x128b.warpx4 moves into four
+// TMEM columns (line l to lane l of every lane quarter), where the MMA expects row r's scales
+// in lane r % 32, column r / 32. Buffers are padded to whole atoms in both directions.
+constexpr uint32_t kSfAtomBytes = 512;
+constexpr uint32_t kSfAtomRows = 128;
+constexpr uint32_t kSfBlockElems = 32;   // K elements per scale
+PATINA_HD constexpr uint64_t mx_scale_atoms(uint64_t rows, uint64_t k) {
+  return ((rows + 127) / 128) * ((k + 127) / 128);
+}
+PATINA_HD constexpr uint64_t mx_scale_offset(uint64_t row, uint64_t k_block32, uint64_t k) {
+  return ((row / 128) * ((k + 127) / 128) + k_block32 / 4) * kSfAtomBytes + (row % 32) * 16 +
+         ((row % 128) / 32) * 4 + (k_block32 % 4);
+}
+// Atoms of B's scales that a tile of width block_n (a multiple of 32) can touch: tiles start at
+// multiples of block_n, so at 0, 32, 64 or 96 rows into an atom.
+PATINA_HD constexpr uint32_t mx_sfb_atoms(uint32_t block_n) {
+  uint32_t most = 0;
+  for (uint32_t j = 0; j < 4; ++j) {
+    const uint32_t need = ((block_n * j) % 128 + block_n + 127) / 128;
+    most = need > most ? need : most;
+  }
+  return most;
 }
 
 // Elements of K one MMA instruction consumes: 32 bytes of a K-major row.
@@ -129,7 +171,8 @@ PATINA_HD constexpr uint32_t staging_buf_bytes(uint32_t m_sub, uint32_t out_byte
 }
 
 PATINA_HD constexpr SmemPlan smem_plan(uint32_t cta_group, uint32_t m_sub, uint32_t block_n,
-                                       uint32_t stages, uint32_t out_bytes = 2) {
+                                       uint32_t stages, uint32_t out_bytes = 2,
+                                       uint32_t sf_stage_bytes = 0) {
   SmemPlan p{};
   p.a_bytes = m_sub * kCtaRows * kBlockKBytes;
   p.b_bytes = (block_n / cta_group) * kBlockKBytes;
@@ -138,7 +181,8 @@ PATINA_HD constexpr SmemPlan smem_plan(uint32_t cta_group, uint32_t m_sub, uint3
   p.staging_bytes = 4 * m_sub * staging_bufs(m_sub) * staging_buf_bytes(m_sub, out_bytes);
   p.barrier_bytes = kBarrierRegionBytes;
   // +1024: the ring is placed on the next 1024-byte boundary (swizzle atom).
-  p.total_bytes = 1024 + stages * p.stage_bytes + p.staging_bytes + p.barrier_bytes;
+  // (block-scaled operands: the scales of a stage sit in a ring of their own behind the staging)
+  p.total_bytes = 1024 + stages * p.stage_bytes + p.staging_bytes + stages * sf_stage_bytes + p.barrier_bytes;
   return p;
 }
 

@@ -127,7 +127,30 @@ constexpr int kNumGroupedKernels = sizeof(kGroupedKernels) / sizeof(kGroupedKern
 static_assert(GemmTraits<2, 2, 256, 4, kBF16, kOutBF16>::kSmemBytes + kGroupTableBytes <= kMaxDynSmem,
               "group tables do not fit behind the largest kernel's shared memory");
 
+// Block-scaled e4m3 (MXFP8) -> bf16. Widths are multiples of 32 (the scales of 32 rows of B
+// share a TMEM lane range). 256-wide accumulators leave no room in TMEM for a second buffer
+// next to the scale columns; 224 and 192 do.
+using MxFn = void (*)(const CUtensorMap, const CUtensorMap, const CStoreMaps<1>, const CUtensorMap,
+                      const CUtensorMap, const GemmParams);
+struct MxKernelEntry {
+  int cta_group, m_sub, block_n, stages;
+  MxFn fn;
+  uint32_t smem_bytes;
+};
+#define PATINA_MX(G, MS, BN, S) \
+  { G, MS, BN, S, gemm_mx_tn_kernel<G, MS, BN, S>, GemmTraits<G, MS, BN, S, kMXE4M3, kOutBF16>::kSmemBytes }
+const MxKernelEntry kMxKernels[] = {
+    PATINA_MX(2, 2, 192, 4),  // 512 x 192 per pair: accumulators + scales fill TMEM
+    PATINA_MX(2, 1, 224, 6),  // 256 x 224 per pair, double-buffered accumulators
+    PATINA_MX(2, 1, 256, 5),  // 256 x 256 per pair, one accumulator
+    PATINA_MX(1, 1, 224, 4),  // 128 x 224, double-buffered
+    PATINA_MX(1, 1, 192, 4),  // 128 x 192, double-buffered
+    PATINA_MX(1, 1, 128, 5),  // 128 x 128, double-buffered: small problems
+};
+constexpr int kNumMxKernels = sizeof(kMxKernels) / sizeof(kMxKernels[0]);
+
 bool type_pair_supported(int in_type, int out_type) {
+  if (in_type == kMXE4M3) return out_type == kOutBF16;
   for (int i = 0; i < kNumKernels; ++i)
     if (kKernels[i].in_type == in_type && kKernels[i].out_type == out_type) return true;
   return false;
@@ -352,6 +375,8 @@ struct PatinaGemmContext {
   uint32_t* d_sk_counters = nullptr;
   size_t cap_sk_partials = 0, cap_sk_counters = 0;
   bool sk_attr_set[2] = {false, false};
+  bool mx_attr_set[kNumMxKernels] = {};
+  int mx_max_clusters[kNumMxKernels] = {};
   uint32_t sk_burst = 4;
   // copy streams and events of patina_gemm_host's pipelined form
   cudaStream_t s_in = nullptr, s_out = nullptr;
@@ -750,6 +775,159 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   return PATINA_GEMM_OK;
 }
 
+// The scale buffer of a [rows, K] operand as a 2-D tensor of 32-bit words: one 512-byte atom per
+// line, lines in (row block, k atom) order. One box = one atom.
+int get_scale_tensor_map(PatinaGemmContext* ctx, const void* ptr, uint64_t atoms, CUtensorMap* out) {
+  TensorMapKey key{ptr, atoms, 128, 128, 1, 128, (int)CU_TENSOR_MAP_DATA_TYPE_UINT32};
+  for (size_t i = 0; i < ctx->tmaps.size(); ++i) {
+    if (ctx->tmaps[i].first == key) {
+      *out = ctx->tmaps[i].second;
+      return PATINA_GEMM_OK;
+    }
+  }
+  const cuuint64_t gdim[2] = {128, atoms};
+  const cuuint64_t gstride[1] = {kSfAtomBytes};
+  const cuuint32_t box[2] = {128, 1};
+  const cuuint32_t estride[2] = {1, 1};
+  CUtensorMap tm;
+  CUresult rc = ctx->encode(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), gdim, gstride, box,
+                            estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return set_error(ctx, PATINA_GEMM_ERR_CUDA,
+                     fmt("cuTensorMapEncodeTiled failed (CUresult %d) for a scale buffer of %llu atoms", (int)rc,
+                         (unsigned long long)atoms));
+  if (ctx->tmaps.size() >= 64) ctx->tmaps.pop_back();
+  ctx->tmaps.insert(ctx->tmaps.begin(), std::make_pair(key, tm));
+  *out = tm;
+  return PATINA_GEMM_OK;
+}
+
+// Same scoring as the other types, on the block-scaled table.
+const MxKernelEntry* pick_mx_kernel(int64_t M, int64_t N, int64_t K, const PatinaGemmConfig* cfg, int num_sms) {
+  const bool explicit_tile = cfg && (cfg->cta_group != 0 || cfg->block_n != 0 || cfg->m_sub != 0);
+  const MxKernelEntry* best = nullptr;
+  double best_score = -1.0;
+  for (int i = 0; i < kNumMxKernels; ++i) {
+    const MxKernelEntry& k = kMxKernels[i];
+    if (explicit_tile) {
+      if (cfg->cta_group != 0 && k.cta_group != cfg->cta_group) continue;
+      if (cfg->block_n != 0 && k.block_n != cfg->block_n) continue;
+      if (k.m_sub != (cfg->m_sub != 0 ? cfg->m_sub : 1)) continue;
+      return &k;
+    }
+    if (k.cta_group == 2 && num_sms < 2) continue;
+    KernelEntry as{k.cta_group, k.m_sub, k.block_n, k.stages, kE4M3, kOutBF16, nullptr, nullptr, nullptr, 0};
+    double s = config_score(as, M, N, K, num_sms);
+    if (k.block_n == 256) s *= 0.93;  // one accumulator: the epilogue is not hidden
+    if (s > best_score) {
+      best_score = s;
+      best = &k;
+    }
+  }
+  return best;
+}
+
+int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sfa, const void* B, int64_t ldb,
+              const void* sfb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha,
+              const PatinaGemmConfig* cfg, cudaStream_t stream) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  std::string err;
+  int rc = validate_args(kMXE4M3, kOutBF16, A, lda, B, ldb, C, ldc, M, N, K, &err);
+  if (rc != PATINA_GEMM_OK) return set_error(ctx, rc, err);
+  if (M == 0 || N == 0) return PATINA_GEMM_OK;
+  if (K % kSfBlockElems != 0)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
+                     fmt("K=%lld: block-scaled operands need K to be a multiple of 32", (long long)K));
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok) return set_error(ctx, PATINA_GEMM_ERR_CUDA, "cudaSetDevice failed");
+  if (K == 0) {
+    cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 2, 0, (size_t)N * 2, (size_t)M, stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaMemset2DAsync");
+    return PATINA_GEMM_OK;
+  }
+  if (!sfa || !sfb || (reinterpret_cast<uintptr_t>(sfa) & 15u) || (reinterpret_cast<uintptr_t>(sfb) & 15u))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "a scale buffer is null or not 16-byte aligned");
+  const MxKernelEntry* k = pick_mx_kernel(M, N, K, cfg, ctx->num_sms);
+  if (!k) return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "no block-scaled kernel for this tile request");
+  const int ki = (int)(k - kMxKernels);
+
+  const uint32_t kelems = kBlockKBytes;  // one byte per element
+  const uint32_t tile_m = 128u * k->cta_group * k->m_sub;
+  CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
+  CStoreMaps<1> tm_c;
+  rc = get_tensor_map(ctx, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kCtaRows,
+                      kelems, &tm_a);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
+                      (uint32_t)(k->block_n / k->cta_group), kelems, &tm_b);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldc,
+                      kStoreBoxRows, staging_row_bytes((uint32_t)k->m_sub, 2) / 2, &tm_c.map[0]);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_scale_tensor_map(ctx, sfa, mx_scale_atoms((uint64_t)M, (uint64_t)K), &tm_sfa);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_scale_tensor_map(ctx, sfb, mx_scale_atoms((uint64_t)N, (uint64_t)K), &tm_sfb);
+  if (rc != PATINA_GEMM_OK) return rc;
+
+  if (!ctx->mx_attr_set[ki]) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k->fn),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->smem_bytes);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(smem, block-scaled)");
+    ctx->mx_attr_set[ki] = true;
+  }
+  GemmParams p{};
+  p.M = (uint32_t)M;
+  p.N = (uint32_t)N;
+  p.K = (uint32_t)K;
+  p.tiles_m = ceil_div(M, tile_m);
+  p.tiles_n = ceil_div(N, k->block_n);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.k_blocks = ceil_div(K, kelems);
+  p.group_m = (cfg && cfg->group_m > 0) ? (uint32_t)cfg->group_m : 8u;
+  p.alpha = alpha;
+  p.n_dests = 1;
+  p.c_dests[0] = C;
+  p.ldc = ldc;
+  p.sf_m_blocks = ceil_div(M, kSfAtomRows);
+  p.sf_n_blocks = ceil_div(N, kSfAtomRows);
+  p.sf_k_atoms = ceil_div(K, 128);
+  p.status = ctx->d_status;
+  p.wait_limit_ns = ctx->wait_limit_ns;
+#ifdef PATINA_TRACE
+  p.trace = nullptr;
+#endif
+  uint32_t slots = (uint32_t)(ctx->num_sms / k->cta_group);
+  if (k->cta_group > 1) {
+    KernelEntry as{k->cta_group, k->m_sub, k->block_n, k->stages, kMXE4M3, kOutBF16,
+                   reinterpret_cast<KernelFn>(k->fn), nullptr, nullptr, k->smem_bytes};
+    const uint32_t cap = (uint32_t)resident_clusters(&as, ctx->num_sms, &ctx->mx_max_clusters[ki]);
+    if (cap < slots) slots = cap;
+  }
+  if (cfg && cfg->max_ctas > 0 && (uint32_t)(cfg->max_ctas / k->cta_group) < slots)
+    slots = (uint32_t)(cfg->max_ctas / k->cta_group);
+  if (slots == 0) slots = 1;
+  const uint32_t clusters = p.num_tiles < slots ? p.num_tiles : slots;
+
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(clusters * k->cta_group, 1, 1);
+  lc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
+  lc.dynamicSmemBytes = k->smem_bytes;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)k->cta_group;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = (k->cta_group > 1) ? 1 : 0;
+  drain_stale_error();
+  cudaError_t e = cudaLaunchKernelEx(&lc, k->fn, tm_a, tm_b, tm_c, tm_sfa, tm_sfb, p);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaLaunchKernelEx(block-scaled)");
+  ctx->launches += 1;
+  return PATINA_GEMM_OK;
+}
+
 // One launch for n_groups GEMMs that share N and K: A and C hold the groups' rows one after
 // another, B one [N, K] block per group, the row counts live in device memory.
 int launch_grouped(PatinaGemmContext* ctx, int in_type, const void* A, int64_t lda, const void* B,
@@ -1106,6 +1284,26 @@ int patina_gemm_fp8e4m3_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_
                                    void* stream) {
   return launch_grouped(ctx, kE4M3, A, lda, B, ldb, C, ldc, group_rows, n_groups, total_rows, N, K,
                         scale_a, group_scale_b, config, static_cast<cudaStream_t>(stream));
+}
+
+int patina_gemm_mxfp8_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* scales_a,
+                         const void* B, int64_t ldb, const void* scales_b, void* C, int64_t ldc, int64_t M,
+                         int64_t N, int64_t K, float alpha, const PatinaGemmConfig* config, void* stream) {
+  return launch_mx(ctx, A, lda, scales_a, B, ldb, scales_b, C, ldc, M, N, K, alpha, config,
+                   static_cast<cudaStream_t>(stream));
+}
+
+uint64_t patina_gemm_mx_scale_bytes(int64_t rows, int64_t K) {
+  if (rows <= 0 || K <= 0) return 0;
+  return mx_scale_atoms((uint64_t)rows, (uint64_t)K) * kSfAtomBytes;
+}
+
+uint64_t patina_gemm_mx_scale_offset(int64_t row, int64_t k_block32, int64_t K) {
+  return mx_scale_offset((uint64_t)row, (uint64_t)k_block32, (uint64_t)K);
+}
+
+uint32_t patina_gemm_idesc_mx(uint32_t umma_m, uint32_t umma_n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return idesc_mx(umma_m, umma_n, a_sf_id, b_sf_id);
 }
 
 // ---- buffers that other processes on the node can write ------------------------------------

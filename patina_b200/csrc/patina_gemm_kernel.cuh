@@ -78,6 +78,9 @@ struct GemmParams {
   // written row by row from the registers instead.
   void* c_dests[kMaxDests];
   int64_t ldc;
+  // block-scaled operands (kernels instantiated with kMXE4M3): extents of the scale buffers in
+  // atoms of 128 rows x 128 K elements, so that tiles hanging over the edge read inside them
+  uint32_t sf_m_blocks, sf_n_blocks, sf_k_atoms;
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
 #ifdef PATINA_TRACE
@@ -196,8 +199,17 @@ struct GemmTraits {
   static constexpr uint32_t kBBytes = kBRows * kBlockKBytes;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kAccCols = kMSub * BN;                  // TMEM columns of one tile
-  static constexpr uint32_t kAccBufs = (2 * kAccCols <= 512) ? 2 : 1;
-  static constexpr uint32_t kTmemUsed = kAccBufs * kAccCols;
+  // Block-scaled operands: every stage also carries the scale atoms of its A slabs and of the
+  // rows of B under the tile (512 bytes each), and TMEM holds one 4-column copy of each behind
+  // the accumulators, rewritten for every k-block (tcgen05.cp and tcgen05.mma run in issue order).
+  static constexpr bool kMx = is_block_scaled(kIn);
+  static constexpr uint32_t kSfbAtoms = kMx ? mx_sfb_atoms(BN) : 0u;
+  static constexpr uint32_t kSfAtoms = kMx ? (kMSub + kSfbAtoms) : 0u;
+  static constexpr uint32_t kSfStageBytes = kSfAtoms * kSfAtomBytes;
+  static constexpr uint32_t kSfCols = 4u * kSfAtoms;
+  static constexpr uint32_t kAccBufs = (2 * kAccCols + kSfCols <= 512) ? 2 : 1;
+  static constexpr uint32_t kSfCol0 = kAccBufs * kAccCols;          // first scale column
+  static constexpr uint32_t kTmemUsed = kAccBufs * kAccCols + kSfCols;
   // tcgen05.alloc takes powers of two (32..512): round the request up
   static constexpr uint32_t kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128
                                         : kTmemUsed <= 256 ? 256 : 512;
@@ -211,7 +223,8 @@ struct GemmTraits {
   static constexpr uint32_t kChunks = (BN + kChunkCols - 1) / kChunkCols;
   static constexpr bool kOverlapLastChunk = (BN % kChunkCols) != 0;
   static constexpr uint32_t kSmemBytes =
-      smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut)).total_bytes;
+      smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut), kSfStageBytes).total_bytes;
+  static_assert(!kMx || BN % 32 == 0, "block-scaled tiles: the scales of 32 rows of B share a TMEM lane range");
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
   static_assert(kTmemUsed <= 512, "accumulators exceed the 512 TMEM columns");
@@ -221,14 +234,19 @@ struct GemmTraits {
   static_assert((2 * kStages + 4) * 8 + 8 <= kBarrierRegionBytes, "barrier region too small");
 };
 
-template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused = false,
-          bool kGrouped = false, int kDests = 1>
-__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-               const __grid_constant__ CStoreMaps<kDests> tm_c, const GemmParams p) {
+// The kernel body; the __global__ entries below differ only in their parameter lists (the
+// block-scaled one carries two more tensor maps, for the scales of A and B).
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused, bool kGrouped,
+          int kDests>
+__device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUtensorMap& tm_b,
+                                             const CStoreMaps<kDests>& tm_c, const GemmParams& p,
+                                             const CUtensorMap* tm_sfa, const CUtensorMap* tm_sfb) {
   using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut>;
   constexpr bool kPair = (kCtaGroup == 2);
+  constexpr bool kMx = T::kMx;
   constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
+  static_assert(!kMx || (!kFused && !kGrouped && kDests == 1 && kOut == kOutBF16),
+                "block-scaled operands: plain bf16 epilogue only");
   constexpr uint32_t kEpiWarps = T::kEpiWarps;
   // The fused epilogue may read C itself as the residual, so no column may be produced twice.
   static_assert(!(kFused && T::kOverlapLastChunk), "fused epilogue needs whole store boxes");
@@ -239,7 +257,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = smem_base;
   const uint32_t staging = ring + kStages * T::kStageBytes;
-  const uint32_t bars = staging + kEpiWarps * T::kStageBufs * T::kBufBytes;
+  const uint32_t sf_ring = staging + kEpiWarps * T::kStageBufs * T::kBufBytes;  // [kStages] scale atoms
+  const uint32_t bars = sf_ring + kStages * T::kSfStageBytes;
   const uint32_t full_bar = bars;                      // [kStages]
   const uint32_t empty_bar = bars + 8u * kStages;      // [kStages]
   const uint32_t tfull_bar = bars + 16u * kStages;     // [2]
@@ -276,6 +295,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_b);
     for (uint32_t d = 0; d < (uint32_t)kDests && d < p.n_dests; ++d) ptx::prefetch_tensormap(&tm_c.map[d]);
+    if constexpr (kMx) {
+      ptx::prefetch_tensormap(tm_sfa);
+      ptx::prefetch_tensormap(tm_sfb);
+    }
     for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
       ptx::mbar_init(full_bar + 8u * s, 1);
       ptx::mbar_init(empty_bar + 8u * s, 1);
@@ -293,7 +316,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   // complete on the leader's barriers, which the partner may only use after the cluster-wide
   // barrier below; a grouped launch needs its tables first.)
   uint32_t pre_kb = 0;
-  if constexpr (!kPair && !kGrouped) {
+  if constexpr (!kPair && !kGrouped && !kMx) {
     if (threadIdx.x == 0 && cluster_id < p.num_tiles) {
       ptx::fence_proxy_async_smem();
       const TileCoord c0 = tile_coord(cluster_id, p.tiles_m, p.tiles_n, p.group_m);
@@ -408,7 +431,27 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int32_t a_row = (int32_t)(c.row_base + c.m * T::kTileM + cta_rank * kCtaRows);
         const int32_t b_row = (int32_t)(c.b_row_base + c.n * BN + cta_rank * T::kBRows);
         const uint32_t n_sub = live_subtiles(c);
-        const uint32_t stage_tx = n_sub * T::kASubBytes + T::kBBytes;  // bytes this CTA loads per stage
+        // bytes this CTA loads per stage
+        const uint32_t stage_tx = n_sub * T::kASubBytes + T::kBBytes + T::kSfStageBytes;
+        // Block scales: the atom row of each A slab, and the atoms under this tile's rows of B
+        // (all of them in both CTAs of a pair: every CTA's accumulator has all BN columns).
+        // Indices are clamped into the buffers; an atom past the edge only scales rows or columns
+        // that are never stored.
+        uint32_t sfa_atom[kMSub] = {}, sfb_atom[T::kSfbAtoms > 0 ? T::kSfbAtoms : 1] = {};
+        if constexpr (kMx) {
+#pragma unroll
+          for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
+            uint32_t mb = ((uint32_t)a_row + ms * kCtaRows * kCtaGroup) / kSfAtomRows;
+            mb = mb < p.sf_m_blocks ? mb : p.sf_m_blocks - 1u;
+            sfa_atom[ms] = mb * p.sf_k_atoms;
+          }
+#pragma unroll
+          for (uint32_t a = 0; a < T::kSfbAtoms; ++a) {
+            uint32_t nb = (c.n * BN) / kSfAtomRows + a;
+            nb = nb < p.sf_n_blocks ? nb : p.sf_n_blocks - 1u;
+            sfb_atom[a] = nb * p.sf_k_atoms;
+          }
+        }
         bool ok = true;
         for (uint32_t kb = kb_first; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
@@ -424,6 +467,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
                                     a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
+            if constexpr (kMx) {
+              const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
+#pragma unroll
+              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
+                ptx::tma_load_2d_pair(sfs + ms * kSfAtomBytes, tm_sfa, leader_full + 8u * s, 0,
+                                      (int32_t)(sfa_atom[ms] + kb));
+#pragma unroll
+              for (uint32_t a = 0; a < T::kSfbAtoms; ++a)
+                ptx::tma_load_2d_pair(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, leader_full + 8u * s, 0,
+                                      (int32_t)(sfb_atom[a] + kb));
+            }
           } else {
             ptx::mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
 #pragma unroll
@@ -432,6 +486,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * s, k0,
                                a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d(sb, &tm_b, full_bar + 8u * s, k0, b_row);
+            if constexpr (kMx) {
+              const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
+#pragma unroll
+              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
+                ptx::tma_load_2d(sfs + ms * kSfAtomBytes, tm_sfa, full_bar + 8u * s, 0,
+                                 (int32_t)(sfa_atom[ms] + kb));
+#pragma unroll
+              for (uint32_t a = 0; a < T::kSfbAtoms; ++a)
+                ptx::tma_load_2d(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, full_bar + 8u * s, 0,
+                                 (int32_t)(sfb_atom[a] + kb));
+            }
           }
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
         }
@@ -449,8 +514,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       uint32_t s = 0, ph = 0, it = 0, grp = 0;
       bool ok = true;
       for (uint32_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
-        const uint32_t n_sub = live_subtiles(locate(t, grp));
+        const TileSpot c = locate(t, grp);
+        const uint32_t n_sub = live_subtiles(c);
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
+        // block scales in TMEM: A's slabs first, then B's atoms; the tile's first row of B may
+        // lie 32, 64 or 96 rows into its first atom, i.e. 1, 2 or 3 columns in
+        const uint32_t tsfa0 = tmem_base + T::kSfCol0;
+        const uint32_t tsfb0 = tsfa0 + 4u * (uint32_t)kMSub + ((c.n * BN) % kSfAtomRows) / 32u;
         ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
         if (!ok) break;
         ptx::tc_fence_after_sync();
@@ -462,6 +532,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           if (it == 0 && kb == 0) PATINA_TRACE_AT(2);
           const uint32_t sa = ring + s * T::kStageBytes;
           const uint64_t db = smem_desc_sw128_kmajor(sa + T::kABytes);
+          if constexpr (kMx) {
+            // this k-block's scales: shared memory -> TMEM, 32 lines of 16 bytes per atom (8-line
+            // groups 128 bytes apart, no swizzle)
+            const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
+#pragma unroll
+            for (uint32_t j = 0; j < T::kSfAtoms; ++j)
+              ptx::tmem_cp_32x128b_warpx4<kCtaGroup>(tsfa0 + 4u * j,
+                                                     smem_desc(sfs + j * kSfAtomBytes, 0, 128, kSwizzleNone));
+          }
 #pragma unroll
           for (uint32_t k = 0; k < T::kUmmaPerStage; ++k) {
             const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
@@ -469,8 +548,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
               if (ms < n_sub) {
                 const uint64_t da = smem_desc_sw128_kmajor(sa + ms * T::kASubBytes);
-                ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db + adv, idesc_v,
-                                            (kb | k) != 0u);
+                if constexpr (kMx) {
+                  // the k-th 32-element block of this stage uses byte k of each scale column
+                  ptx::umma_mx<kCtaGroup>(tmem_d + ms * BN, da + adv, db + adv,
+                                          idesc_mx(kCtaRows * kCtaGroup, BN, k, k),
+                                          (tsfa0 + 4u * ms) | (k << 30), tsfb0 | (k << 30), (kb | k) != 0u);
+                } else {
+                  ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db + adv, idesc_v,
+                                              (kb | k) != 0u);
+                }
               }
             }
           }
@@ -794,6 +880,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   ptx::tc_fence_after_sync();
   if (warp_idx == 1) ptx::tmem_dealloc<kCtaGroup>(tmem_base, T::kTmemCols);
   if (threadIdx.x == 32) PATINA_TRACE_AT(7);
+}
+
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused = false,
+          bool kGrouped = false, int kDests = 1>
+__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const __grid_constant__ CStoreMaps<kDests> tm_c, const GemmParams p) {
+  gemm_tn_body<kCtaGroup, kMSub, BN, kStages, kIn, kOut, kFused, kGrouped, kDests>(tm_a, tm_b, tm_c, p,
+                                                                                   nullptr, nullptr);
+}
+
+// Block-scaled operands (e4m3 elements, one E8M0 scale per 32 K elements of a row): the same
+// kernel with the scale buffers of A and B as two more tensor maps.
+template <int kCtaGroup, int kMSub, int BN, int kStages>
+__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
+gemm_mx_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CStoreMaps<1> tm_c, const __grid_constant__ CUtensorMap tm_sfa,
+                  const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
+  gemm_tn_body<kCtaGroup, kMSub, BN, kStages, kMXE4M3, kOutBF16, false, false, 1>(tm_a, tm_b, tm_c, p,
+                                                                                 &tm_sfa, &tm_sfb);
 }
 
 }  // namespace patina

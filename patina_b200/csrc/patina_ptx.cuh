@@ -273,6 +273,37 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
         : "memory");
 }
 
+// Block-scaled form (kind::mxf8f6f4.block_scale, one scale per 32 K elements): the scales of A
+// and B are read from TMEM at tsfa / tsfb (bits 30-31 of those addresses and the descriptor's
+// scale ids select the byte of the 32-bit scale column).
+template <int kCtaGroup>
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+  if constexpr (kCtaGroup == 1)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
+}
+
+// Shared memory -> TMEM: 32 lines of 16 bytes (described by a no-swizzle matrix descriptor) go to
+// 4 consecutive TMEM columns of lanes 0..31 and are repeated in the other three lane quarters.
+// With cta_group::2 each CTA of the pair copies from its own shared memory into its own TMEM.
+template <int kCtaGroup>
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  if constexpr (kCtaGroup == 1)
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+  else
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 // One arrival on `cluster_bar` (a shared::cluster address: this CTA's or its
 // pair partner's) once every tcgen05 operation this thread issued so far has
 // completed. Plain (non-multicast) form; a pair is signalled with two calls.

@@ -155,6 +155,33 @@ class GemmContext:
             self._raise(rc)
         return out
 
+    def gemm_mxfp8_tn(self, Aq, scales_a, Bq, scales_b, out=None, alpha: float = 1.0,
+                      config: GemmConfig | None = None):
+        """bf16 out = alpha * (Aq * sa) @ (Bq * sb)^T for block-scaled fp8 operands: Aq [M, K] and
+        Bq [N, K] float8_e4m3fn (or uint8-viewed) CUDA tensors, scales_a / scales_b uint8 CUDA
+        tensors holding one E8M0 scale per 32 K elements of a row in the library's atom layout
+        (`inputs.pack_mx_scales`); K a multiple of 32."""
+        M, K = Aq.shape
+        N = Bq.shape[0]
+        if not (Aq.is_cuda and Bq.is_cuda and scales_a.is_cuda and scales_b.is_cuda):
+            raise PatinaGemmError(_l.ERR_INVALID_ARG, "operands and scales must be CUDA tensors (no CPU path)")
+        need_a = int(self._lib.patina_gemm_mx_scale_bytes(M, K))
+        need_b = int(self._lib.patina_gemm_mx_scale_bytes(N, K))
+        if scales_a.element_size() != 1 or scales_b.element_size() != 1 or scales_a.numel() < need_a \
+                or scales_b.numel() < need_b or not scales_a.is_contiguous() or not scales_b.is_contiguous():
+            raise PatinaGemmError(_l.ERR_INVALID_ARG,
+                                  f"scale buffers must be contiguous bytes of at least {need_a} and {need_b}")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=Aq.device)
+        rc = self._lib.patina_gemm_mxfp8_tn(
+            self._h, Aq.data_ptr(), Aq.stride(0) if M > 1 else max(K, 1), scales_a.data_ptr(), Bq.data_ptr(),
+            Bq.stride(0) if N > 1 else max(K, 1), scales_b.data_ptr(), out.data_ptr(),
+            out.stride(0) if M > 1 else max(N, 1), M, N, K, float(alpha),
+            C.byref(config) if config is not None else None, _stream_ptr(self.device))
+        if rc != _l.OK:
+            self._raise(rc)
+        return out
+
     def gemm_f16_tn_f32out(self, A, B, out=None, alpha=1.0):
         M, K = A.shape
         N = B.shape[0]

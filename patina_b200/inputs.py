@@ -53,3 +53,41 @@ def make_fp8_operands(M: int, N: int, K: int, seed: int = DEFAULT_SEED):
     Aq, sa = quantize_e4m3(A)
     Bq, sb = quantize_e4m3(B)
     return Aq, sa, Bq, sb
+
+
+# ------------------------------------------------------------ block-scaled fp8 (MXFP8)
+def quantize_mxfp8(x: torch.Tensor):
+    """Block-scaled fp8 of a [rows, K] float tensor, K a multiple of 32: every 32 consecutive K
+    elements of a row share a power-of-two scale 2^(e - 127), e = ceil(log2(amax / 448)) + 127
+    stored as one E8M0 byte, and the elements are e4m3_rne(x / scale). Returns
+    (q [rows, K] float8_e4m3fn, e [rows, K / 32] uint8)."""
+    rows, K = x.shape
+    assert K % 32 == 0
+    blocks = x.float().reshape(rows, K // 32, 32)
+    amax = blocks.abs().amax(dim=2)
+    exp = torch.ceil(torch.log2(torch.clamp(amax, min=2.0 ** -120) / 448.0)).clamp_(-127, 127)
+    scale = torch.exp2(exp)
+    q = (blocks / scale[..., None]).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn).reshape(rows, K)
+    return q, (exp + 127).to(torch.uint8)
+
+
+def pack_mx_scales(e: torch.Tensor, fill: int = 127) -> torch.Tensor:
+    """Scales [rows, K / 32] (uint8) in the layout the library's block-scaled GEMM takes: atoms of
+    512 bytes covering 128 rows x 4 scales, atom index (row / 128) * ceil(K / 128) + kb / 4, byte
+    (row % 32) * 16 + ((row % 128) / 32) * 4 + kb % 4 inside; padded to whole atoms with `fill`
+    (127 = the scale 1.0; padding must not be 0xFF, which is NaN)."""
+    rows, kb = e.shape
+    rb, ka = (rows + 127) // 128, (kb + 3) // 4
+    padded = torch.full((rb * 128, ka * 4), fill, dtype=torch.uint8, device=e.device)
+    padded[:rows, :kb] = e
+    # [rb, 4 (row / 32), 32 (row % 32), ka, 4 (kb % 4)] -> [rb, ka, 32, 4, 4]
+    v = padded.view(rb, 4, 32, ka, 4).permute(0, 3, 2, 1, 4).contiguous()
+    return v.view(-1)
+
+
+def make_mxfp8_operands(M: int, N: int, K: int, seed: int = DEFAULT_SEED, workload: str = "unit_normal"):
+    """(Aq, ea, Bq, eb): block-scaled fp8 operands drawn from a named distribution."""
+    A, B = make_operands(workload, M, N, K, dtype=torch.float32, seed=seed)
+    Aq, ea = quantize_mxfp8(A)
+    Bq, eb = quantize_mxfp8(B)
+    return Aq, ea, Bq, eb

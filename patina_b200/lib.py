@@ -10,7 +10,7 @@ import os
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libpatina_gemm.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED_ARCH, ERR_CUDA, ERR_TIMEOUT = 0, 1, 2, 3, 4
-IN_F16, IN_BF16, IN_E4M3 = 0, 1, 2
+IN_F16, IN_BF16, IN_E4M3, IN_MXE4M3 = 0, 1, 2, 3
 OUT_BF16, OUT_F32, OUT_E4M3 = 0, 1, 2
 
 # every symbol include/patina_gemm.h declares
@@ -23,6 +23,7 @@ SYMBOLS = (
     "patina_gemm_k_advance_units", "patina_gemm_tmem_lane_offset", "patina_gemm_tile_coord",
     "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_chosen", "patina_gemm_streamk_range",
     "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped", "patina_gemm_fp8e4m3_tn_grouped",
+    "patina_gemm_mxfp8_tn", "patina_gemm_mx_scale_bytes", "patina_gemm_mx_scale_offset", "patina_gemm_idesc_mx",
     "patina_gemm_peer_alloc",
     "patina_gemm_peer_open", "patina_gemm_peer_close", "patina_gemm_peer_free",
 )
@@ -122,6 +123,14 @@ def load() -> C.CDLL:
     L.patina_gemm_peer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
     L.patina_gemm_peer_close.argtypes = [vp, vp]
     L.patina_gemm_peer_free.argtypes = [vp, vp]
+    L.patina_gemm_mxfp8_tn.argtypes = [vp, vp, i64, vp, vp, i64, vp, vp, i64, i64, i64, i64, f32,
+                                       C.POINTER(GemmConfig), vp]
+    L.patina_gemm_mx_scale_bytes.argtypes = [i64, i64]
+    L.patina_gemm_mx_scale_bytes.restype = C.c_uint64
+    L.patina_gemm_mx_scale_offset.argtypes = [i64, i64, i64]
+    L.patina_gemm_mx_scale_offset.restype = C.c_uint64
+    L.patina_gemm_idesc_mx.argtypes = [C.c_uint32] * 4
+    L.patina_gemm_idesc_mx.restype = C.c_uint32
     L.patina_gemm_bf16_tn_skinny_noalloc.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, f32, vp,
                                                      C.c_char_p, C.c_size_t]
     _lib = L

@@ -112,3 +112,111 @@ def gemm_scatter_columns(ctx, A: torch.Tensor, B_shard: torch.Tensor, shared: Sh
     if n1 > n0:
         ctx.gemm_bf16_tn_scatter(A, B_shard, shared.column_block_ptrs(n0), shared.n_total, alpha=alpha)
     return shared.local
+
+
+# ----------------------------------------------------------- host buffers, many GPUs
+def row_blocks(m: int, world: int, max_blocks: int = 8, min_rows: int = 1024) -> list[tuple[int, int, int]]:
+    """Row blocks of the replicated A for the pipelined host-buffer call: (first row, one past
+    the last row, rows each rank uploads). A block is `world` equal slices (one per rank, the
+    last block's slices padded by the caller's buffer), so that every rank uploads 1/world of A
+    over its own PCIe link and NVLink carries the rest."""
+    if m <= 0:
+        return []
+    n_blocks = max(1, min(max_blocks, m // max(min_rows, 1)))
+    rows = -(-m // n_blocks)
+    rows = -(-rows // world) * world            # a whole number of slices
+    out = []
+    r0 = 0
+    while r0 < m:
+        r1 = min(m, r0 + rows)
+        out.append((r0, r1, rows // world))
+        r0 = r1
+    return out
+
+
+class _NoStream:
+    """Stands in for a CUDA stream where there is none (host-side tests of the orchestration)."""
+
+    def wait_stream(self, other): pass
+    def wait_event(self, ev): pass
+    def __enter__(self): return self
+    def __exit__(self, *exc): return False
+
+
+class _NoEvent:
+    def record(self, stream=None): pass
+
+
+class HostShardedGemm:
+    """C[:, n0:n1] = alpha * A @ B[n0:n1]^T from HOST buffers on every rank of a node, one
+    process per GPU: the multi-GPU form of `GemmContext.gemm_host`.
+
+    A is replicated (every rank holds the same host copy), so it crosses PCIe ONCE per node:
+    each rank uploads 1/world of every row block over its own link and an all-gather over
+    NVLink hands every rank the whole block. A rank's PCIe traffic per call is therefore
+    M*K/world + (n1-n0)*K elements in and M*(n1-n0) out. Row blocks are pipelined on three
+    streams: upload + all-gather of block i+1, the GEMM of block i and the copy-out of block
+    i-1 run concurrently. Device buffers are allocated once, at construction.
+
+    `gemm(A_block, B, out=C_block, alpha=...)` is the per-rank kernel call, by default the
+    context's; `device` "cpu" with an injected `gemm` runs the same orchestration without
+    streams (used by the host-side tests, never by the library itself).
+    """
+
+    def __init__(self, ctx, m: int, n_shard: int, k: int, dtype=torch.bfloat16, out_dtype=torch.bfloat16,
+                 group=None, device=None, gemm=None, max_blocks: int = 8):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.m, self.n, self.k = m, n_shard, k
+        self.device = torch.device("cuda", ctx.device) if device is None else torch.device(device)
+        self.gemm = gemm if gemm is not None else ctx.gemm_tn
+        self.blocks = row_blocks(m, self.world, max_blocks)
+        padded = (self.blocks[-1][0] + self.blocks[-1][2] * self.world) if self.blocks else 0
+        self.dA = torch.empty((max(padded, m), k), dtype=dtype, device=self.device)
+        self.dB = torch.empty((n_shard, k), dtype=dtype, device=self.device)
+        self.dC = torch.empty((m, n_shard), dtype=out_dtype, device=self.device)
+        cuda = self.device.type == "cuda"
+        self.s_in = torch.cuda.Stream(self.device) if cuda else _NoStream()
+        self.s_out = torch.cuda.Stream(self.device) if cuda else _NoStream()
+        mk = (lambda: torch.cuda.Event()) if cuda else (lambda: _NoEvent())
+        self.ev_b = mk()
+        self.ev_a = [mk() for _ in self.blocks]
+        self.ev_g = [mk() for _ in self.blocks]
+
+    def pcie_bytes(self) -> tuple[int, int]:
+        """(host-to-device, device-to-host) bytes this rank moves per call."""
+        up_rows = sum(min(per, max(0, min(r1, r0 + (self.rank + 1) * per) - (r0 + self.rank * per)))
+                      for r0, r1, per in self.blocks)
+        eb, ob = self.dA.element_size(), self.dC.element_size()
+        return (up_rows * self.k + self.n * self.k) * eb, self.m * self.n * ob
+
+    def __call__(self, hA: torch.Tensor, hB: torch.Tensor, hC: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
+        cuda = self.device.type == "cuda"
+        cur = torch.cuda.current_stream(self.device) if cuda else _NoStream()
+        scope = (lambda s: torch.cuda.stream(s)) if cuda else (lambda s: s)
+        self.s_in.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        with scope(self.s_in):
+            self.dB.copy_(hB, non_blocking=True)
+            self.ev_b.record(self.s_in)
+            for i, (r0, r1, per) in enumerate(self.blocks):
+                blk = self.dA[r0:r0 + per * self.world]
+                mine = blk[self.rank * per:(self.rank + 1) * per]
+                lo = r0 + self.rank * per
+                hi = min(r1, lo + per)
+                if hi > lo:
+                    mine[:hi - lo].copy_(hA[lo:hi], non_blocking=True)
+                if self.world > 1:
+                    # (in place on the GPU: `mine` is this rank's slot of `blk`)
+                    dist.all_gather_into_tensor(blk, mine if cuda else mine.clone(), group=self.group)
+                self.ev_a[i].record(self.s_in)
+        cur.wait_event(self.ev_b)
+        for i, (r0, r1, per) in enumerate(self.blocks):
+            cur.wait_event(self.ev_a[i])
+            self.gemm(self.dA[r0:r1], self.dB, out=self.dC[r0:r1], alpha=alpha)
+            self.ev_g[i].record(cur)
+            self.s_out.wait_event(self.ev_g[i])
+            with scope(self.s_out):
+                hC[r0:r1].copy_(self.dC[r0:r1], non_blocking=True)
+        cur.wait_stream(self.s_out)
+        return hC

@@ -237,3 +237,50 @@ def test_automatic_choice_between_the_two_kernels(built_lib):
     assert chosen(129, 3584, 8192) == 0        # the stream-K kernel holds at most 128 rows of X
     assert chosen(16, 28672, 8192, L.IN_E4M3) == 1
     assert chosen(128, 128, 4096, L.IN_F16, L.OUT_F32) == 0   # f32 output: large-tile kernel only
+
+
+def test_block_scaled_encodings(built_lib):
+    """The block-scaled (MXFP8) instruction descriptor and the scale-buffer layout. Field
+    positions as documented for tcgen05.mma kind::mxf8f6f4.block_scale: B scale id [4,6),
+    N >> 3 at bit 17, E8M0 scale format bit 23, M >> 4 at bit 24, A scale id [29,31); the
+    reference has no block-scaled path (its idesc 136314896 is the kind::f16 form)."""
+    import torch
+    from patina_b200 import inputs
+    L = built_lib
+    assert L.patina_gemm_idesc_mx(128, 256, 0, 0) == (32 << 17) | (1 << 23) | (8 << 24)
+    assert L.patina_gemm_idesc_mx(256, 224, 3, 2) == (2 << 4) | (28 << 17) | (1 << 23) | (16 << 24) | (3 << 29)
+    assert L.patina_gemm_mx_scale_bytes(128, 128) == 512
+    assert L.patina_gemm_mx_scale_bytes(129, 160) == 2 * 2 * 512
+    assert L.patina_gemm_mx_scale_bytes(0, 128) == 0
+    # the packer and the library's offset function describe the same layout
+    rows, K = 300, 416                      # 3 row blocks, 13 scales per row -> 4 atoms along K
+    e = torch.arange(rows * (K // 32), dtype=torch.int64).reshape(rows, K // 32)
+    e8 = (e % 251).to(torch.uint8)
+    packed = inputs.pack_mx_scales(e8, fill=127)
+    assert packed.numel() == L.patina_gemm_mx_scale_bytes(rows, K)
+    seen = torch.zeros(packed.numel(), dtype=torch.bool)
+    for r in (0, 1, 31, 32, 95, 127, 128, 200, 299):
+        for kb in range(K // 32):
+            off = L.patina_gemm_mx_scale_offset(r, kb, K)
+            assert int(packed[off]) == int(e8[r, kb]), (r, kb)
+            seen[off] = True
+    assert int(packed[L.patina_gemm_mx_scale_offset(299 + 1, 0, K)]) == 127      # padding rows
+    assert int(packed[L.patina_gemm_mx_scale_offset(0, 13, K)]) == 127           # padding scales
+    # byte position inside an atom: (r % 32) * 16 + (r / 32) * 4 + j
+    assert L.patina_gemm_mx_scale_offset(33, 2, 128) == 1 * 16 + 1 * 4 + 2
+    assert L.patina_gemm_mx_scale_offset(128 + 5, 4 + 1, 256) == (1 * 2 + 1) * 512 + 5 * 16 + 1
+
+
+def test_mx_quantiser_round_trip(oracle_mod):
+    """quantize_mxfp8 + oracle.mx_dequant: every element within half an e4m3 step of its block's
+    scale, blocks scaled independently."""
+    import numpy as np
+    import torch
+    from patina_b200 import inputs
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn((40, 96), generator=g) * torch.exp2(torch.randint(-5, 6, (40, 3, 1), generator=g).float()).expand(40, 3, 32).reshape(40, 96)
+    q, e = inputs.quantize_mxfp8(x)
+    back = oracle_mod.mx_dequant(q.view(torch.uint8).numpy(), e.numpy())
+    amax = x.reshape(40, 3, 32).abs().amax(dim=2, keepdim=True).expand(40, 3, 32).reshape(40, 96).numpy()
+    assert np.all(np.abs(back - x.numpy()) <= amax * 2.0 ** -3)      # e4m3: 3 mantissa bits, scale within 2x of amax/448
+    assert np.all(np.abs(back) <= 448.0 * np.ldexp(1.0, e.numpy().astype(np.int32) - 127).repeat(32, axis=1) + 0)

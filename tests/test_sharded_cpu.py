@@ -72,3 +72,74 @@ def test_all_gather_assembles_full_c_two_gloo_ranks(n_total):
         assert p.exitcode == 0
     assert sorted(r[0] for r in results) == [0, 1]
     assert all(ok and shape == (48, n_total) for _, ok, shape in results), results
+
+
+def test_row_blocks_cover_a_and_split_evenly():
+    for m, world in [(8192, 8), (8192, 1), (8192, 2), (1000, 3), (100, 8), (4100, 4), (1, 2)]:
+        blocks = sharded.row_blocks(m, world)
+        assert blocks[0][0] == 0 and blocks[-1][1] == m
+        for (a0, a1, per), (b0, _, _) in zip(blocks, blocks[1:]):
+            assert a1 == b0 and a1 - a0 == per * world      # full blocks are `world` equal slices
+        r0, r1, per = blocks[-1]
+        assert 0 < r1 - r0 <= per * world
+    assert sharded.row_blocks(0, 4) == []
+    assert len(sharded.row_blocks(8192, 8)) == 8 and sharded.row_blocks(8192, 8)[0] == (0, 1024, 128)
+
+
+def _host_worker(rank, world, port, shape, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        M, N, K = shape
+        rng = np.random.default_rng(11)                 # the same host copy of A and B on every rank
+        A = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32))
+        B = torch.from_numpy(rng.standard_normal((N, K)).astype(np.float32))
+        n0, n1 = sharded.column_shard(N, world, rank, align=8)
+
+        def cpu_gemm(a, b, out=None, alpha=1.0):
+            out.copy_(torch.from_numpy((alpha * oracle.ref_gemm_tn(a.contiguous().numpy(),
+                                                                    b.contiguous().numpy())).astype(np.float32)))
+
+        class FakeCtx:
+            device = 0
+            gemm_tn = None
+        run = sharded.HostShardedGemm(FakeCtx(), M, n1 - n0, K, dtype=torch.float32, out_dtype=torch.float32,
+                                      device="cpu", gemm=cpu_gemm, max_blocks=4)
+        # a rank only reads ITS slices of A from the host: poison the rest of its copy
+        mineA = torch.full_like(A, float("nan"))
+        for r0, r1, per in run.blocks:
+            lo, hi = r0 + rank * per, min(r1, r0 + (rank + 1) * per)
+            if hi > lo:
+                mineA[lo:hi] = A[lo:hi]
+        Cn = torch.empty((M, n1 - n0), dtype=torch.float32)
+        run(mineA, B[n0:n1].contiguous(), Cn, alpha=0.5)
+        want = torch.from_numpy((0.5 * oracle.ref_gemm_tn(A.numpy(), B[n0:n1].contiguous().numpy())).astype(np.float32))
+        up, down = run.pcie_bytes()
+        rows_up = sum(max(0, min(r1, r0 + (rank + 1) * per) - (r0 + rank * per)) for r0, r1, per in run.blocks)
+        q.put((rank, bool(torch.equal(Cn, want)) and up == (rows_up * K + (n1 - n0) * K) * 4
+               and down == M * (n1 - n0) * 4, len(run.blocks)))
+    except Exception as exc:
+        q.put((rank, False, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("shape", [(4096, 64, 32), (4100, 40, 24), (10, 16, 8)])
+def test_host_sharded_pipeline_two_gloo_ranks(shape):
+    """The multi-GPU host-buffer call's orchestration on two CPU ranks: every rank uploads only
+    its slices of A (the rest of its host copy is poisoned with NaN), the all-gather completes
+    each row block, and each rank's column shard of C equals the oracle's."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_host_worker, args=(r, world, port, shape, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok is True for _, ok, _ in results), results

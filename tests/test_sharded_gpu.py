@@ -53,8 +53,25 @@ def _worker(rank, world, port, q):
         fused_ok = bool(torch.equal(shared.local, single))
         dist.barrier()
         shared.close()
+        # the host-buffer form over several GPUs: A crosses PCIe once per node (each rank uploads
+        # only its slices; the rest of its host copy is poisoned), NVLink all-gather completes it
+        M2 = 4100
+        A2, _ = inputs.make_operands("llm", M2, 1, K, seed=43)
+        run = sharded.HostShardedGemm(ctx, M2, n1 - n0, K, max_blocks=4)
+        mine = torch.full((M2, K), float("nan"), dtype=torch.bfloat16).pin_memory()
+        for r0, r1, per in run.blocks:
+            lo, hi = r0 + rank * per, min(r1, r0 + (rank + 1) * per)
+            if hi > lo:
+                mine[lo:hi] = A2[lo:hi]
+        hB = B[n0:n1].contiguous().pin_memory()
+        hC = torch.empty((M2, n1 - n0), dtype=torch.bfloat16).pin_memory()
+        for _ in range(2):
+            run(mine, hB, hC)
+            ctx.status()
+        host_ok = bool(torch.equal(hC.cuda(), ctx.gemm_tn(A2.cuda(), dB[n0:n1])))
+        ctx.status()
         ok = (bool(torch.equal(full, single)) and bool(torch.equal(wide[:, n0:n1], single[:, n0:n1]))
-              and fused_ok)
+              and fused_ok and host_ok)
         untouched = bool((wide[:, :n0] == 0).all()) and bool((wide[:, n1:] == 0).all())
         q.put((rank, ok and untouched, tuple(full.shape)))
         dist.destroy_process_group()

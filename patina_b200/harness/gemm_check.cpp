@@ -15,14 +15,23 @@
 //
 //     gemm_check --m M --n N --k K [--dtype bf16|fp8|f16] [--cta 1|2] [--block-n 128|256]
 //                [--dist uniform|normal01|llm] [--seed S] [--alpha X] [--iters I]
-//                [--check-rows R]
+//                [--check-rows R] [--splitk MODE] [--gpus G] [--allgather]
 //
-// and adds time_us / tflops / pct_peak lines. Verification is this program's
-// job, as in the reference: it carries its own CPU reference loop.
+// and adds time_us / tflops / pct_peak lines. --splitk forces (1, 2, 3) or forbids (-1) the
+// skinny stream-K path (PatinaGemmConfig::stream_k). --gpus G splits the N columns of a bf16
+// problem over G GPUs of this node, one host thread and one library context per GPU, A
+// replicated, no communication during the GEMM; with --allgather every GPU's epilogue stores
+// its column block into every GPU's full-width C over NVLink (patina_gemm_bf16_tn_scatter:
+// peer stores, nothing loaded from a peer, nothing multicast), and every GPU's copy of the
+// whole C is verified. The reference harness is single-GPU (harness/gemm_check.cpp:222).
+// Verification is this program's job, as in the reference: it carries its own CPU reference loop.
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
+#include <condition_variable>
+#include <mutex>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -151,7 +160,8 @@ void reference_rows(const std::vector<float>& A, const std::vector<float>& B, in
 struct Options {
   int64_t m = 128, n = 128, k = 128;
   std::string dtype = "f16", dist = "closed_form";
-  int cta = 0, block_n = 0, iters = 0;
+  int cta = 0, block_n = 0, iters = 0, splitk = 0, gpus = 1;
+  bool allgather = false;
   int64_t check_rows = 0;
   uint64_t seed = 0x5EED;
   float alpha = 1.0f;
@@ -159,12 +169,220 @@ struct Options {
   std::string kernel_name = "patina_gemm";
 };
 
+// ---- several GPUs: N-column shards, one host thread per GPU ---------------------------------
+// Shards are contiguous, in whole 256-column tiles while columns last (the same split the
+// Python side uses), so every listed projection width divides evenly over 2, 4 and 8 GPUs.
+void column_shard(int64_t n, int world, int rank, int64_t* n0, int64_t* n1) {
+  const int64_t blocks = (n + 255) / 256, per = (blocks + world - 1) / world;
+  *n0 = std::min<int64_t>(n, (int64_t)rank * per * 256);
+  *n1 = std::min<int64_t>(n, (int64_t)(rank + 1) * per * 256);
+}
+
+// A reusable barrier for the per-GPU host threads.
+struct HostBarrier {
+  std::mutex mu;
+  std::condition_variable cv;
+  int count, waiting = 0;
+  uint64_t generation = 0;
+  explicit HostBarrier(int n) : count(n) {}
+  void wait() {
+    std::unique_lock<std::mutex> lk(mu);
+    const uint64_t gen = generation;
+    if (++waiting == count) {
+      waiting = 0;
+      ++generation;
+      cv.notify_all();
+    } else {
+      cv.wait(lk, [&] { return generation != gen; });
+    }
+  }
+};
+
+int run_sharded(const Options& o) {
+  const int G = o.gpus;
+  const int64_t M = o.m, N = o.n, K = o.k;
+  const int64_t ldk = (K + 7) / 8 * 8, ldn = (N + 7) / 8 * 8;
+  std::vector<float> Af((size_t)M * K), Bf((size_t)N * K);
+  std::vector<uint16_t> Ab((size_t)M * ldk, 0), Bb((size_t)N * ldk, 0);
+  for (size_t i = 0; i < Af.size(); ++i) Af[i] = draw(o.dist, false, o.seed, i);
+  for (size_t i = 0; i < Bf.size(); ++i) Bf[i] = draw(o.dist, true, o.seed, i);
+  for (int64_t r = 0; r < M; ++r)
+    for (int64_t k = 0; k < K; ++k) {
+      const uint16_t q = to_bf16(Af[(size_t)r * K + k]);
+      Ab[(size_t)r * ldk + k] = q;
+      Af[(size_t)r * K + k] = from_bf16(q);
+    }
+  for (int64_t r = 0; r < N; ++r)
+    for (int64_t k = 0; k < K; ++k) {
+      const uint16_t q = to_bf16(Bf[(size_t)r * K + k]);
+      Bb[(size_t)r * ldk + k] = q;
+      Bf[(size_t)r * K + k] = from_bf16(q);
+    }
+  std::vector<int64_t> rows;
+  int64_t want_rows = o.check_rows > 0 ? o.check_rows : ((double)M * N * K <= 9e9 ? M : 64);
+  want_rows = std::min(want_rows, M);
+  for (int64_t i = 0; i < want_rows; ++i)
+    rows.push_back(want_rows == M ? i : (i * (M - 1)) / std::max<int64_t>(1, want_rows - 1));
+  std::vector<double> Cref(rows.size() * (size_t)N);
+  reference_rows(Af, Bf, N, K, rows, Cref);
+
+  struct Dev {
+    PatinaGemmContext* ctx = nullptr;
+    void *dA = nullptr, *dB = nullptr, *dC = nullptr;   // dC: the shard [M, ldn_shard], or with
+    int64_t n0 = 0, n1 = 0, ldc = 0;                    // --allgather the whole C [M, ldn]
+    std::vector<uint16_t> C;
+    double device_us = 0, wall_us = 0;
+    std::string error;
+  };
+  std::vector<Dev> dev(G);
+  HostBarrier bar(G);
+  std::chrono::steady_clock::time_point t_start;
+  std::mutex start_mu;
+  auto worker = [&](int g) {
+    Dev& d = dev[g];
+    auto fail = [&](const std::string& what) { if (d.error.empty()) d.error = what; };
+    auto rt = [&](cudaError_t e, const char* what) {
+      if (e != cudaSuccess) fail(std::string(what) + ": " + cudaGetErrorString(e));
+      return e == cudaSuccess;
+    };
+    column_shard(N, G, g, &d.n0, &d.n1);
+    const int64_t nw = d.n1 - d.n0;
+    d.ldc = o.allgather ? ldn : (nw + 7) / 8 * 8;
+    bool ok = rt(cudaSetDevice(g), "cudaSetDevice");
+    if (ok && patina_gemm_context_create(g, &d.ctx) != PATINA_GEMM_OK) { fail("patina_gemm_context_create"); ok = false; }
+    if (ok && o.allgather)
+      for (int p = 0; p < G; ++p)
+        if (p != g) {
+          const cudaError_t e = cudaDeviceEnablePeerAccess(p, 0);
+          if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) fail("cudaDeviceEnablePeerAccess");
+          cudaGetLastError();
+        }
+    const size_t c_bytes = (size_t)M * std::max<int64_t>(d.ldc, 8) * 2;
+    ok = ok && rt(cudaMalloc(&d.dA, Ab.size() * 2), "cudaMalloc(A)") &&
+         rt(cudaMalloc(&d.dB, std::max<size_t>((size_t)nw * ldk * 2, 16)), "cudaMalloc(B)") &&
+         rt(cudaMalloc(&d.dC, c_bytes), "cudaMalloc(C)") && rt(cudaMemset(d.dC, 0, c_bytes), "cudaMemset(C)") &&
+         rt(cudaMemcpy(d.dA, Ab.data(), Ab.size() * 2, cudaMemcpyHostToDevice), "cudaMemcpy(A)");
+    if (ok && nw > 0)
+      ok = rt(cudaMemcpy(d.dB, &Bb[(size_t)d.n0 * ldk], (size_t)nw * ldk * 2, cudaMemcpyHostToDevice), "cudaMemcpy(B)");
+    if (!ok) fail("set-up");
+    bar.wait();                                   // every GPU's buffers exist from here on
+    // destinations of this GPU's column block: its own C first, then (--allgather) every peer's
+    std::vector<void*> dests;
+    if (o.allgather) {
+      dests.push_back(static_cast<char*>(d.dC) + 2 * d.n0);
+      for (int p = 0; p < G; ++p)
+        if (p != g) dests.push_back(static_cast<char*>(dev[p].dC) + 2 * d.n0);
+    }
+    auto launch = [&]() -> int {
+      if (nw == 0 || !d.error.empty()) return PATINA_GEMM_OK;
+      if (o.allgather)
+        return patina_gemm_bf16_tn_scatter(d.ctx, d.dA, ldk, d.dB, ldk, dests.data(), (int)dests.size(), d.ldc, M, nw,
+                                           K, o.alpha, nullptr);
+      return patina_gemm_bf16_tn(d.ctx, d.dA, ldk, d.dB, ldk, d.dC, d.ldc, M, nw, K, o.alpha, nullptr);
+    };
+    auto run_checked = [&](const char* what) {
+      int rc = launch();
+      if (rc == PATINA_GEMM_OK && d.ctx) rc = patina_gemm_status(d.ctx, nullptr);
+      if (rc != PATINA_GEMM_OK) {
+        char* msg = d.ctx ? patina_gemm_last_error(d.ctx) : nullptr;
+        fail(std::string(what) + ": " + (msg ? msg : "?"));
+        patina_gemm_string_free(msg);
+      }
+    };
+    run_checked("first launch");
+    bar.wait();                                   // every block of every C has been written
+    if (d.error.empty()) {
+      d.C.resize((size_t)M * d.ldc);
+      rt(cudaMemcpy(d.C.data(), d.dC, d.C.size() * 2, cudaMemcpyDeviceToHost), "cudaMemcpy(C)");
+    }
+    if (o.iters > 0) {
+      cudaEvent_t e0 = nullptr, e1 = nullptr;
+      cudaEventCreate(&e0);
+      cudaEventCreate(&e1);
+      for (int i = 0; i < 3; ++i) run_checked("warm-up");
+      double best_dev = 1e30, best_wall = 1e30;
+      for (int i = 0; i < o.iters; ++i) {
+        bar.wait();
+        if (g == 0) { std::lock_guard<std::mutex> lk(start_mu); t_start = std::chrono::steady_clock::now(); }
+        bar.wait();                               // common host time stamp taken
+        cudaEventRecord(e0, nullptr);
+        launch();
+        cudaEventRecord(e1, nullptr);
+        cudaEventSynchronize(e1);
+        const auto t1 = std::chrono::steady_clock::now();
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        best_dev = std::min(best_dev, (double)ms * 1e3);
+        best_wall = std::min(best_wall, std::chrono::duration<double, std::micro>(t1 - t_start).count());
+      }
+      run_checked("timed launches");
+      d.device_us = best_dev;
+      d.wall_us = best_wall;
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+    }
+    bar.wait();                                   // nobody still writes into anybody's C
+    cudaFree(d.dA);
+    cudaFree(d.dB);
+    cudaFree(d.dC);
+    if (d.ctx) patina_gemm_context_destroy(d.ctx);
+  };
+  std::vector<std::thread> pool;
+  for (int g = 0; g < G; ++g) pool.emplace_back(worker, g);
+  for (auto& t : pool) t.join();
+  for (int g = 0; g < G; ++g)
+    if (!dev[g].error.empty()) {
+      std::fprintf(stderr, "GPU %d: %s\n", g, dev[g].error.c_str());
+      return kExitError;
+    }
+
+  // every GPU's result against the CPU reference: its shard, or with --allgather the whole C
+  double max_abs = 0, max_ref = 0, se = 0, sr = 0, sum = 0;
+  uint64_t checked = 0;
+  for (int g = 0; g < G; ++g) {
+    const Dev& d = dev[g];
+    const int64_t c0 = o.allgather ? 0 : d.n0, c1 = o.allgather ? N : d.n1;
+    for (size_t i = 0; i < rows.size(); ++i)
+      for (int64_t n = c0; n < c1; ++n) {
+        const double ref = from_bf16(to_bf16((float)((double)o.alpha * Cref[i * (size_t)N + n])));
+        const double got = from_bf16(d.C[(size_t)rows[i] * d.ldc + (o.allgather ? n : n - d.n0)]);
+        const double abs_err = std::fabs(got - ref);
+        if (g == 0 || !o.allgather) sum += got;
+        max_abs = std::max(max_abs, abs_err);
+        max_ref = std::max(max_ref, std::fabs(ref));
+        se += abs_err * abs_err;
+        sr += ref * ref;
+        ++checked;
+      }
+  }
+  const double fro = sr > 0 ? std::sqrt(se / sr) : 0.0;
+  const bool pass = max_abs <= 1e-2 * max_ref && fro <= 1e-3 && checked > 0;
+  std::printf("kernel: patina_gemm bf16  M=%lld N=%lld K=%lld  gpus=%d  shard_columns=%lld%s\n", (long long)M,
+              (long long)N, (long long)K, G, (long long)(dev[0].n1 - dev[0].n0),
+              o.allgather ? "  allgather=fused (peer stores)" : "");
+  std::printf("max abs err: %.6e   fro rel err: %.6e   max|ref|: %.6e\n", max_abs, fro, max_ref);
+  std::printf("elements checked: %llu (%zu rows on every GPU)\n", (unsigned long long)checked, rows.size());
+  std::printf("sum(C):      %.9e\n", sum);
+  if (o.iters > 0) {
+    double dev_us = 0, wall_us = 0;
+    for (const Dev& d : dev) { dev_us = std::max(dev_us, d.device_us); wall_us = std::max(wall_us, d.wall_us); }
+    const double tflops = 2.0 * M * N * K / (dev_us * 1e-6) / 1e12;
+    std::printf("time_us:     %.2f on the slowest GPU (CUDA events, best of %d); %.2f from a common host time stamp "
+                "to the last GPU's completion\n", dev_us, o.iters, wall_us);
+    std::printf("tflops:      %.1f aggregate   per_gpu: %.1f   pct_peak: %.1f (of 2250 nominal dense per GPU)\n", tflops,
+                tflops / G, 100.0 * tflops / G / 2250.0);
+  }
+  std::printf("%s\n", pass ? "PASS" : "FAIL");
+  return pass ? kExitPass : kExitFail;
+}
+
 int usage(const char* argv0) {
   std::fprintf(stderr,
                "usage: %s <ptx_file> <kernel_name> <K>\n"
                "  kernel_name: tcgen05_gemm_v1 (K=32) | tcgen05_gemm_v2 (K multiple of 32)\n"
                "   or: %s --m M --n N --k K [--dtype bf16|fp8|f16] [--cta 1|2] [--block-n 128|256]\n"
-               "          [--dist uniform|normal01|llm] [--seed S] [--alpha X] [--iters I] [--check-rows R]\n",
+               "          [--dist uniform|normal01|llm] [--seed S] [--alpha X] [--iters I] [--check-rows R]\n"
+               "          [--splitk -1|1|2|3] [--gpus G] [--allgather]\n",
                argv0, argv0);
   return kExitError;
 }
@@ -209,11 +427,19 @@ int main(int argc, char** argv) {
       else if (a == "--check-rows") o.check_rows = std::atoll(val());
       else if (a == "--seed") o.seed = std::strtoull(val(), nullptr, 0);
       else if (a == "--alpha") o.alpha = (float)std::atof(val());
+      else if (a == "--splitk") o.splitk = std::atoi(val());
+      else if (a == "--gpus") o.gpus = std::atoi(val());
+      else if (a == "--allgather") o.allgather = true;
       else return usage(argv[0]);
     }
     if (o.m <= 0 || o.n <= 0 || o.k <= 0) return usage(argv[0]);
     if (o.dtype != "bf16" && o.dtype != "fp8" && o.dtype != "f16") return usage(argv[0]);
     if (o.dist != "uniform" && o.dist != "normal01" && o.dist != "llm") return usage(argv[0]);
+    if (o.gpus < 1 || o.gpus > 8 || o.splitk < -1 || o.splitk > 3) return usage(argv[0]);
+    if ((o.gpus > 1 || o.allgather) && o.dtype != "bf16") {
+      std::fprintf(stderr, "--gpus / --allgather take bf16 problems\n");
+      return kExitError;
+    }
   }
 
   int ndev = 0;
@@ -224,6 +450,18 @@ int main(int argc, char** argv) {
   cudaDeviceProp prop;
   RT_CHECK(cudaGetDeviceProperties(&prop, 0));
   std::printf("device: %s (sm_%d%d)\n", prop.name, prop.major, prop.minor);
+  if (o.gpus > 1 || o.allgather) {
+    if (prop.major != 10) {
+      std::fprintf(stderr, "device is sm_%d%d, but tcgen05 needs sm_100a (Blackwell). This GPU cannot run it.\n",
+                   prop.major, prop.minor);
+      return kExitNotSm100;
+    }
+    if (o.gpus > ndev) {
+      std::fprintf(stderr, "--gpus %d, but only %d device(s) are visible\n", o.gpus, ndev);
+      return kExitError;
+    }
+    return run_sharded(o);
+  }
   PatinaGemmContext* ctx = nullptr;
   int rc = patina_gemm_context_create(0, &ctx);
   if (rc == PATINA_GEMM_ERR_UNSUPPORTED_ARCH) {
@@ -289,6 +527,7 @@ int main(int argc, char** argv) {
   PatinaGemmConfig cfg{};
   cfg.cta_group = o.cta;
   cfg.block_n = o.block_n;
+  cfg.stream_k = o.splitk;
   PatinaGemmPlan plan{};
   patina_gemm_plan(in_type, out_type, M, N, K, &cfg, prop.multiProcessorCount, &plan);
   auto launch = [&]() {

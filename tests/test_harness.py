@@ -53,3 +53,35 @@ def test_flag_form_bf16_and_fp8(harness):
     assert r.returncode == 0 and r.stdout.strip().endswith("PASS"), r.stdout + r.stderr
     r = run(harness, "--m", "256", "--n", "512", "--k", "512", "--dtype", "fp8", "--dist", "normal01", "--iters", "3")
     assert r.returncode == 0 and "tflops:" in r.stdout, r.stdout + r.stderr
+
+
+def test_sharded_flags_usage(harness):
+    assert run(harness, "--m", "128", "--gpus", "0").returncode == 2
+    assert run(harness, "--m", "128", "--gpus", "9").returncode == 2
+    assert run(harness, "--m", "128", "--splitk", "7").returncode == 2
+    r = run(harness, "--m", "128", "--n", "128", "--k", "128", "--dtype", "fp8", "--gpus", "2")
+    assert r.returncode == 2 and "bf16" in r.stderr
+
+
+@pytest.mark.gpu
+def test_splitk_flag_and_single_gpu_gather_form(harness):
+    """--splitk forces the skinny stream-K path; --allgather on one GPU runs the scatter entry
+    point with its single (own) destination and verifies the whole C."""
+    r = run(harness, "--m", "48", "--n", "2048", "--k", "4096", "--dist", "llm", "--splitk", "2", "--iters", "3")
+    assert r.returncode == 0 and r.stdout.strip().endswith("PASS"), r.stdout + r.stderr
+    r = run(harness, "--m", "1000", "--n", "776", "--k", "520", "--dist", "llm", "--gpus", "1", "--allgather",
+            "--iters", "2")
+    assert r.returncode == 0 and "allgather=fused" in r.stdout and r.stdout.strip().endswith("PASS"), r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_two_gpu_shards_and_fused_gather(harness):
+    """Two GPUs, one host thread each: column shards verified per GPU, then the fused gather
+    (every GPU stores its block into both full-width C buffers over NVLink) verified on both."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = run(harness, "--m", "1024", "--n", "1792", "--k", "512", "--dist", "llm", "--gpus", "2", "--iters", "3")
+    assert r.returncode == 0 and "gpus=2" in r.stdout and r.stdout.strip().endswith("PASS"), r.stdout + r.stderr
+    r = run(harness, "--m", "1024", "--n", "1792", "--k", "512", "--dist", "llm", "--gpus", "2", "--allgather")
+    assert r.returncode == 0 and r.stdout.strip().endswith("PASS"), r.stdout + r.stderr

@@ -208,7 +208,7 @@ int patina_gemm_fp8e4m3_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_
  * core's scale loads take (the "128x4 swizzled" layout other libraries use for MX scales).
  * patina_gemm_mx_scale_offset gives the byte offset of one scale. The buffer is padded to whole
  * atoms; padding bytes must be valid scales (anything but 0xFF), e.g. 127 (= 1.0). Scale buffers
- * are device pointers, 16-byte aligned. `config` may be NULL; block_n is 256, 224, 192 or 128. */
+ * are device pointers, 16-byte aligned. `config` may be NULL; block_n is 256, 192 or 128. */
 int patina_gemm_mxfp8_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* scales_a,
                          const void* B, int64_t ldb, const void* scales_b, void* C, int64_t ldc, int64_t M,
                          int64_t N, int64_t K, float alpha, const PatinaGemmConfig* config, void* stream);

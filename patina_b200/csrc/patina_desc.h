@@ -98,8 +98,8 @@ PATINA_HD constexpr uint64_t mx_scale_offset(uint64_t row, uint64_t k_block32, u
   return ((row / 128) * ((k + 127) / 128) + k_block32 / 4) * kSfAtomBytes + (row % 32) * 16 +
          ((row % 128) / 32) * 4 + (k_block32 % 4);
 }
-// Atoms of B's scales that a tile of width block_n (a multiple of 32) can touch: tiles start at
-// multiples of block_n, so at 0, 32, 64 or 96 rows into an atom.
+// Atoms of B's scales that a tile of width block_n (a multiple of 64) can touch: tiles start at
+// multiples of block_n, so at 0 or 64 rows into an atom.
 PATINA_HD constexpr uint32_t mx_sfb_atoms(uint32_t block_n) {
   uint32_t most = 0;
   for (uint32_t j = 0; j < 4; ++j) {

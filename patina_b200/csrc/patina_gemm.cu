@@ -127,9 +127,10 @@ constexpr int kNumGroupedKernels = sizeof(kGroupedKernels) / sizeof(kGroupedKern
 static_assert(GemmTraits<2, 2, 256, 4, kBF16, kOutBF16>::kSmemBytes + kGroupTableBytes <= kMaxDynSmem,
               "group tables do not fit behind the largest kernel's shared memory");
 
-// Block-scaled e4m3 (MXFP8) -> bf16. Widths are multiples of 32 (the scales of 32 rows of B
-// share a TMEM lane range). 256-wide accumulators leave no room in TMEM for a second buffer
-// next to the scale columns; 224 and 192 do.
+// Block-scaled e4m3 (MXFP8) -> bf16. Widths are multiples of 64: a tile's scales of B start a whole
+// number of 64 rows into a scale atom, i.e. an even number of TMEM columns (an odd column offset
+// faults with "misaligned address": measured with 224-wide tiles). 256-wide accumulators leave no
+// room in TMEM for a second buffer next to the scale columns; 192 does.
 using MxFn = void (*)(const CUtensorMap, const CUtensorMap, const CStoreMaps<1>, const CUtensorMap,
                       const CUtensorMap, const GemmParams);
 struct MxKernelEntry {
@@ -140,10 +141,9 @@ struct MxKernelEntry {
 #define PATINA_MX(G, MS, BN, S) \
   { G, MS, BN, S, gemm_mx_tn_kernel<G, MS, BN, S>, GemmTraits<G, MS, BN, S, kMXE4M3, kOutBF16>::kSmemBytes }
 const MxKernelEntry kMxKernels[] = {
-    PATINA_MX(2, 2, 192, 4),  // 512 x 192 per pair: accumulators + scales fill TMEM
-    PATINA_MX(2, 1, 224, 6),  // 256 x 224 per pair, double-buffered accumulators
+    PATINA_MX(2, 2, 192, 4),  // 512 x 192 per pair: one accumulator set + scales
+    PATINA_MX(2, 1, 192, 6),  // 256 x 192 per pair, double-buffered accumulators
     PATINA_MX(2, 1, 256, 5),  // 256 x 256 per pair, one accumulator
-    PATINA_MX(1, 1, 224, 4),  // 128 x 224, double-buffered
     PATINA_MX(1, 1, 192, 4),  // 128 x 192, double-buffered
     PATINA_MX(1, 1, 128, 5),  // 128 x 128, double-buffered: small problems
 };
@@ -388,6 +388,7 @@ struct PatinaGemmContext {
   size_t cap_a = 0, cap_b = 0, cap_c = 0;
 #ifdef PATINA_TRACE
   unsigned long long* trace = nullptr;  // trace builds only: [grid][32] time stamps of the next launch
+  uint32_t l2_hint_a = 0, l2_hint_b = 0;
 #endif
 };
 
@@ -740,6 +741,8 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   p.wait_limit_ns = ctx->wait_limit_ns;
 #ifdef PATINA_TRACE
   p.trace = ctx->trace;
+  p.l2_hint_a = ctx->l2_hint_a;
+  p.l2_hint_b = ctx->l2_hint_b;
 #endif
 
   cudaLaunchConfig_t lc{};
@@ -896,6 +899,7 @@ int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sf
   p.wait_limit_ns = ctx->wait_limit_ns;
 #ifdef PATINA_TRACE
   p.trace = nullptr;
+  p.l2_hint_a = p.l2_hint_b = 0;
 #endif
   uint32_t slots = (uint32_t)(ctx->num_sms / k->cta_group);
   if (k->cta_group > 1) {
@@ -1071,6 +1075,14 @@ extern "C" {
 int patina_gemm_debug_set_trace(PatinaGemmContext* ctx, void* buf) {
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   ctx->trace = static_cast<unsigned long long*>(buf);
+  return PATINA_GEMM_OK;
+}
+// Trace builds only: L2 eviction hints on the operand loads of pair kernels (0 none, 1 evict-first,
+// 2 evict-last), for measuring what they do to DRAM traffic.
+int patina_gemm_debug_set_l2_hints(PatinaGemmContext* ctx, uint32_t hint_a, uint32_t hint_b) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  ctx->l2_hint_a = hint_a;
+  ctx->l2_hint_b = hint_b;
   return PATINA_GEMM_OK;
 }
 #endif

@@ -85,6 +85,8 @@ struct GemmParams {
   uint64_t wait_limit_ns;  // bound for every barrier wait
 #ifdef PATINA_TRACE
   unsigned long long* trace;  // [grid][32]: time stamps of a trace build (never in the shipped library)
+  uint32_t l2_hint_a, l2_hint_b;  // trace builds: L2 eviction hint on operand loads of pair kernels
+                                  // (0 none, 1 evict-first, 2 evict-last)
 #endif
 };
 
@@ -224,7 +226,7 @@ struct GemmTraits {
   static constexpr bool kOverlapLastChunk = (BN % kChunkCols) != 0;
   static constexpr uint32_t kSmemBytes =
       smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut), kSfStageBytes).total_bytes;
-  static_assert(!kMx || BN % 32 == 0, "block-scaled tiles: the scales of 32 rows of B share a TMEM lane range");
+  static_assert(!kMx || BN % 64 == 0, "block-scaled tiles: B's scales must start an even number of TMEM columns into an atom");
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
   static_assert(kTmemUsed <= 512, "accumulators exceed the 512 TMEM columns");
@@ -461,12 +463,29 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
           const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
           if constexpr (kPair) {
             if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, 2u * stage_tx);
+#ifdef PATINA_TRACE
+            if (p.l2_hint_a | p.l2_hint_b) {
+              const uint64_t pol_first = ptx::l2_policy_evict_first(), pol_last = ptx::l2_policy_evict_last();
+              const uint64_t pa = p.l2_hint_a == 1 ? pol_first : pol_last, pb = p.l2_hint_b == 1 ? pol_first : pol_last;
+#pragma unroll
+              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
+                if (ms >= n_sub) continue;
+                const int32_t r = a_row + (int32_t)(ms * kCtaRows * kCtaGroup);
+                if (p.l2_hint_a) ptx::tma_load_2d_pair_hint(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0, r, pa);
+                else ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0, r);
+              }
+              if (p.l2_hint_b) ptx::tma_load_2d_pair_hint(sb, &tm_b, leader_full + 8u * s, k0, b_row, pb);
+              else ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
+            } else
+#endif
+            {
 #pragma unroll
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
               if (ms < n_sub)
                 ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
                                     a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
+            }
             if constexpr (kMx) {
               const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
 #pragma unroll
@@ -518,7 +537,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         const uint32_t n_sub = live_subtiles(c);
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
         // block scales in TMEM: A's slabs first, then B's atoms; the tile's first row of B may
-        // lie 32, 64 or 96 rows into its first atom, i.e. 1, 2 or 3 columns in
+        // lie 64 rows into its first atom, i.e. 2 columns in (widths are multiples of 64)
         const uint32_t tsfa0 = tmem_base + T::kSfCol0;
         const uint32_t tsfb0 = tsfa0 + 4u * (uint32_t)kMSub + ((c.n * BN) % kSfAtomRows) / 32u;
         ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);

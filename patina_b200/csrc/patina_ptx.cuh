@@ -164,6 +164,17 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
       : "memory");
 }
 
+// The pair form with an L2 eviction-priority hint.
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const void* tmap, uint32_t cluster_bar,
+                                                      int32_t c0, int32_t c1, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(cluster_bar), "r"(c0), "r"(c1), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int32_t c0,
                                              int32_t c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

@@ -389,6 +389,8 @@ struct PatinaGemmContext {
 #ifdef PATINA_TRACE
   unsigned long long* trace = nullptr;  // trace builds only: [grid][32] time stamps of the next launch
   uint32_t l2_hint_a = 0, l2_hint_b = 0;
+  PatinaGemmConfig scatter_cfg{};       // trace builds only: tile override for the scatter entry
+  bool has_scatter_cfg = false;
 #endif
 };
 
@@ -1077,6 +1079,14 @@ int patina_gemm_debug_set_trace(PatinaGemmContext* ctx, void* buf) {
   ctx->trace = static_cast<unsigned long long*>(buf);
   return PATINA_GEMM_OK;
 }
+// Trace builds only: a tile configuration for the scatter entry point (null: the library's choice),
+// for comparing store-box shapes over NVLink.
+int patina_gemm_debug_set_scatter_config(PatinaGemmContext* ctx, const PatinaGemmConfig* cfg) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  ctx->has_scatter_cfg = cfg != nullptr;
+  if (cfg) ctx->scatter_cfg = *cfg;
+  return PATINA_GEMM_OK;
+}
 // Trace builds only: L2 eviction hints on the operand loads of pair kernels (0 none, 1 evict-first,
 // 2 evict-last), for measuring what they do to DRAM traffic.
 int patina_gemm_debug_set_l2_hints(PatinaGemmContext* ctx, uint32_t hint_a, uint32_t hint_b) {
@@ -1277,7 +1287,11 @@ int patina_gemm_bf16_tn_scatter(PatinaGemmContext* ctx, const void* A, int64_t l
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   if (!C_dests || n_dests < 1 || n_dests > kMaxDests)
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "n_dests must be 1..8 and C_dests non-null");
-  return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C_dests[0], ldc, M, N, K, alpha, nullptr,
+  const PatinaGemmConfig* cfg = nullptr;
+#ifdef PATINA_TRACE
+  if (ctx->has_scatter_cfg) cfg = &ctx->scatter_cfg;
+#endif
+  return launch_gemm(ctx, kBF16, kOutBF16, A, lda, B, ldb, C_dests[0], ldc, M, N, K, alpha, cfg,
                      static_cast<cudaStream_t>(stream), C_dests + 1, n_dests - 1);
 }
 

@@ -138,6 +138,11 @@ extern "C" {
         i64, k: i64, alpha: f32, config: *const PatinaGemmConfig, stream: *mut c_void) -> i32;
     pub fn patina_gemm_mx_scale_bytes(rows: i64, k: i64) -> u64;
     pub fn patina_gemm_mx_scale_offset(row: i64, k_block32: i64, k: i64) -> u64;
+    pub fn patina_gemm_column_shard(n: i64, world: i32, rank: i32, n0: *mut i64, n1: *mut i64);
+    pub fn patina_gemm_sharded_bf16_tn(ctxs: *const *mut PatinaGemmContext, n_shards: i32,
+        a: *const *const c_void, lda: i64, b_shards: *const *const c_void, ldb: i64,
+        c_shards: *const *mut c_void, ldc: i64, m: i64, n: i64, k: i64, alpha: f32,
+        streams: *const *mut c_void) -> i32;
     pub fn patina_gemm_peer_alloc(ctx: *mut PatinaGemmContext, bytes: usize, ptr: *mut *mut c_void,
         handle_out: *mut u8) -> i32;
     pub fn patina_gemm_peer_open(ctx: *mut PatinaGemmContext, handle: *const u8, ptr: *mut *mut c_void) ->
@@ -369,6 +374,13 @@ impl Drop for Gemm {
     fn drop(&mut self) {
         unsafe { patina_gemm_context_destroy(self.raw) }
     }
+}
+
+/// Shard `rank` of `world`: its columns [n0, n1) of an N-wide problem.
+pub fn column_shard(n: i64, world: i32, rank: i32) -> (i64, i64) {
+    let (mut n0, mut n1) = (0i64, 0i64);
+    unsafe { patina_gemm_column_shard(n, world, rank, &mut n0, &mut n1) };
+    (n0, n1)
 }
 
 /// The skinny GEMM (1 <= M <= 128) that allocates nothing: no context, fixed scratch inside the

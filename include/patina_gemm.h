@@ -215,6 +215,22 @@ int patina_gemm_mxfp8_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, con
 uint64_t patina_gemm_mx_scale_bytes(int64_t rows, int64_t K);
 uint64_t patina_gemm_mx_scale_offset(int64_t row, int64_t k_block32, int64_t K);
 
+/* N-column sharding over several GPUs (no counterpart in the reference, which uses device 0 only,
+ * harness/gemm_check.cpp:222). patina_gemm_column_shard gives shard `rank` of `world` its columns
+ * [*n0, *n1) of an N-wide problem: contiguous, in whole 256-column tiles while columns last
+ * (trailing shards may be narrower or empty). patina_gemm_sharded_bf16_tn enqueues the whole
+ * sharded bf16 GEMM from one host thread: for every shard g one launch on ctxs[g]'s device and
+ * streams[g] (NULL array or entry: that device's default stream) computing
+ *     C_shards[g][M, n1-n0] = alpha * A[g][M, K] * B_shards[g][n1-n0, K]^T
+ * where A[g] is shard g's copy of the replicated A, B_shards[g] the rows [n0, n1) of B and
+ * C_shards[g] the address of shard g's first column (its own buffer, or column n0 of a full-width
+ * C with ldc = N). No GPU waits for another; call patina_gemm_status per context afterwards.
+ * Two shards may share a device (two contexts, two streams). n_shards is 1..8. */
+void patina_gemm_column_shard(int64_t n, int world, int rank, int64_t* n0, int64_t* n1);
+int patina_gemm_sharded_bf16_tn(PatinaGemmContext* const* ctxs, int n_shards, const void* const* A, int64_t lda,
+                                const void* const* B_shards, int64_t ldb, void* const* C_shards, int64_t ldc,
+                                int64_t M, int64_t N, int64_t K, float alpha, void* const* streams);
+
 /* Buffers for the scatter above (no counterpart in the reference). peer_alloc gives device
  * memory of this context's GPU plus a 64-byte handle that another PROCESS on the node passes
  * to peer_open (with its own context) to get a pointer its GPU can write through NVLink.

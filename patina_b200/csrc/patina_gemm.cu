@@ -1312,6 +1312,36 @@ int patina_gemm_fp8e4m3_tn_grouped(PatinaGemmContext* ctx, const void* A, int64_
                         scale_a, group_scale_b, config, static_cast<cudaStream_t>(stream));
 }
 
+void patina_gemm_column_shard(int64_t n, int world, int rank, int64_t* n0, int64_t* n1) {
+  int64_t a = 0, b = 0;
+  if (n > 0 && world > 0 && rank >= 0 && rank < world) {
+    const int64_t blocks = (n + 255) / 256, per = (blocks + world - 1) / world;
+    a = (int64_t)rank * per * 256 < n ? (int64_t)rank * per * 256 : n;
+    b = (int64_t)(rank + 1) * per * 256 < n ? (int64_t)(rank + 1) * per * 256 : n;
+  }
+  if (n0) *n0 = a;
+  if (n1) *n1 = b;
+}
+
+int patina_gemm_sharded_bf16_tn(PatinaGemmContext* const* ctxs, int n_shards, const void* const* A, int64_t lda,
+                                const void* const* B_shards, int64_t ldb, void* const* C_shards, int64_t ldc,
+                                int64_t M, int64_t N, int64_t K, float alpha, void* const* streams) {
+  if (!ctxs || !A || !B_shards || !C_shards || n_shards < 1 || n_shards > kMaxDests) return PATINA_GEMM_ERR_INVALID_ARG;
+  for (int g = 0; g < n_shards; ++g)
+    if (!ctxs[g]) return PATINA_GEMM_ERR_INVALID_ARG;
+  // One launch per shard, each on its own context's device and stream; nothing waits here, so
+  // the shards run concurrently when the contexts are on different GPUs (or streams).
+  for (int g = 0; g < n_shards; ++g) {
+    int64_t n0, n1;
+    patina_gemm_column_shard(N, n_shards, g, &n0, &n1);
+    if (n1 == n0) continue;
+    const int rc = launch_gemm(ctxs[g], kBF16, kOutBF16, A[g], lda, B_shards[g], ldb, C_shards[g], ldc, M, n1 - n0,
+                               K, alpha, nullptr, static_cast<cudaStream_t>(streams ? streams[g] : nullptr));
+    if (rc != PATINA_GEMM_OK) return rc;
+  }
+  return PATINA_GEMM_OK;
+}
+
 int patina_gemm_mxfp8_tn(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* scales_a,
                          const void* B, int64_t ldb, const void* scales_b, void* C, int64_t ldc, int64_t M,
                          int64_t N, int64_t K, float alpha, const PatinaGemmConfig* config, void* stream) {

@@ -24,6 +24,7 @@ SYMBOLS = (
     "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_chosen", "patina_gemm_streamk_range",
     "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped", "patina_gemm_fp8e4m3_tn_grouped",
     "patina_gemm_mxfp8_tn", "patina_gemm_mx_scale_bytes", "patina_gemm_mx_scale_offset", "patina_gemm_idesc_mx",
+    "patina_gemm_column_shard", "patina_gemm_sharded_bf16_tn",
     "patina_gemm_peer_alloc",
     "patina_gemm_peer_open", "patina_gemm_peer_close", "patina_gemm_peer_free",
 )
@@ -131,6 +132,10 @@ def load() -> C.CDLL:
     L.patina_gemm_mx_scale_offset.restype = C.c_uint64
     L.patina_gemm_idesc_mx.argtypes = [C.c_uint32] * 4
     L.patina_gemm_idesc_mx.restype = C.c_uint32
+    L.patina_gemm_column_shard.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
+    L.patina_gemm_column_shard.restype = None
+    L.patina_gemm_sharded_bf16_tn.argtypes = [C.POINTER(vp), i32, C.POINTER(vp), i64, C.POINTER(vp), i64,
+                                              C.POINTER(vp), i64, i64, i64, i64, f32, C.POINTER(vp)]
     L.patina_gemm_bf16_tn_skinny_noalloc.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64, f32, vp,
                                                      C.c_char_p, C.c_size_t]
     _lib = L

@@ -505,6 +505,44 @@ def test_scatter_to_several_destinations_on_one_gpu(ctx, oracle_mod):
         ctx.gemm_bf16_tn_scatter(dA, dB, [ptrs[0], ptrs[1] + 2], ldc)   # misaligned destination
 
 
+def test_sharded_entry_point_on_one_gpu(oracle_mod):
+    """patina_gemm_sharded_bf16_tn with several shards that all live on this GPU (one context and
+    one stream per shard, as on a multi-GPU node one per GPU): each shard writes its column block
+    of one full-width C through the leading dimension, and the result equals the unsharded call
+    bit for bit, for shard counts that split the width evenly and unevenly."""
+    import ctypes as C
+    import patina_b200
+    from patina_b200 import inputs, sharded, lib as L
+    lib = L.load()
+    M, N, K = 1000, 1800, 520
+    A, B = inputs.make_operands("llm", M, N, K, seed=12)
+    dA, dB = A.cuda(), B.cuda()
+    ctxs = [patina_b200.GemmContext(0) for _ in range(4)]
+    single = ctxs[0].gemm_tn(dA, dB)
+    ctxs[0].status()
+    for world in (1, 2, 3, 4):
+        full = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        streams = [torch.cuda.Stream() for _ in range(world)]
+        for st in streams:
+            st.wait_stream(torch.cuda.current_stream())
+        spans = [sharded.column_shard(N, world, r) for r in range(world)]
+        vp = C.c_void_p
+        arr = lambda vals: (vp * world)(*vals)
+        rc = lib.patina_gemm_sharded_bf16_tn(
+            arr([c._h.value for c in ctxs[:world]]), world, arr([dA.data_ptr()] * world), dA.stride(0),
+            arr([dB.data_ptr() + 2 * K * n0 for n0, _ in spans]), dB.stride(0),
+            arr([full.data_ptr() + 2 * n0 for n0, _ in spans]), full.stride(0), M, N, K, 1.0,
+            arr([st.cuda_stream for st in streams]))
+        assert rc == L.OK
+        for c, st in zip(ctxs, streams):
+            with torch.cuda.stream(st):
+                c.status()
+        assert torch.equal(full, single), f"{world} shards"
+    check_norm(oracle_mod, single, expect_bf16(oracle_mod, A, B), "sharded reference")
+    for c in ctxs:
+        c.close()
+
+
 # ------------------------------------------------------- full benchmark sizes
 def test_bf16_8192_cubed_samples_and_properties(ctx, oracle_mod):
     """8192^3 (the benchmark size): 64 sampled rows against the oracle, plus

@@ -143,3 +143,12 @@ def test_host_sharded_pipeline_two_gloo_ranks(shape):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert all(ok is True for _, ok, _ in results), results
+
+
+def test_c_shard_arithmetic_matches_python(built_lib):
+    import ctypes as C
+    for n, world in [(8192, 8), (4096, 8), (14336, 8), (28672, 4), (1000, 3), (100, 8), (0, 2), (16384, 8)]:
+        for r in range(world):
+            a, b = C.c_int64(), C.c_int64()
+            built_lib.patina_gemm_column_shard(n, world, r, C.byref(a), C.byref(b))
+            assert (a.value, b.value) == sharded.column_shard(n, world, r), (n, world, r)

@@ -47,6 +47,7 @@ pub struct PatinaGemmConfig {
     pub max_ctas: i32,
     pub m_sub: i32,
     pub stream_k: i32,
+    pub cluster_k: i32,
 }
 
 #[repr(C)]
@@ -164,6 +165,7 @@ extern "C" {
     pub fn patina_gemm_streamk_range(cta: u64, units: u64, parts: u64, begin: *mut u64, end: *mut u64);
     pub fn patina_gemm_streamk_chosen(in_type: i32, out_type: i32, m: i64, n: i64, k: i64, num_sms: i32) ->
         i32;
+    pub fn patina_gemm_cluster_k_chosen(in_type: i32, out_type: i32, m: i64, n: i64, k: i64, num_sms: i32) -> i32;
     pub fn patina_gemm_streamk_owner(unit: u64, units: u64, parts: u64) -> u32;
     pub fn patina_gemm_smem_desc(smem_addr: u32, lbo_bytes: u32, sbo_bytes: u32, swizzle_code: i32) -> u64;
     pub fn patina_gemm_idesc(in_type: i32, umma_m: u32, umma_n: u32) -> u32;
@@ -178,7 +180,8 @@ extern "C" {
 impl Default for PatinaGemmConfig {
     /// All zero: "choose for me" in every field.
     fn default() -> Self {
-        PatinaGemmConfig { cta_group: 0, block_n: 0, stages: 0, group_m: 0, max_ctas: 0, m_sub: 0, stream_k: 0 }
+        PatinaGemmConfig { cta_group: 0, block_n: 0, stages: 0, group_m: 0, max_ctas: 0, m_sub: 0, stream_k: 0,
+                           cluster_k: 0 }
     }
 }
 

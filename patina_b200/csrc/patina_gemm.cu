@@ -19,6 +19,7 @@
 
 #include "patina_desc.h"
 #include "patina_gemm_kernel.cuh"
+#include "patina_gemm_splitk.cuh"
 #include "patina_gemm_streamk.cuh"
 
 using namespace patina;
@@ -242,6 +243,11 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (k.cta_group == 2 && num_sms < 2) continue;
       if (need_fused && !k.fn_fused) continue;
       if (need_scatter && !k.fn_scatter) continue;
+      // Peer destinations: store boxes with 128-byte rows (four-warp epilogues) cross NVLink at 0.84
+      // of the plain copy rate, the 64-byte rows of the eight-warp epilogue at 0.55 (measured on
+      // two GPUs: 621 vs 408 GB/s out of each GPU, copy 744), and at eight GPUs the gather is
+      // what bounds the call.
+      if (need_scatter && k.m_sub != 1) continue;
       const double s = config_score(k, M, N, K, num_sms);
       if (s > best_score) {
         best_score = s;
@@ -375,6 +381,7 @@ struct PatinaGemmContext {
   uint32_t* d_sk_counters = nullptr;
   size_t cap_sk_partials = 0, cap_sk_counters = 0;
   bool sk_attr_set[2] = {false, false};
+  bool ck_attr_set[3] = {false, false, false};   // cluster split-K kernels (2, 4, 8 CTAs)
   bool mx_attr_set[kNumMxKernels] = {};
   int mx_max_clusters[kNumMxKernels] = {};
   uint32_t sk_burst = 4;
@@ -611,6 +618,97 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   return PATINA_GEMM_OK;
 }
 
+// ------------------------------------------------ K cut across a cluster (few tiles, deep K)
+// One cluster of S CTAs per 128 x 256 tile, each CTA taking 1/S of the k-blocks; the partial tiles
+// are summed through distributed shared memory (patina_gemm_splitk.cuh). Measured facts behind
+// the choice: a 128-byte k-block costs a CTA about 525 cycles whatever the tile width, so a
+// problem with few tiles only gets faster by giving each CTA fewer k-blocks; the exchange and its
+// two cluster barriers cost about as much as kClusterKMinSaved k-blocks.
+constexpr uint32_t kClusterKMinSaved = 8;
+
+bool cluster_k_supported(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int split) {
+  if (in_type != kBF16 || out_type != kOutBF16) return false;
+  if (split != 2 && split != 4 && split != 8) return false;
+  if (M < 1 || N < 1 || (N % 8) != 0) return false;               // whole 16-byte pieces in every store box
+  return (int64_t)ceil_div(K, kBlockKBytes / 2) >= split;          // every CTA gets at least one k-block
+}
+
+// 0: do not split; else the cluster size.
+int cluster_k_choice(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
+  if (M <= 128) return 0;                                          // the skinny paths cover these
+  const uint64_t tiles = (uint64_t)ceil_div(M, kCtaRows) * ceil_div(N, kSplitBN);
+  const uint32_t kb = ceil_div(K, kBlockKBytes / 2);
+  for (int split = 8; split >= 2; split /= 2) {
+    if (!cluster_k_supported(in_type, out_type, M, N, K, split)) continue;
+    if (tiles * (uint64_t)split > (uint64_t)num_sms) continue;     // one wave of clusters
+    const uint32_t saved = kb - kb / (uint32_t)split;              // k-blocks every CTA no longer runs
+    if (saved >= kClusterKMinSaved && kb / (uint32_t)split >= 2u) return split;
+  }
+  return 0;
+}
+
+int launch_cluster_k(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* B, int64_t ldb, void* C,
+                     int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, int split, int group_m,
+                     cudaStream_t stream) {
+  CUtensorMap tm_a, tm_b, tm_c;
+  const uint32_t kelems = kBlockKBytes / 2;
+  int rc = get_tensor_map(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
+                          kCtaRows, kelems, &tm_a);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, kSplitBN,
+                      kelems, &tm_b);
+  if (rc != PATINA_GEMM_OK) return rc;
+  rc = get_tensor_map(ctx, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldc,
+                      kStoreBoxRows, 32, &tm_c);
+  if (rc != PATINA_GEMM_OK) return rc;
+  using Fn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+  const Fn fn = split == 2 ? gemm_splitk_cluster_kernel<2> : split == 4 ? gemm_splitk_cluster_kernel<4>
+                                                                        : gemm_splitk_cluster_kernel<8>;
+  const int fi = split == 2 ? 0 : split == 4 ? 1 : 2;
+  if (!ctx->ck_attr_set[fi]) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)splitk_smem_bytes());
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(smem, cluster split-K)");
+    ctx->ck_attr_set[fi] = true;
+  }
+  GemmParams p{};
+  p.M = (uint32_t)M;
+  p.N = (uint32_t)N;
+  p.K = (uint32_t)K;
+  p.tiles_m = ceil_div(M, kCtaRows);
+  p.tiles_n = ceil_div(N, kSplitBN);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.k_blocks = ceil_div(K, kelems);
+  p.group_m = group_m > 0 ? (uint32_t)group_m : 8u;
+  p.alpha = alpha;
+  p.n_dests = 1;
+  p.c_dests[0] = C;
+  p.ldc = ldc;
+  p.status = ctx->d_status;
+  p.wait_limit_ns = ctx->wait_limit_ns;
+#ifdef PATINA_TRACE
+  p.trace = nullptr;
+  p.l2_hint_a = p.l2_hint_b = 0;
+#endif
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(p.num_tiles * (uint32_t)split, 1, 1);
+  lc.blockDim = dim3(192, 1, 1);
+  lc.dynamicSmemBytes = splitk_smem_bytes();
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  drain_stale_error();
+  cudaError_t e = cudaLaunchKernelEx(&lc, fn, tm_a, tm_b, tm_c, p);
+  if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaLaunchKernelEx(cluster split-K)");
+  ctx->launches += 1;
+  return PATINA_GEMM_OK;
+}
+
 // Clusters of this kernel that can be resident at once (cached per kernel). A persistent grid
 // must not exceed it, or the late clusters would start their tile lists after the others finish.
 int resident_clusters(const KernelEntry* k, int num_sms, int* cache) {
@@ -669,6 +767,17 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
       (want_sk > 0 || (want_sk == 0 && !explicit_tile &&
                        streamk_preferred(in_type, out_type, M, N, K, ctx->num_sms))))
     return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream, want_sk);
+  const int want_ck = cfg ? cfg->cluster_k : 0;
+  if (want_ck > 0 && (n_extra > 0 || epi != nullptr || explicit_tile ||
+                      !cluster_k_supported(in_type, out_type, M, N, K, want_ck)))
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
+                     "cluster_k needs bf16 in and out, 2, 4 or 8 CTAs, at least that many 128-byte k-blocks, "
+                     "N a multiple of 8, the plain epilogue and no explicit tile");
+  if (n_extra == 0 && epi == nullptr && !explicit_tile && want_ck >= 0 && want_sk <= 0) {
+    const int split = want_ck > 0 ? want_ck : cluster_k_choice(in_type, out_type, M, N, K, ctx->num_sms);
+    if (split >= 2)
+      return launch_cluster_k(ctx, A, lda, B, ldb, C, ldc, M, N, K, alpha, split, cfg ? cfg->group_m : 0, stream);
+  }
   PatinaGemmPlan plan;
   const KernelEntry* k = nullptr;
   rc = make_plan(in_type, out_type, M, N, K, cfg, ctx->num_sms, &plan, &k, &err, epi != nullptr,
@@ -1538,6 +1647,12 @@ int patina_gemm_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
 int patina_gemm_streamk_chosen(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
   if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return 0;
   return streamk_preferred(in_type, out_type, M, N, K, num_sms) ? 1 : 0;
+}
+
+int patina_gemm_cluster_k_chosen(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return 0;
+  if (streamk_preferred(in_type, out_type, M, N, K, num_sms)) return 0;
+  return cluster_k_choice(in_type, out_type, M, N, K, num_sms);
 }
 
 int patina_gemm_streamk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms,

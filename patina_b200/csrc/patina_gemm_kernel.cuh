@@ -84,7 +84,9 @@ struct GemmParams {
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
 #ifdef PATINA_TRACE
-  unsigned long long* trace;  // [grid][32]: time stamps of a trace build (never in the shipped library)
+  unsigned long long* trace;  // [grid][64]: time stamps of a trace build (never in the shipped library);
+                              // words 32..47: cycle counter when the MMA issuer's wait for k-block i of
+                              // its first tile returned, 48..63: when the producer issued its loads
   uint32_t l2_hint_a, l2_hint_b;  // trace builds: L2 eviction hint on operand loads of pair kernels
                                   // (0 none, 1 evict-first, 2 evict-last)
 #endif
@@ -96,13 +98,20 @@ struct GemmParams {
 #define PATINA_TRACE_AT(slot)                                                     \
   do {                                                                            \
     if (p.trace) {                                                                \
-      p.trace[(size_t)blockIdx.x * 32u + (slot)] = ptx::globaltimer_ns();         \
-      p.trace[(size_t)blockIdx.x * 32u + 16u + (slot)] = (unsigned long long)clock64(); \
+      p.trace[(size_t)blockIdx.x * 64u + (slot)] = ptx::globaltimer_ns();         \
+      p.trace[(size_t)blockIdx.x * 64u + 16u + (slot)] = (unsigned long long)clock64(); \
     }                                                                             \
+  } while (0)
+#define PATINA_TRACE_KB(base, i)                                                             \
+  do {                                                                                      \
+    if (p.trace && (i) < 16u) p.trace[(size_t)blockIdx.x * 64u + (base) + (i)] = (unsigned long long)clock64(); \
   } while (0)
 #else
 #define PATINA_TRACE_AT(slot) \
   do {                        \
+  } while (0)
+#define PATINA_TRACE_KB(base, i) \
+  do {                           \
   } while (0)
 #endif
 
@@ -458,6 +467,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         for (uint32_t kb = kb_first; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
           if (!ok) break;
+          if (t == cluster_id) PATINA_TRACE_KB(48u, kb);
           const uint32_t sa = ring + s * T::kStageBytes;
           const uint32_t sb = sa + T::kABytes;
           const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
@@ -549,6 +559,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
           if (!ok) break;
           ptx::tc_fence_after_sync();
           if (it == 0 && kb == 0) PATINA_TRACE_AT(2);
+          if (it == 0) PATINA_TRACE_KB(32u, kb);
           const uint32_t sa = ring + s * T::kStageBytes;
           const uint64_t db = smem_desc_sw128_kmajor(sa + T::kABytes);
           if constexpr (kMx) {

@@ -22,7 +22,7 @@ SYMBOLS = (
     "patina_gemm_plan", "patina_gemm_smem_desc", "patina_gemm_idesc",
     "patina_gemm_k_advance_units", "patina_gemm_tmem_lane_offset", "patina_gemm_tile_coord",
     "patina_gemm_version", "patina_gemm_streamk_plan", "patina_gemm_streamk_chosen", "patina_gemm_streamk_range",
-    "patina_gemm_streamk_owner", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped", "patina_gemm_fp8e4m3_tn_grouped",
+    "patina_gemm_streamk_owner", "patina_gemm_cluster_k_chosen", "patina_gemm_bf16_tn_skinny_noalloc", "patina_gemm_bf16_tn_scatter", "patina_gemm_bf16_tn_fused", "patina_gemm_bf16_tn_fused_fp8out", "patina_gemm_bf16_tn_grouped", "patina_gemm_fp8e4m3_tn_grouped",
     "patina_gemm_mxfp8_tn", "patina_gemm_mx_scale_bytes", "patina_gemm_mx_scale_offset", "patina_gemm_idesc_mx",
     "patina_gemm_column_shard", "patina_gemm_sharded_bf16_tn",
     "patina_gemm_peer_alloc",
@@ -39,7 +39,8 @@ class StreamKPlan(C.Structure):
 
 class GemmConfig(C.Structure):
     _fields_ = [("cta_group", C.c_int32), ("block_n", C.c_int32), ("stages", C.c_int32),
-                ("group_m", C.c_int32), ("max_ctas", C.c_int32), ("m_sub", C.c_int32), ("stream_k", C.c_int32)]
+                ("group_m", C.c_int32), ("max_ctas", C.c_int32), ("m_sub", C.c_int32), ("stream_k", C.c_int32),
+                ("cluster_k", C.c_int32)]
 
 
 class GemmEpilogue(C.Structure):
@@ -109,6 +110,7 @@ def load() -> C.CDLL:
     L.patina_gemm_version.restype = C.c_char_p
     L.patina_gemm_streamk_plan.argtypes = [i32, i64, i64, i64, i32, C.POINTER(StreamKPlan)]
     L.patina_gemm_streamk_chosen.argtypes = [i32, i32, i64, i64, i64, i32]
+    L.patina_gemm_cluster_k_chosen.argtypes = [i32, i32, i64, i64, i64, i32]
     L.patina_gemm_streamk_range.argtypes = [C.c_uint64] * 3 + [C.POINTER(C.c_uint64)] * 2
     L.patina_gemm_streamk_range.restype = None
     L.patina_gemm_streamk_owner.argtypes = [C.c_uint64] * 3

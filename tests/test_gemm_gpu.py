@@ -505,6 +505,54 @@ def test_scatter_to_several_destinations_on_one_gpu(ctx, oracle_mod):
         ctx.gemm_bf16_tn_scatter(dA, dB, [ptrs[0], ptrs[1] + 2], ldc)   # misaligned destination
 
 
+@pytest.mark.parametrize("M,N,K", [(1024, 1024, 1024), (256, 4096, 4096), (1000, 776, 2056), (129, 264, 520),
+                                   (512, 512, 512)])
+def test_cluster_split_k(ctx, oracle_mod, M, N, K):
+    """K cut across a thread-block cluster (2, 4 and 8 CTAs per 128 x 256 tile), partial tiles
+    summed through distributed shared memory in rank order: every cluster size against the
+    oracle, ragged M / N / K, padding columns untouched, two runs bit-identical, and the
+    library's own choice for the shape."""
+    from patina_b200 import inputs, GemmConfig, lib as L
+    A, B = inputs.make_operands("llm", M, N, K, seed=M + K)
+    want = expect_bf16(oracle_mod, A, B, alpha=0.5)
+    dA, dB = A.cuda(), B.cuda()
+    ldc = N + 8
+    for split in (2, 4, 8):
+        if (K + 63) // 64 < split:
+            continue
+        outs = []
+        for _ in range(2):
+            full = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")
+            before = ctx.launch_count
+            ctx.gemm_tn(dA, dB, out=full[:, :N], alpha=0.5, config=GemmConfig(0, 0, 0, 0, 0, 0, 0, split))
+            ctx.status()
+            assert ctx.launch_count - before == 1
+            check_norm(oracle_mod, full[:, :N], want, f"cluster_k={split} {M}x{N}x{K}")
+            assert bool(torch.isnan(full[:, N:]).all()), f"cluster_k={split}: columns behind N were written"
+            outs.append(full[:, :N].clone())
+        assert torch.equal(outs[0], outs[1])
+    auto = ctx.gemm_tn(dA, dB, alpha=0.5)
+    never = ctx.gemm_tn(dA, dB, alpha=0.5, config=GemmConfig(0, 0, 0, 0, 0, 0, 0, -1))
+    ctx.status()
+    check_norm(oracle_mod, auto, want, "library's choice")
+    check_norm(oracle_mod, never, auto.float().cpu().numpy(), "large-tile kernel vs library's choice")
+
+
+def test_cluster_split_k_refusals(ctx):
+    import patina_b200
+    from patina_b200 import GemmConfig
+    A = torch.zeros((256, 128), dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros((260, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(patina_b200.PatinaGemmError, match="cluster_k"):
+        ctx.gemm_tn(A, B[:256], config=GemmConfig(0, 0, 0, 0, 0, 0, 0, 4))       # 2 k-blocks < 4 CTAs
+    with pytest.raises(patina_b200.PatinaGemmError, match="cluster_k"):
+        ctx.gemm_tn(A, B, out=torch.empty((256, 264), dtype=torch.bfloat16, device="cuda")[:, :260],
+                    config=GemmConfig(0, 0, 0, 0, 0, 0, 0, 2))                   # N = 260 is not a multiple of 8
+    with pytest.raises(patina_b200.PatinaGemmError, match="cluster_k"):
+        ctx.gemm_tn(A, B[:256], config=GemmConfig(0, 0, 0, 0, 0, 0, 0, 3))
+    ctx.status()
+
+
 def test_sharded_entry_point_on_one_gpu(oracle_mod):
     """patina_gemm_sharded_bf16_tn with several shards that all live on this GPU (one context and
     one stream per shard, as on a multi-GPU node one per GPU): each shard writes its column block

@@ -284,3 +284,21 @@ def test_mx_quantiser_round_trip(oracle_mod):
     amax = x.reshape(40, 3, 32).abs().amax(dim=2, keepdim=True).expand(40, 3, 32).reshape(40, 96).numpy()
     assert np.all(np.abs(back - x.numpy()) <= amax * 2.0 ** -3)      # e4m3: 3 mantissa bits, scale within 2x of amax/448
     assert np.all(np.abs(back) <= 448.0 * np.ldexp(1.0, e.numpy().astype(np.int32) - 127).repeat(32, axis=1) + 0)
+
+
+def test_cluster_split_k_choice(built_lib):
+    """Which problems get K cut across a cluster: more than 128 rows, few 128 x 256 tiles (one
+    wave of clusters), enough k-blocks saved per CTA to pay for the exchange; never the skinny
+    shapes (stream-K), never shapes that fill the machine."""
+    from patina_b200 import lib as Lm
+    c = lambda M, N, K: built_lib.patina_gemm_cluster_k_chosen(Lm.IN_BF16, Lm.OUT_BF16, M, N, K, 148)
+    assert c(1024, 1024, 1024) == 4          # 32 tiles x 4 = 128 CTAs, 16 -> 4 k-blocks each
+    assert c(256, 4096, 4096) == 4
+    assert c(1024, 1024, 4096) == 4
+    assert c(512, 512, 4096) == 8            # 8 tiles: eight CTAs per tile
+    assert c(2048, 2048, 2048) == 0          # 128 tiles: no room for a second CTA per tile
+    assert c(8192, 8192, 8192) == 0
+    assert c(1024, 1024, 256) == 0           # 4 k-blocks: nothing to save
+    assert c(128, 1024, 8192) == 0 and c(16, 28672, 8192) == 0      # skinny paths
+    assert c(1024, 1028, 1024) == 0          # N not a multiple of 8
+    assert built_lib.patina_gemm_cluster_k_chosen(Lm.IN_E4M3, Lm.OUT_BF16, 1024, 1024, 1024, 148) == 0

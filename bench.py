@@ -62,6 +62,9 @@ WORKLOADS = {
                         "bf16 TN GEMM M=N=K=4096, N(0,1)*0.1, fp32 accumulate, bf16 out"),
     "fp8_tn_8192": _wl(8192, 8192, 8192, "unit_normal", "fp8 e4m3 TN GEMM M=N=K=8192, per-tensor scales "
                        "amax/448, fp32 accumulate, bf16 out scaled by sa*sb", dtype="e4m3"),
+    "mxfp8_tn_8192": _wl(8192, 8192, 8192, "unit_normal", "block-scaled fp8 (MXFP8) TN GEMM M=N=K=8192: e4m3 elements, "
+                         "one E8M0 scale per 32 K elements of a row, quantised from N(0,1), fp32 accumulate, bf16 out",
+                         dtype="mxe4m3"),
     "fp8_tn_16384": _wl(16384, 16384, 16384, "unit_normal", "fp8 e4m3 TN GEMM M=N=K=16384, per-tensor "
                         "scales, bf16 out; N split over the GPUs", dtype="e4m3", scaling="strong"),
 }
@@ -274,14 +277,25 @@ def run_ours(args):
     else:
         N = wl["N"]
         n_total = wl["N"] * world
-    fp8 = wl["dtype"] == "e4m3"
+    mx = wl["dtype"] == "mxe4m3"
+    fp8 = wl["dtype"] == "e4m3" or mx
     ebytes = 1 if fp8 else 2
     G = wl["groups"]
     ctx = patina_b200.GemmContext(local_rank)
     # This rank's column shard: its own seed, so shards differ like real weight shards do;
     # A (activations) is replicated: every rank draws it from rank 0's seed.
     alpha = 1.0
-    if fp8:
+    sfa_h = sfb_h = d_sfa = d_sfb = None
+    if mx:
+        A32, _ = inputs.make_operands(wl["dist"], M, 1, K, dtype=torch.float32, seed=inputs.DEFAULT_SEED)
+        _, B32 = inputs.make_operands(wl["dist"], 1, N, K, dtype=torch.float32, seed=inputs.DEFAULT_SEED + rank)
+        A_h, ea = inputs.quantize_mxfp8(A32)
+        B_h, eb_ = inputs.quantize_mxfp8(B32)
+        sfa_h, sfb_h = inputs.pack_mx_scales(ea).pin_memory(), inputs.pack_mx_scales(eb_).pin_memory()
+        d_sfa, d_sfb = sfa_h.cuda(), sfb_h.cuda()
+        A_h, B_h = A_h.pin_memory(), B_h.pin_memory()
+        del A32, B32
+    elif fp8:
         A32, _ = inputs.make_operands(wl["dist"], M, 1, K, dtype=torch.float32, seed=inputs.DEFAULT_SEED)
         _, B32 = inputs.make_operands(wl["dist"], 1, N, K, dtype=torch.float32, seed=inputs.DEFAULT_SEED + rank)
         A_h, sa = inputs.quantize_e4m3(A32)
@@ -382,6 +396,8 @@ def run_ours(args):
                                                     residual=res_d, activation=act)
     elif G:
         step = lambda i: ctx.gemm_bf16_tn_grouped(dA, dBs[i % len(dBs)], d_rows, out=dC, alpha=alpha)
+    elif mx:
+        step = lambda i: ctx.gemm_mxfp8_tn(dA, d_sfa, dBs[i % len(dBs)], d_sfb, out=dC, alpha=alpha)
     else:
         step = lambda i: ctx.gemm_tn(dA, dBs[i % len(dBs)], out=dC, alpha=alpha)
     # A step shorter than ~150 us is launch-bound from Python: replay it from a CUDA graph.
@@ -449,6 +465,19 @@ def run_ours(args):
             torch.cuda.current_stream().synchronize()
         e2e_total_ms, _ = timed(e2e_step, e2e_steps, min(args.warmup, 3))
         ctx.status()
+    elif mx:
+        # elements and scales from pinned host memory every step, the result back
+        def e2e_step(i):
+            dA.copy_(A_h, non_blocking=True)
+            dBs[0].copy_(B_h, non_blocking=True)
+            d_sfa.copy_(sfa_h, non_blocking=True)
+            d_sfb.copy_(sfb_h, non_blocking=True)
+            ctx.gemm_mxfp8_tn(dA, d_sfa, dBs[0], d_sfb, out=dC, alpha=alpha)
+            C_h.copy_(dC, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e2e_total_ms, _ = timed(e2e_step, e2e_steps, min(args.warmup, 3))
+        ctx.status()
+        e2e_note = "explicit copies of elements and scales, patina_gemm_mxfp8_tn, copy of C back"
     elif world > 1 and not fp8:
         # Many GPUs: the replicated A crosses PCIe once per node (every rank uploads 1/world of
         # it and an all-gather over NVLink completes it), each rank uploads its own B shard.
@@ -465,6 +494,8 @@ def run_ours(args):
         ctx.status()
     e2e_value = flops_total / (e2e_total_ms / e2e_steps * 1e-3) / 1e12
     h2d = (M * K + N * K) * ebytes if not G else M * K * ebytes + 4 * G
+    if mx:
+        h2d += sfa_h.numel() + sfb_h.numel()
     d2h = M * N * 2
     if world > 1 and not fp8 and not G and not args.no_e2e:
         h2d, d2h = h2d_rank, d2h_rank
@@ -507,7 +538,7 @@ def run_ours(args):
     # ---- other configurations (N = 1) and the strong-scaling block (every N)
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     peaks = json.load(open(peaks_path)) if os.path.isfile(peaks_path) else None
-    del dA, dBs, dC
+    del dA, dBs, dC, d_sfa, d_sfb
     torch.cuda.empty_cache()
 
     def device_operands(w, m, n, k, seed):
@@ -520,6 +551,10 @@ def run_ours(args):
                 return torch.rand(shape, generator=g, device="cuda") * (spec[2] - spec[1]) + spec[1]
             return torch.randn(shape, generator=g, device="cuda") * spec[1]
         a, b, al = draw(da, (m, k)), draw(db, (n, k)), 1.0
+        if w["dtype"] == "mxe4m3":
+            a, ea = inputs.quantize_mxfp8(a)
+            b, eb = inputs.quantize_mxfp8(b)
+            return a, b, (inputs.pack_mx_scales(ea), inputs.pack_mx_scales(eb))
         if w["dtype"] == "e4m3":
             sa, sb = float(a.abs().max()) / 448.0, float(b.abs().max()) / 448.0
             a = (a / sa).clamp_(-448, 448).to(torch.float8_e4m3fn)
@@ -559,7 +594,7 @@ def run_ours(args):
             n, nt = c1 - c0, w["N"]
         else:
             c0, n, nt = 0, w["N"], w["N"]
-        eb = 1 if w["dtype"] == "e4m3" else 2
+        eb = 1 if w["dtype"] in ("e4m3", "mxe4m3") else 2
         a, b, al = device_operands(w, m, n, k, inputs.DEFAULT_SEED + 17 * rank)
         bs = [b] + [b.clone() for _ in range(w["rotate"] - 1)]
         c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
@@ -569,7 +604,10 @@ def run_ours(args):
         st = int(min(400, max(10, budget_ms * 1e3 / est)))
         if gs:
             st = max(gs, st // gs * gs)
-        fn = lambda i: ctx.gemm_tn(a, bs[i % len(bs)], out=c, alpha=al)
+        if w["dtype"] == "mxe4m3":
+            fn = lambda i: ctx.gemm_mxfp8_tn(a, al[0], bs[i % len(bs)], al[1], out=c)
+        else:
+            fn = lambda i: ctx.gemm_tn(a, bs[i % len(bs)], out=c, alpha=al)
         t_ms, per_ms = timed(fn, st, 3, gs)
         ctx.status()
         ms = t_ms / st
@@ -585,7 +623,7 @@ def run_ours(args):
             ach = fl / (ms * 1e-3) / 1e12
             pk = (float(peaks["bf16_tflops"]) if peaks else FALLBACK_BF16_TFLOPS) * (2.0 if eb == 1 else 1.0)
             note = "measured bf16 burst (MEASURED_PEAKS.json)" + (" x 2" if eb == 1 else "")
-            if eb == 1 and world == 1:
+            if eb == 1 and world == 1 and w["dtype"] == "e4m3":
                 # No fp8 figure is in MEASURED_PEAKS.json: measure the library's fp8 GEMM (cuBLASLt
                 # through torch._scaled_mm) on these operands here, the way the bf16 peak was
                 # measured (best of 10, CUDA events), and use it as the denominator.
@@ -622,8 +660,8 @@ def run_ours(args):
     if not args.no_extras and not (G or args.fused_epilogue) and args.workload == "bf16_tn_8192":
         if world == 1:
             extras["configs"] = {nm: measure(nm) for nm in
-                                 ("bf16_tn_1024", "bf16_tn_4096", "fp8_tn_8192", "skinny_m16", "skinny_m64",
-                                  "skinny_m128")}
+                                 ("bf16_tn_1024", "bf16_tn_4096", "fp8_tn_8192", "mxfp8_tn_8192", "skinny_m16",
+                                  "skinny_m64", "skinny_m128")}
         strong = {}
         for nm in ("llm_proj_4096x4096", "llm_proj_14336x4096", "llm_proj_4096x14336", "llm_proj_28672x8192",
                    "fp8_tn_16384", "skinny_m16", "skinny_m128"):
@@ -679,7 +717,7 @@ def run_ours(args):
         "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
         "higher_is_better": True, "scaling": wl["scaling"], "vs_baseline": None,
-        "dtype": "fp8_e4m3" if fp8 else "bf16", "data": "synthetic",
+        "dtype": "mxfp8_e4m3" if mx else ("fp8_e4m3" if fp8 else "bf16"), "data": "synthetic",
         "config": {"workload": f"{args.workload}: {wl['desc']}" +
                                (f"; N-column shards, one {N}-column shard per GPU, A replicated"
                                 if world > 1 else ""),

@@ -172,18 +172,30 @@ __device__ __noinline__ void raise_abort(const WaitCtx& w, uint32_t code, uint32
 
 // Returns false when the wait was abandoned (limit reached here, or another
 // role raised the abort flag).
+//
+// The poll loop is kept tight: the barrier is re-tested back to back, and the abort flag and
+// the clock are looked at only every kWaitCheckEvery-th failed poll. (Looking at them every
+// fourth poll, as an earlier version did, paced every load-bound pipeline at about 560 cycles per
+// stage whatever the stage size: a completion that arrives while the waiting thread reads the
+// global timer is only seen afterwards.)
+#ifndef PATINA_WAIT_MODE
+#define PATINA_WAIT_MODE 1
+#endif
+constexpr uint32_t kWaitCheckEvery = (PATINA_WAIT_MODE == 0) ? 4u : (PATINA_WAIT_MODE == 1 ? 64u : 1024u);
 template <bool kClusterScope>
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx& w,
                                              uint32_t code, uint32_t detail) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
   for (;;) {
+#if PATINA_WAIT_MODE == 2
+    const bool done = kClusterScope ? ptx::mbar_test_wait_cluster(bar, parity) : ptx::mbar_test_wait(bar, parity);
+#else
     const bool done = kClusterScope ? ptx::mbar_try_wait_cluster(bar, parity)
                                     : ptx::mbar_try_wait(bar, parity);
+#endif
     if (done) return true;
-    // try_wait itself blocks for a hardware-defined slice, so a few failed polls
-    // already mean microseconds; look at the clock every fourth one.
-    if ((++spins & 3u) == 0u) {
+    if ((++spins & (kWaitCheckEvery - 1u)) == 0u) {
       if (*w.abort_flag) return false;
       const uint64_t now = ptx::globaltimer_ns();
       if (t0 == 0) {

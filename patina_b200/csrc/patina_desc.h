@@ -157,28 +157,42 @@ constexpr uint32_t kStoreBoxRows = 32;      // one epilogue warp's rows
 constexpr uint32_t kBarrierRegionBytes = 256;
 constexpr uint32_t kMaxDynSmem = 232448;    // 227 KB
 
-// Epilogue staging: every epilogue warp owns two buffers of 32 rows, double-buffered so that
-// filling one overlaps the TMA store reading the other. With four epilogue warps a row
-// segment is 128 bytes (128-byte swizzle); with eight warps (m_sub = 2) it is 64 bytes
-// (64-byte swizzle), which keeps the total at 32 KB. One-byte outputs also stage 64-byte rows
-// (64 columns per box, the same register count per chunk as a 128-byte row of bf16).
-PATINA_HD constexpr uint32_t staging_bufs(uint32_t) { return 2u; }
-PATINA_HD constexpr uint32_t staging_row_bytes(uint32_t m_sub, uint32_t out_bytes) {
+// Epilogue staging, 32 KB in every configuration. With four epilogue warps each warp owns two
+// buffers of 32 rows x 128 bytes (128-byte swizzle), double-buffered so that filling one overlaps
+// the TMA store reading the other. With eight warps (m_sub = 2) the plain bf16 epilogue gives each
+// warp ONE buffer of 32 rows x 128 bytes: half as many boxes per tile as 64-byte rows would take,
+// and per box the proxy fence, the TMA store issue (235 cycles on one lane) and the buffer wait are
+// paid once; the store's read of the buffer is waited out before it is refilled. (128-byte-row
+// boxes also cross NVLink faster when the destinations are peer buffers.) The fused epilogue of
+// the eight-warp tiles keeps two buffers of 64-byte rows (64-byte swizzle): 64 accumulator words
+// plus 64 bias/residual words per thread would not fit its registers. One-byte outputs stage
+// 64-byte rows (64 columns per box).
+#ifndef PATINA_WIDE_EPILOGUE
+#define PATINA_WIDE_EPILOGUE 1
+#endif
+PATINA_HD constexpr bool staging_wide(uint32_t m_sub, uint32_t out_bytes, bool fused) {
+  return PATINA_WIDE_EPILOGUE != 0 && m_sub == 2 && out_bytes == 2 && !fused;
+}
+PATINA_HD constexpr uint32_t staging_bufs(uint32_t m_sub, uint32_t out_bytes = 2, bool fused = false) {
+  return staging_wide(m_sub, out_bytes, fused) ? 1u : 2u;
+}
+PATINA_HD constexpr uint32_t staging_row_bytes(uint32_t m_sub, uint32_t out_bytes, bool fused = false) {
+  if (staging_wide(m_sub, out_bytes, fused)) return 128u;
   return ((m_sub == 2 && out_bytes == 2) || out_bytes == 1) ? 64u : 128u;
 }
-PATINA_HD constexpr uint32_t staging_buf_bytes(uint32_t m_sub, uint32_t out_bytes) {
-  return kStoreBoxRows * staging_row_bytes(m_sub, out_bytes);
+PATINA_HD constexpr uint32_t staging_buf_bytes(uint32_t m_sub, uint32_t out_bytes, bool fused = false) {
+  return kStoreBoxRows * staging_row_bytes(m_sub, out_bytes, fused);
 }
 
 PATINA_HD constexpr SmemPlan smem_plan(uint32_t cta_group, uint32_t m_sub, uint32_t block_n,
                                        uint32_t stages, uint32_t out_bytes = 2,
-                                       uint32_t sf_stage_bytes = 0) {
+                                       uint32_t sf_stage_bytes = 0, bool fused = false) {
   SmemPlan p{};
   p.a_bytes = m_sub * kCtaRows * kBlockKBytes;
   p.b_bytes = (block_n / cta_group) * kBlockKBytes;
   p.stage_bytes = p.a_bytes + p.b_bytes;
   p.stages = stages;
-  p.staging_bytes = 4 * m_sub * staging_bufs(m_sub) * staging_buf_bytes(m_sub, out_bytes);
+  p.staging_bytes = 4 * m_sub * staging_bufs(m_sub, out_bytes, fused) * staging_buf_bytes(m_sub, out_bytes, fused);
   p.barrier_bytes = kBarrierRegionBytes;
   // +1024: the ring is placed on the next 1024-byte boundary (swizzle atom).
   // (block-scaled operands: the scales of a stage sit in a ring of their own behind the staging)

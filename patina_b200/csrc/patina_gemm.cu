@@ -800,7 +800,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
                         : out_type == kOutE4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                                : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                         ob, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kStoreBoxRows,
-                        staging_row_bytes((uint32_t)k->m_sub, ob) / ob, &tm_c.map[d]);
+                        staging_row_bytes((uint32_t)k->m_sub, ob, epi != nullptr) / ob, &tm_c.map[d]);
     if (rc != PATINA_GEMM_OK) return rc;
   }
   for (int d = n_extra + 1; d < kMaxDests; ++d) tm_c.map[d] = tm_c.map[0];

@@ -208,7 +208,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
   }
 }
 
-template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut>
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFusedEpi = false>
 struct GemmTraits {
   static constexpr uint32_t kEpiWarps = 4 * kMSub;            // one warp per (sub-tile, lane quarter)
   static constexpr uint32_t kThreads = 64 + 32 * kEpiWarps;   // producer + MMA + epilogue warps
@@ -236,9 +236,9 @@ struct GemmTraits {
   // tcgen05.alloc takes powers of two (32..512): round the request up
   static constexpr uint32_t kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128
                                         : kTmemUsed <= 256 ? 256 : 512;
-  static constexpr uint32_t kStageBufs = staging_bufs(kMSub);       // per epilogue warp
-  static constexpr uint32_t kRowBytes = staging_row_bytes(kMSub, output_bytes(kOut));  // 128 or 64
-  static constexpr uint32_t kBufBytes = staging_buf_bytes(kMSub, output_bytes(kOut));
+  static constexpr uint32_t kStageBufs = staging_bufs(kMSub, output_bytes(kOut), kFusedEpi);  // per epilogue warp
+  static constexpr uint32_t kRowBytes = staging_row_bytes(kMSub, output_bytes(kOut), kFusedEpi);  // 128 or 64
+  static constexpr uint32_t kBufBytes = staging_buf_bytes(kMSub, output_bytes(kOut), kFusedEpi);
   static constexpr uint32_t kChunkCols = kRowBytes / output_bytes(kOut);  // columns per store box
   // A width that is not a whole number of store boxes ends with one box moved left so that it
   // finishes at the tile's edge; the columns it shares with its neighbour are written twice
@@ -246,7 +246,7 @@ struct GemmTraits {
   static constexpr uint32_t kChunks = (BN + kChunkCols - 1) / kChunkCols;
   static constexpr bool kOverlapLastChunk = (BN % kChunkCols) != 0;
   static constexpr uint32_t kSmemBytes =
-      smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut), kSfStageBytes).total_bytes;
+      smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut), kSfStageBytes, kFusedEpi).total_bytes;
   static_assert(!kMx || BN % 64 == 0, "block-scaled tiles: B's scales must start an even number of TMEM columns into an atom");
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
@@ -264,7 +264,7 @@ template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool
 __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                                              const CStoreMaps<kDests>& tm_c, const GemmParams& p,
                                              const CUtensorMap* tm_sfa, const CUtensorMap* tm_sfb) {
-  using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut>;
+  using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut, kFused>;
   constexpr bool kPair = (kCtaGroup == 2);
   constexpr bool kMx = T::kMx;
   constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
@@ -569,7 +569,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
-          ptx::tc_fence_after_sync();
+          PATINA_KLOOP_FENCE();
           if (it == 0 && kb == 0) PATINA_TRACE_AT(2);
           if (it == 0) PATINA_TRACE_KB(32u, kb);
           const uint32_t sa = ring + s * T::kStageBytes;

@@ -161,7 +161,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       for (uint32_t kb = kb0; kb < kb1; ++kb) {
         ok = bounded_wait<false>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, tile);
         if (!ok) break;
-        ptx::tc_fence_after_sync();
+        PATINA_KLOOP_FENCE();
         const uint32_t sa = ring + s * kSplitStageBytes;
         const uint64_t da = smem_desc_sw128_kmajor(sa), db = smem_desc_sw128_kmajor(sa + kABytes);
 #pragma unroll

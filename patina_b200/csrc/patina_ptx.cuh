@@ -281,6 +281,20 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// Experiment switch: whether the MMA issuer also fences after every stage's barrier wait (the
+// operands come from TMA and go to the tensor core, both on the async proxy, and the barrier wait
+// already acquires them, so no tcgen05 fence is needed there).
+#ifndef PATINA_KLOOP_FENCE_ON
+#define PATINA_KLOOP_FENCE_ON 1
+#endif
+#if PATINA_KLOOP_FENCE_ON
+#define PATINA_KLOOP_FENCE() ::patina::ptx::tc_fence_after_sync()
+#else
+#define PATINA_KLOOP_FENCE() \
+  do {                       \
+  } while (0)
+#endif
+
 // D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate != 0 keeps D.
 // kKind: 0 = kind::f16 (f16/bf16 inputs), 1 = kind::f8f6f4 (e4m3 inputs).
 template <int kCtaGroup, int kKind>

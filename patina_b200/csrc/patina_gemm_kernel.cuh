@@ -877,7 +877,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
           }
           ptx::tma_store_commit();
         }
-        sbuf ^= 1u;
+        sbuf = (sbuf + 1u) % T::kStageBufs;   // one or two staging buffers per warp
       };
       // (Requesting chunk ch + 1 from TMEM before chunk ch is converted was measured: nothing
       // gained on the plain epilogue, and the fused one lost 10 % to the second register set.)

@@ -64,7 +64,7 @@ typedef struct PatinaGemmConfig {
                         -1 = never; 2 = force, and sum shared tiles in the follow-up kernel;
                         3 = force, and let the last CTA to reach a tile sum it */
   int32_t cluster_k; /* few tiles, deep K, M > 128 (bf16): K cut across a thread-block cluster of
-                        this many CTAs (2, 4, 8) per 128 x 256 tile, partial tiles summed through
+                        this many CTAs (2 or 4) per 128 x 256 tile, partial tiles summed through
                         distributed shared memory; 0 = library decides, -1 = never */
 } PatinaGemmConfig;
 
@@ -322,7 +322,7 @@ void patina_gemm_streamk_range(uint64_t cta, uint64_t units, uint64_t parts, uin
  * problem on a device with num_sms SMs, 0 if the large-tile kernel (host-only; for tests). */
 int patina_gemm_streamk_chosen(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms);
 uint32_t patina_gemm_streamk_owner(uint64_t unit, uint64_t units, uint64_t parts);
-/* The cluster size (2, 4, 8) a call without an explicit configuration would cut K across for this
+/* The cluster size (2 or 4) a call without an explicit configuration would cut K across for this
  * problem on a device with num_sms SMs, or 0 (host-only; for tests). */
 int patina_gemm_cluster_k_chosen(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms);
 

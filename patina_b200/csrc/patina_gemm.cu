@@ -243,11 +243,9 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (k.cta_group == 2 && num_sms < 2) continue;
       if (need_fused && !k.fn_fused) continue;
       if (need_scatter && !k.fn_scatter) continue;
-      // Peer destinations: store boxes with 128-byte rows (four-warp epilogues) cross NVLink at 0.84
-      // of the plain copy rate, the 64-byte rows of the eight-warp epilogue at 0.55 (measured on
-      // two GPUs: 621 vs 408 GB/s out of each GPU, copy 744), and at eight GPUs the gather is
-      // what bounds the call.
-      if (need_scatter && k.m_sub != 1) continue;
+      // (Peer destinations: store boxes with 128-byte rows cross NVLink at 0.84 of the plain copy
+      // rate, boxes with 64-byte rows at 0.55: measured on two GPUs, 621 vs 408 GB/s out of each
+      // GPU, copy 744. Every plain epilogue stages 128-byte rows.)
       const double s = config_score(k, M, N, K, num_sms);
       if (s > best_score) {
         best_score = s;
@@ -619,7 +617,7 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
 }
 
 // ------------------------------------------------ K cut across a cluster (few tiles, deep K)
-// One cluster of S CTAs per 128 x 256 tile, each CTA taking 1/S of the k-blocks; the partial tiles
+// One cluster of S (2 or 4) CTAs per 128 x 256 tile, each CTA taking 1/S of the k-blocks; the partial tiles
 // are summed through distributed shared memory (patina_gemm_splitk.cuh). Measured facts behind
 // the choice: a 128-byte k-block costs a CTA about 525 cycles whatever the tile width, so a
 // problem with few tiles only gets faster by giving each CTA fewer k-blocks; the exchange and its
@@ -628,7 +626,7 @@ constexpr uint32_t kClusterKMinSaved = 8;
 
 bool cluster_k_supported(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int split) {
   if (in_type != kBF16 || out_type != kOutBF16) return false;
-  if (split != 2 && split != 4 && split != 8) return false;
+  if (split != 2 && split != 4) return false;
   if (M < 1 || N < 1 || (N % 8) != 0) return false;               // whole 16-byte pieces in every store box
   return (int64_t)ceil_div(K, kBlockKBytes / 2) >= split;          // every CTA gets at least one k-block
 }
@@ -638,7 +636,7 @@ int cluster_k_choice(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   if (M <= 128) return 0;                                          // the skinny paths cover these
   const uint64_t tiles = (uint64_t)ceil_div(M, kCtaRows) * ceil_div(N, kSplitBN);
   const uint32_t kb = ceil_div(K, kBlockKBytes / 2);
-  for (int split = 8; split >= 2; split /= 2) {
+  for (int split = 4; split >= 2; split /= 2) {
     if (!cluster_k_supported(in_type, out_type, M, N, K, split)) continue;
     if (tiles * (uint64_t)split > (uint64_t)num_sms) continue;     // one wave of clusters
     const uint32_t saved = kb - kb / (uint32_t)split;              // k-blocks every CTA no longer runs
@@ -662,9 +660,8 @@ int launch_cluster_k(PatinaGemmContext* ctx, const void* A, int64_t lda, const v
                       kStoreBoxRows, 32, &tm_c);
   if (rc != PATINA_GEMM_OK) return rc;
   using Fn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
-  const Fn fn = split == 2 ? gemm_splitk_cluster_kernel<2> : split == 4 ? gemm_splitk_cluster_kernel<4>
-                                                                        : gemm_splitk_cluster_kernel<8>;
-  const int fi = split == 2 ? 0 : split == 4 ? 1 : 2;
+  const Fn fn = split == 2 ? gemm_splitk_cluster_kernel<2> : gemm_splitk_cluster_kernel<4>;
+  const int fi = split == 2 ? 0 : 1;
   if (!ctx->ck_attr_set[fi]) {
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)splitk_smem_bytes());
@@ -771,7 +768,7 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   if (want_ck > 0 && (n_extra > 0 || epi != nullptr || explicit_tile ||
                       !cluster_k_supported(in_type, out_type, M, N, K, want_ck)))
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
-                     "cluster_k needs bf16 in and out, 2, 4 or 8 CTAs, at least that many 128-byte k-blocks, "
+                     "cluster_k needs bf16 in and out, 2 or 4 CTAs, at least that many 128-byte k-blocks, "
                      "N a multiple of 8, the plain epilogue and no explicit tile");
   if (n_extra == 0 && epi == nullptr && !explicit_tile && want_ck >= 0 && want_sk <= 0) {
     const int split = want_ck > 0 ? want_ck : cluster_k_choice(in_type, out_type, M, N, K, ctx->num_sms);

@@ -173,27 +173,20 @@ __device__ __noinline__ void raise_abort(const WaitCtx& w, uint32_t code, uint32
 // Returns false when the wait was abandoned (limit reached here, or another
 // role raised the abort flag).
 //
-// The poll loop is kept tight: the barrier is re-tested back to back, and the abort flag and
-// the clock are looked at only every kWaitCheckEvery-th failed poll. (Looking at them every
-// fourth poll, as an earlier version did, paced every load-bound pipeline at about 560 cycles per
-// stage whatever the stage size: a completion that arrives while the waiting thread reads the
-// global timer is only seen afterwards.)
-#ifndef PATINA_WAIT_MODE
-#define PATINA_WAIT_MODE 1
-#endif
-constexpr uint32_t kWaitCheckEvery = (PATINA_WAIT_MODE == 0) ? 4u : (PATINA_WAIT_MODE == 1 ? 64u : 1024u);
+// try_wait itself blocks for a hardware-defined slice, so a few failed polls already mean
+// microseconds; the abort flag and the clock are looked at every fourth one. (Looking at them
+// only every 64th or 1024th poll, or polling with the non-blocking test_wait, was measured on
+// twenty load- and compute-bound shapes: no difference in time anywhere, and an expired wait is
+// noticed later, so the frequent check stays.)
+constexpr uint32_t kWaitCheckEvery = 4u;
 template <bool kClusterScope>
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx& w,
                                              uint32_t code, uint32_t detail) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
   for (;;) {
-#if PATINA_WAIT_MODE == 2
-    const bool done = kClusterScope ? ptx::mbar_test_wait_cluster(bar, parity) : ptx::mbar_test_wait(bar, parity);
-#else
     const bool done = kClusterScope ? ptx::mbar_try_wait_cluster(bar, parity)
                                     : ptx::mbar_try_wait(bar, parity);
-#endif
     if (done) return true;
     if ((++spins & (kWaitCheckEvery - 1u)) == 0u) {
       if (*w.abort_flag) return false;
@@ -569,7 +562,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
-          PATINA_KLOOP_FENCE();
+          ptx::tc_fence_after_sync();
           if (it == 0 && kb == 0) PATINA_TRACE_AT(2);
           if (it == 0) PATINA_TRACE_KB(32u, kb);
           const uint32_t sa = ring + s * T::kStageBytes;

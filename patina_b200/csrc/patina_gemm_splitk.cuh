@@ -16,13 +16,18 @@
 //   1. runs the usual TMA -> ring -> tcgen05.mma mainloop (same 1 + 1 + 4 warp roles as the
 //      reference's generated kernel, v2_gemm_pipelined.ptx:89-94) over ITS k-blocks only, into
 //      one 256-column accumulator in TMEM;
-//   2. after a cluster barrier (every CTA's ring is idle from then on) its epilogue warps send,
-//      for every other CTA o, the 256/kSplit columns that o owns, as fp32, into o's shared memory
-//      (st.shared::cluster into the idle ring, slot r);
-//   3. after a second cluster barrier sums its own columns over the CTAs in rank order (its own
-//      part comes from TMEM), so the result does not depend on timing, scales, rounds to bf16 and
-//      stores through swizzled staging and TMA like the large-tile kernel.
-// Every mbarrier wait is bounded; a CTA whose wait ran out still joins both cluster barriers.
+//   2. after a cluster barrier (every CTA's ring is idle from then on) its epilogue warps copy,
+//      for every other CTA o, the 256/kSplit columns that o owns, as fp32, from TMEM through a
+//      local staging area into o's shared memory with bulk copies (cp.async.bulk shared::cta ->
+//      shared::cluster, completing on o's receive barrier). Plain st.shared::cluster stores were
+//      measured first: about 10 bytes per clock per SM, 6.5 us for the 96 KB a CTA of a 4-cluster
+//      sends; the copy engine moves the same bytes several times faster;
+//   3. waits for its own receive barrier (all parts for its columns have landed), sums them in
+//      rank order with its own part from TMEM, so the result does not depend on timing, scales,
+//      rounds to bf16 and stores through swizzled staging and TMA like the large-tile kernel.
+// A last cluster barrier (arrive after the receive wait, wait before exit) keeps every CTA's
+// shared memory alive until the copies that read it are done. Every mbarrier wait is bounded; a
+// CTA whose wait ran out still joins the cluster barriers.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -51,6 +56,16 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
                "r"(d)
                : "memory");
 }
+// Bulk copy from this CTA's shared memory into another CTA's of the cluster; the bytes count on
+// an mbarrier of the destination CTA (both destination addresses are shared::cluster addresses).
+// Addresses and size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                                     uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster),
+               "r"(src_cta), "r"(bytes), "r"(bar_cluster)
+               : "memory");
+}
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -62,7 +77,7 @@ template <int kSplit>
 __global__ void __launch_bounds__(192, 1)
 gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
-  static_assert(kSplit == 2 || kSplit == 4 || kSplit == 8, "cluster sizes 2, 4, 8");
+  static_assert(kSplit == 2 || kSplit == 4, "cluster sizes 2 and 4: receive and send areas of 8 would not fit the ring");
   constexpr uint32_t kOwnCols = kSplitBN / kSplit;       // columns of the tile this CTA finishes
   constexpr uint32_t kOwnChunks = kOwnCols / 32u;        // 32-column chunks of them
   constexpr uint32_t kBlockKElems = kBlockKBytes / 2u;   // bf16
@@ -71,7 +86,9 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   // so that a warp's store or load of one piece is 512 contiguous bytes.
   constexpr uint32_t kChunkBytes = 8u * 32u * 16u;
   constexpr uint32_t kSlotBytes = 4u * kOwnChunks * kChunkBytes;   // one sender's part: 128 rows x kOwnCols fp32
-  static_assert(kSplit * kSlotBytes <= kSplitStages * kSplitStageBytes, "receive slots must fit in the ring");
+  // ring, once idle: [kSplit - 1 receive slots][kSplit - 1 send slots]
+  constexpr uint32_t kRecvBytes = (kSplit - 1u) * kSlotBytes;
+  static_assert(2u * kRecvBytes <= kSplitStages * kSplitStageBytes, "receive and send areas must fit in the ring");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -81,7 +98,8 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   const uint32_t full_bar = bars;
   const uint32_t empty_bar = bars + 8u * kSplitStages;
   const uint32_t tfull_bar = bars + 16u * kSplitStages;
-  const uint32_t tmem_slot = tfull_bar + 8u;
+  const uint32_t recv_bar = tfull_bar + 8u;         // completes when every other CTA's part has landed
+  const uint32_t tmem_slot = recv_bar + 8u;
   const uint32_t abort_slot = tmem_slot + 4u;
   uint8_t* const smem_generic = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   volatile uint32_t* const tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot - smem_base));
@@ -112,9 +130,12 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       ptx::mbar_init(empty_bar + 8u * s, 1);
     }
     ptx::mbar_init(tfull_bar, 1);
+    ptx::mbar_init(recv_bar, 1);
     *abort_ptr = 0u;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
+    // what this CTA will receive: kSplit - 1 parts of 128 rows x kOwnCols fp32
+    ptx::mbar_arrive_expect_tx(recv_bar, kRecvBytes);
   }
   // The producer lane starts the first pass through the ring before the set-up barrier.
   uint32_t pre = 0;
@@ -161,7 +182,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       for (uint32_t kb = kb0; kb < kb1; ++kb) {
         ok = bounded_wait<false>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, tile);
         if (!ok) break;
-        PATINA_KLOOP_FENCE();
+        ptx::tc_fence_after_sync();
         const uint32_t sa = ring + s * kSplitStageBytes;
         const uint64_t da = smem_desc_sw128_kmajor(sa), db = smem_desc_sw128_kmajor(sa + kABytes);
 #pragma unroll
@@ -195,11 +216,14 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   const uint32_t taddr = tmem_base + tmem_lane_offset(q);
   const bool live = (*abort_ptr == 0u);
   if (warp_idx >= 2 && live) {
-    // ---- 2. send the columns the other CTAs own into their receive slots (slot = my rank) ----
-#pragma unroll 1
+    // ---- 2. my accumulator's columns that other CTAs own -> local send area -> their receive slot
+    const uint32_t send_area = ring + kRecvBytes;
+    const uint32_t my_slot = rank;                                     // slot index at a receiver: senders in rank order,
+#pragma unroll 1                                                       // the receiver's own rank left out
     for (uint32_t o = 0; o < (uint32_t)kSplit; ++o) {
       if (o == rank) continue;
-      const uint32_t remote = ptx::mapa(ring + rank * kSlotBytes + q * (kOwnChunks * kChunkBytes), o);
+      const uint32_t oi = o < rank ? o : o - 1u;                        // my send slot for destination o
+      const uint32_t local = send_area + oi * kSlotBytes + q * (kOwnChunks * kChunkBytes);
 #pragma unroll 1
       for (uint32_t c = 0; c < kOwnChunks; ++c) {
         uint32_t v[32];
@@ -207,18 +231,32 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         ptx::tmem_ld_wait();
 #pragma unroll
         for (uint32_t j = 0; j < 8u; ++j)
-          ptx::st_cluster_v4(remote + c * kChunkBytes + (j * 32u + lane) * 16u, v[4 * j], v[4 * j + 1], v[4 * j + 2],
-                             v[4 * j + 3]);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(local + c * kChunkBytes + (j * 32u + lane) * 16u),
+                       "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                       : "memory");
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t si = my_slot < o ? my_slot : my_slot - 1u;     // my slot at receiver o
+        const uint32_t remote = ptx::mapa(ring + si * kSlotBytes + q * (kOwnChunks * kChunkBytes), o);
+        ptx::bulk_copy_to_cluster(remote, local, kOwnChunks * kChunkBytes, ptx::mapa(recv_bar, o));
       }
     }
   }
 
-  // ---- barrier 2: all parts have arrived (release / acquire at cluster scope) ------------------
+  // ---- all parts for my columns have landed -------------------------------------------------
+  bool got = true;
+  if (warp_idx >= 2) {
+    got = bounded_wait<true>(recv_bar, 0u, w, kTimeoutEpilogueTmemFull, tile);
+    got = __all_sync(0xffffffffu, got);
+  }
+  // Everything this CTA will ever read from a partner has arrived; tell the cluster (the matching
+  // wait is at the very end: nobody's shared memory may go away while a copy still reads it).
   __syncwarp();
   ptx::cluster_arrive();
-  ptx::cluster_wait();
 
-  if (warp_idx >= 2 && live && (*abort_ptr == 0u)) {
+  if (warp_idx >= 2 && live && got && (*abort_ptr == 0u)) {
     // ---- 3. sum my columns over the CTAs in rank order, scale, round, store ------------------
     const uint32_t e = warp_idx - 2u;
     const uint32_t stg0 = staging + e * (2u * kStoreBoxRows * 64u);
@@ -239,7 +277,8 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 #pragma unroll
           for (uint32_t i = 0; i < 32u; ++i) acc[i] = (src == 0u) ? __uint_as_float(own[i]) : acc[i] + __uint_as_float(own[i]);
         } else {
-          const uint32_t base = ring + src * kSlotBytes + q * (kOwnChunks * kChunkBytes) + c * kChunkBytes;
+          const uint32_t si = src < rank ? src : src - 1u;
+          const uint32_t base = ring + si * kSlotBytes + q * (kOwnChunks * kChunkBytes) + c * kChunkBytes;
 #pragma unroll
           for (uint32_t j = 0; j < 8u; ++j) {
             const uint4 x = ptx::ld_shared_v4(base + (j * 32u + lane) * 16u);
@@ -286,6 +325,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
   __syncwarp();
+  ptx::cluster_wait();        // every CTA of the cluster has received all its parts: no copy still reads my send area
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();

@@ -238,7 +238,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (uint32_t kb = kb0; kb < kb1; ++kb) {
           ok = bounded_wait<false>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
-          PATINA_KLOOP_FENCE();
+          ptx::tc_fence_after_sync();
           const uint32_t sw = ring + s * kSkStageStride;
           const uint64_t dw = smem_desc_sw128_kmajor(sw);
           const uint64_t dx = smem_desc_sw128_kmajor(sw + kWBytes);

@@ -113,34 +113,6 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return ok != 0;
 }
 
-// Non-blocking tests of the same condition (no hardware suspend).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -280,20 +252,6 @@ __device__ __forceinline__ void tc_fence_before_sync() {
 __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-
-// Experiment switch: whether the MMA issuer also fences after every stage's barrier wait (the
-// operands come from TMA and go to the tensor core, both on the async proxy, and the barrier wait
-// already acquires them, so no tcgen05 fence is needed there).
-#ifndef PATINA_KLOOP_FENCE_ON
-#define PATINA_KLOOP_FENCE_ON 1
-#endif
-#if PATINA_KLOOP_FENCE_ON
-#define PATINA_KLOOP_FENCE() ::patina::ptx::tc_fence_after_sync()
-#else
-#define PATINA_KLOOP_FENCE() \
-  do {                       \
-  } while (0)
-#endif
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate != 0 keeps D.
 // kKind: 0 = kind::f16 (f16/bf16 inputs), 1 = kind::f8f6f4 (e4m3 inputs).

@@ -295,7 +295,7 @@ def test_cluster_split_k_choice(built_lib):
     assert c(1024, 1024, 1024) == 4          # 32 tiles x 4 = 128 CTAs, 16 -> 4 k-blocks each
     assert c(256, 4096, 4096) == 4
     assert c(1024, 1024, 4096) == 4
-    assert c(512, 512, 4096) == 8            # 8 tiles: eight CTAs per tile
+    assert c(512, 512, 4096) == 4            # 8 tiles: the largest cluster
     assert c(2048, 2048, 2048) == 0          # 128 tiles: no room for a second CTA per tile
     assert c(8192, 8192, 8192) == 0
     assert c(1024, 1024, 256) == 0           # 4 k-blocks: nothing to save

@@ -619,10 +619,13 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
 // ------------------------------------------------ K cut across a cluster (few tiles, deep K)
 // One cluster of S (2 or 4) CTAs per 128 x 256 tile, each CTA taking 1/S of the k-blocks; the partial tiles
 // are summed through distributed shared memory (patina_gemm_splitk.cuh). Measured facts behind
-// the choice: a 128-byte k-block costs a CTA about 525 cycles whatever the tile width, so a
-// problem with few tiles only gets faster by giving each CTA fewer k-blocks; the exchange and its
-// two cluster barriers cost about as much as kClusterKMinSaved k-blocks.
-constexpr uint32_t kClusterKMinSaved = 8;
+// the choice: a 128-byte k-block costs a CTA about 560 cycles (0.3 us) whatever the tile width (a
+// tcgen05.mma of 128 rows takes its 128 cycles whether it has 64 or 256 columns), so a problem
+// with few tiles only gets faster by giving each CTA fewer k-blocks; the cluster launch, the
+// exchange and its barriers cost 3 us (two CTAs) to 6 us (four), i.e. kClusterKMinSaved k-blocks
+// must be saved per CTA before the cut pays (1024 x 2048 x 2048: 12.4 vs 14.5 us;
+// 256 x 4096 x 4096: 15.8 vs 23.2 us; 512 x 512 x 4096: 13.0 vs 22.0 us; but 1024^3: 9.4 vs 8.7 us).
+constexpr uint32_t kClusterKMinSaved = 16;
 
 bool cluster_k_supported(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int split) {
   if (in_type != kBF16 || out_type != kOutBF16) return false;
@@ -684,7 +687,7 @@ int launch_cluster_k(PatinaGemmContext* ctx, const void* A, int64_t lda, const v
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
 #ifdef PATINA_TRACE
-  p.trace = nullptr;
+  p.trace = ctx->trace;
   p.l2_hint_a = p.l2_hint_b = 0;
 #endif
   cudaLaunchConfig_t lc{};
@@ -1576,6 +1579,18 @@ int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const vo
       e = cudaEventCreateWithFlags(&ctx->ev[i], cudaEventDisableTiming);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "creating copy streams/events");
   }
+  // Every row block takes the path the whole problem would take, so that the result does not
+  // depend on how this call cuts the rows (a block alone might be small enough for the cluster
+  // split, whose sums round differently).
+  PatinaGemmConfig block_cfg{};
+  if (cfg) block_cfg = *cfg;
+  if (block_cfg.cluster_k == 0) {
+    const bool tile_given = block_cfg.cta_group != 0 || block_cfg.block_n != 0 || block_cfg.m_sub != 0;
+    const int whole = tile_given ? 0 : cluster_k_choice(in_type, out_type, M, N, K, ctx->num_sms);
+    block_cfg.cluster_k = whole > 0 ? whole : -1;
+  }
+  if (block_cfg.stream_k == 0) block_cfg.stream_k = -1;   // M >= 1024 here
+  cfg = &block_cfg;
   cudaEvent_t ev_start = ctx->ev[0], ev_b = ctx->ev[1], ev_done = ctx->ev[2];
   cudaEvent_t* ev_a = &ctx->ev[3];
   cudaEvent_t* ev_g = &ctx->ev[3 + kHostChunksMax];

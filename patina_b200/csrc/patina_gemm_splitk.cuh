@@ -122,6 +122,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 
   // ---------------------------------------------------------------- prologue
   if (threadIdx.x == 0) {
+    PATINA_TRACE_AT(0);
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_b);
     ptx::prefetch_tensormap(&tm_c);
@@ -158,6 +159,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) PATINA_TRACE_AT(1);
 
   if (warp_idx == 0) {
     // ---------------------------------------------------------- TMA producer
@@ -183,6 +185,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         ok = bounded_wait<false>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, tile);
         if (!ok) break;
         ptx::tc_fence_after_sync();
+        if (kb == kb0) PATINA_TRACE_AT(2);
         const uint32_t sa = ring + s * kSplitStageBytes;
         const uint64_t da = smem_desc_sw128_kmajor(sa), db = smem_desc_sw128_kmajor(sa + kABytes);
 #pragma unroll
@@ -197,6 +200,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         ptx::umma_commit<1>(tfull_bar);
         // every MMA has retired (and so every load was consumed) before the ring changes hands
         bounded_wait<false>(tfull_bar, 0u, w, kTimeoutMmaDrain, tile);
+        PATINA_TRACE_AT(3);
       }
     }
   } else {
@@ -211,6 +215,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   __syncwarp();
   ptx::cluster_arrive();
   ptx::cluster_wait();
+  if (threadIdx.x == 64) PATINA_TRACE_AT(4);       // first cluster barrier passed
 
   const uint32_t q = warp_idx & 3u;                                  // TMEM lane quarter of an epilogue warp
   const uint32_t taddr = tmem_base + tmem_lane_offset(q);
@@ -245,6 +250,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     }
   }
 
+  if (threadIdx.x == 64) PATINA_TRACE_AT(5);       // my parts are staged and their copies issued
   // ---- all parts for my columns have landed -------------------------------------------------
   bool got = true;
   if (warp_idx >= 2) {
@@ -253,6 +259,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   }
   // Everything this CTA will ever read from a partner has arrived; tell the cluster (the matching
   // wait is at the very end: nobody's shared memory may go away while a copy still reads it).
+  if (threadIdx.x == 64) PATINA_TRACE_AT(6);       // received everything
   __syncwarp();
   ptx::cluster_arrive();
 
@@ -330,6 +337,7 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (warp_idx == 1) ptx::tmem_dealloc<1>(tmem_base, 256);
+  if (threadIdx.x == 32) PATINA_TRACE_AT(7);
 }
 
 }  // namespace patina

@@ -292,7 +292,8 @@ def test_cluster_split_k_choice(built_lib):
     shapes (stream-K), never shapes that fill the machine."""
     from patina_b200 import lib as Lm
     c = lambda M, N, K: built_lib.patina_gemm_cluster_k_chosen(Lm.IN_BF16, Lm.OUT_BF16, M, N, K, 148)
-    assert c(1024, 1024, 1024) == 4          # 32 tiles x 4 = 128 CTAs, 16 -> 4 k-blocks each
+    assert c(1024, 1024, 1024) == 0          # 16 k-blocks: the exchange costs more than it saves
+    assert c(1024, 2048, 2048) == 2          # 64 tiles, 32 k-blocks: two CTAs per tile
     assert c(256, 4096, 4096) == 4
     assert c(1024, 1024, 4096) == 4
     assert c(512, 512, 4096) == 4            # 8 tiles: the largest cluster

@@ -452,6 +452,7 @@ def run_ours(args):
     # end to end: host buffers in, host buffer out, every step
     e2e_steps = min(args.steps, 200)
     e2e_note = "patina_gemm_host: H2D of A and B, GEMM, D2H of C, pipelined over row blocks"
+    link_probe = None
     if args.no_e2e:
         e2e_total_ms = float("nan")
     elif G:
@@ -488,6 +489,25 @@ def run_ours(args):
                     f"(all-gather, {M * K * ebytes * (world - 1) // world} bytes received per rank)")
         h2d_rank, d2h_rank = host_run.pcie_bytes()
         del host_run
+        # What the host side can deliver when every rank copies at once (no GEMM, no NVLink): the
+        # B shard in, the C shard out, together. e2e cannot be faster than this on this host.
+        dB0 = dBs[0]
+        side_out = torch.cuda.Stream()
+
+        def copies_only(i):
+            cur = torch.cuda.current_stream()
+            side_out.wait_stream(cur)
+            dB0.copy_(B_h, non_blocking=True)
+            with torch.cuda.stream(side_out):
+                C_h.copy_(dC, non_blocking=True)
+            cur.wait_stream(side_out)
+        probe_ms, _ = timed(copies_only, 10, 2)
+        probe_ms /= 10
+        link_probe = {"ms_per_step": round(probe_ms, 4),
+                      "bytes_per_rank": N * K * ebytes + M * N * 2,
+                      "aggregate_GBps": round(world * (N * K * ebytes + M * N * 2) / (probe_ms * 1e-3) / 1e9, 1),
+                      "what": "all ranks at once: B shard host-to-device and C shard device-to-host, pinned "
+                              "buffers, two streams, nothing else; max over ranks"}
     else:
         e2e_total_ms, _ = timed(lambda i: ctx.gemm_host(A_h, B_h, C_h, alpha=alpha), e2e_steps,
                                 min(args.warmup, 3))
@@ -734,7 +754,8 @@ def run_ours(args):
         "pct_of_nominal_peak": round(100.0 * value / world / nominal, 2),
         "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_total_ms / e2e_steps, 4),
-                "bytes_are": "per rank (rank 0's)", "path": e2e_note},
+                "bytes_are": "per rank (rank 0's)", "path": e2e_note,
+                **({"host_link_probe": link_probe} if link_probe else {})},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": wl["bound"], "achieved": round(achieved, 2), "peak": peak, "unit": unit,

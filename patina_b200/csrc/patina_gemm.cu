@@ -608,6 +608,9 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   if (p.split_reduce && !streamk_any_shared_tile(sp.units, sp.grid, sp.k_blocks)) p.split_reduce = 0u;
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
+#ifdef PATINA_TRACE
+  p.trace = ctx->trace;
+#endif
   cudaError_t e = (in_type == kBF16)
                       ? launch_sk_kernel<kBF16>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[0])
                       : launch_sk_kernel<kE4M3>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[1]);
@@ -1873,6 +1876,9 @@ extern "C" int patina_gemm_bf16_tn_skinny_noalloc(const void* A, int64_t lda, co
   p.counters = reinterpret_cast<uint32_t*>(d.scratch + kNoAllocStatusBytes);
   p.partials = reinterpret_cast<float*>(d.scratch + kNoAllocStatusBytes + kNoAllocCounterBytes);
   p.wait_limit_ns = 2000000000ull;
+#ifdef PATINA_TRACE
+  p.trace = nullptr;
+#endif
   gemm_streamk_kernel<kBF16><<<sp.grid, 192, streamk_smem_bytes(sp.m_pad), stream>>>(tm_w, tm_x, p);
   e = cudaGetLastError();
   if (e != cudaSuccess)

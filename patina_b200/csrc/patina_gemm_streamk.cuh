@@ -50,6 +50,9 @@ struct StreamKParams {
                            // streamk_reduce_kernel, launched right after on the same stream
   uint32_t* status;
   uint64_t wait_limit_ns;
+#ifdef PATINA_TRACE
+  unsigned long long* trace;  // trace builds only: [grid][64] time stamps (see patina_gemm_kernel.cuh)
+#endif
 };
 
 enum : uint32_t { kTimeoutStreamK = 6 };
@@ -148,6 +151,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // W is read exactly once: keep it from displacing X (re-read by every CTA) in L2.
   uint64_t stream_once = 0, keep = 0;
   if (threadIdx.x == 0) {
+    PATINA_TRACE_AT(0);
     ptx::prefetch_tensormap(&tm_w);
     ptx::prefetch_tensormap(&tm_x);
     for (uint32_t s = 0; s < kStages; ++s) {
@@ -184,6 +188,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) PATINA_TRACE_AT(1);
   // Let the follow-up reduce kernel's blocks take their places now; they wait for this grid to
   // complete before touching memory.
   if (p.split_reduce) ptx::launch_dependents();
@@ -239,6 +244,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           ok = bounded_wait<false>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
           ptx::tc_fence_after_sync();
+          if (u == u_begin && kb == kb0) PATINA_TRACE_AT(2);
+          if (seg == 0) PATINA_TRACE_KB(32u, kb - kb0);
           const uint32_t sw = ring + s * kSkStageStride;
           const uint64_t dw = smem_desc_sw128_kmajor(sw);
           const uint64_t dx = smem_desc_sw128_kmajor(sw + kWBytes);
@@ -252,6 +259,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         if (!ok) break;
         ptx::umma_commit<1>(tfull_bar + 8u * buf);
+        PATINA_TRACE_AT(3);
         u += kb1 - kb0;
         ++seg;
       }
@@ -283,6 +291,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         dead = !ok;
       }
       ptx::tc_fence_after_sync();
+      if (epi_tid == 0) PATINA_TRACE_AT(4);   // (last segment's stamp stays)
       const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * 128u;
       const uint32_t n = t * kSkTileRows + q * 32u + lane;  // the column of C this thread owns
       const bool whole = (kb0 == 0u && kb1 == p.k_blocks);
@@ -331,6 +340,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           if (is_last) __threadfence();
         }
       }
+      if (epi_tid == 0) PATINA_TRACE_AT(5);   // partial published / arrival counted
       if (is_last) {
         // 2. sum the contributors in their fixed order (this CTA's part comes from TMEM), scale,
         //    round to bf16 and store C[m][n]. Sixteen values of m at a time; the partials of up
@@ -384,6 +394,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
         }
       }
+      if (epi_tid == 0) PATINA_TRACE_AT(6);   // segment finished (C written if this CTA was last)
       // accumulator drained: hand the TMEM buffer back
       if (!dead) {
         ptx::tc_fence_before_sync();
@@ -406,6 +417,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (warp_idx == 1) ptx::tmem_dealloc<1>(tmem_base, kSkTmemCols);
+  if (threadIdx.x == 32) PATINA_TRACE_AT(7);
 }
 
 // Second half of a split-reduce launch: sums the partial tiles that gemm_streamk_kernel

@@ -718,7 +718,7 @@ int resident_clusters(const KernelEntry* k, int num_sms, int* cache) {
   if (*cache != 0) return *cache;
   cudaLaunchConfig_t qc{};
   qc.gridDim = dim3((unsigned)(num_sms / k->cta_group) * k->cta_group, 1, 1);
-  qc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
+  qc.blockDim = dim3(64 + 128 * k->m_sub + (k->in_type == kMXE4M3 ? 32 : 0), 1, 1);
   qc.dynamicSmemBytes = k->smem_bytes;
   cudaLaunchAttribute qa[1];
   qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -1029,7 +1029,7 @@ int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sf
 
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3(clusters * k->cta_group, 1, 1);
-  lc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
+  lc.blockDim = dim3(64 + 128 * k->m_sub + 32, 1, 1);   // + the scale-producer warp
   lc.dynamicSmemBytes = k->smem_bytes;
   lc.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -204,7 +204,8 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
 template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFusedEpi = false>
 struct GemmTraits {
   static constexpr uint32_t kEpiWarps = 4 * kMSub;            // one warp per (sub-tile, lane quarter)
-  static constexpr uint32_t kThreads = 64 + 32 * kEpiWarps;   // producer + MMA + epilogue warps
+  // producer + MMA + epilogue warps (+ the scale-producer warp of block-scaled kernels)
+  static constexpr uint32_t kThreads = 64 + 32 * kEpiWarps + (is_block_scaled(kIn) ? 32u : 0u);
   static constexpr uint32_t kBlockKElems = kBlockKBytes / input_bytes(kIn);
   static constexpr uint32_t kUmmaK = umma_k(kIn);
   static constexpr uint32_t kUmmaPerStage = kBlockKElems / kUmmaK;  // 4
@@ -449,25 +450,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         const uint32_t n_sub = live_subtiles(c);
         // bytes this CTA loads per stage
         const uint32_t stage_tx = n_sub * T::kASubBytes + T::kBBytes + T::kSfStageBytes;
-        // Block scales: the atom row of each A slab, and the atoms under this tile's rows of B
-        // (all of them in both CTAs of a pair: every CTA's accumulator has all BN columns).
-        // Indices are clamped into the buffers; an atom past the edge only scales rows or columns
-        // that are never stored.
-        uint32_t sfa_atom[kMSub] = {}, sfb_atom[T::kSfbAtoms > 0 ? T::kSfbAtoms : 1] = {};
-        if constexpr (kMx) {
-#pragma unroll
-          for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
-            uint32_t mb = ((uint32_t)a_row + ms * kCtaRows * kCtaGroup) / kSfAtomRows;
-            mb = mb < p.sf_m_blocks ? mb : p.sf_m_blocks - 1u;
-            sfa_atom[ms] = mb * p.sf_k_atoms;
-          }
-#pragma unroll
-          for (uint32_t a = 0; a < T::kSfbAtoms; ++a) {
-            uint32_t nb = (c.n * BN) / kSfAtomRows + a;
-            nb = nb < p.sf_n_blocks ? nb : p.sf_n_blocks - 1u;
-            sfb_atom[a] = nb * p.sf_k_atoms;
-          }
-        }
+        // (block scales of a stage are loaded by the scale-producer warp, onto the same barrier)
         bool ok = true;
         for (uint32_t kb = kb_first; kb < p.k_blocks; ++kb) {
           ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
@@ -501,17 +484,6 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
                                     a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
             }
-            if constexpr (kMx) {
-              const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
-#pragma unroll
-              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-                ptx::tma_load_2d_pair(sfs + ms * kSfAtomBytes, tm_sfa, leader_full + 8u * s, 0,
-                                      (int32_t)(sfa_atom[ms] + kb));
-#pragma unroll
-              for (uint32_t a = 0; a < T::kSfbAtoms; ++a)
-                ptx::tma_load_2d_pair(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, leader_full + 8u * s, 0,
-                                      (int32_t)(sfb_atom[a] + kb));
-            }
           } else {
             ptx::mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
 #pragma unroll
@@ -520,17 +492,6 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
                 ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * s, k0,
                                a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
             ptx::tma_load_2d(sb, &tm_b, full_bar + 8u * s, k0, b_row);
-            if constexpr (kMx) {
-              const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
-#pragma unroll
-              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-                ptx::tma_load_2d(sfs + ms * kSfAtomBytes, tm_sfa, full_bar + 8u * s, 0,
-                                 (int32_t)(sfa_atom[ms] + kb));
-#pragma unroll
-              for (uint32_t a = 0; a < T::kSfbAtoms; ++a)
-                ptx::tma_load_2d(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, full_bar + 8u * s, 0,
-                                 (int32_t)(sfb_atom[a] + kb));
-            }
           }
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
         }
@@ -610,6 +571,59 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         const uint32_t last = it - 1;
         bounded_wait<kPair>(tfull_bar + 8u * (last % T::kAccBufs), (last / T::kAccBufs) & 1u, w,
                             kTimeoutMmaDrain, it);
+      }
+    }
+  }
+  // ---------------------------------------------------- scale producer (block-scaled kernels)
+  // One more warp behind the epilogue warps: it walks the same tiles and stages as the TMA
+  // producer and issues the stage's scale atoms (512 bytes each: the atom row of each A slab,
+  // and the atoms under the tile's rows of B -- all of them in both CTAs of a pair, since every
+  // CTA's accumulator has all BN columns) onto the same `full` barrier, whose expected byte
+  // count, set by the TMA producer, includes them. Issuing a TMA load costs the issuing lane
+  // over a hundred cycles; with up to four more loads per stage on the operand producer's lane
+  // the ring was issue-bound (tensor pipe 60 % at 8192^3). Atom indices are clamped into the
+  // buffers; an atom past the edge only scales rows or columns that are never stored.
+  else if (kMx && warp_idx == 2u + kEpiWarps) {
+    if constexpr (kMx) {
+      if (lane == 0) {
+        uint32_t s = 0, ph = 0, grp = 0;
+        const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
+        for (uint32_t t = cluster_id; t < num_tiles; t += num_clusters) {
+          const TileSpot c = locate(t, grp);
+          const uint32_t a_row = c.row_base + c.m * T::kTileM + cta_rank * kCtaRows;
+          uint32_t sfa_atom[kMSub], sfb_atom[T::kSfbAtoms > 0 ? T::kSfbAtoms : 1];
+#pragma unroll
+          for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
+            uint32_t mb = (a_row + ms * kCtaRows * kCtaGroup) / kSfAtomRows;
+            mb = mb < p.sf_m_blocks ? mb : p.sf_m_blocks - 1u;
+            sfa_atom[ms] = mb * p.sf_k_atoms;
+          }
+#pragma unroll
+          for (uint32_t a = 0; a < T::kSfbAtoms; ++a) {
+            uint32_t nb = (c.n * BN) / kSfAtomRows + a;
+            nb = nb < p.sf_n_blocks ? nb : p.sf_n_blocks - 1u;
+            sfb_atom[a] = nb * p.sf_k_atoms;
+          }
+          bool ok = true;
+          for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+            ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
+            if (!ok) break;
+            const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
+            const uint32_t bar = (kPair ? leader_full : full_bar) + 8u * s;
+#pragma unroll
+            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
+              if constexpr (kPair) ptx::tma_load_2d_pair(sfs + ms * kSfAtomBytes, tm_sfa, bar, 0, (int32_t)(sfa_atom[ms] + kb));
+              else ptx::tma_load_2d(sfs + ms * kSfAtomBytes, tm_sfa, bar, 0, (int32_t)(sfa_atom[ms] + kb));
+            }
+#pragma unroll
+            for (uint32_t a = 0; a < T::kSfbAtoms; ++a) {
+              if constexpr (kPair) ptx::tma_load_2d_pair(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, bar, 0, (int32_t)(sfb_atom[a] + kb));
+              else ptx::tma_load_2d(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, bar, 0, (int32_t)(sfb_atom[a] + kb));
+            }
+            if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
+          }
+          if (!ok) break;
+        }
       }
     }
   }
@@ -929,7 +943,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 // Block-scaled operands (e4m3 elements, one E8M0 scale per 32 K elements of a row): the same
 // kernel with the scale buffers of A and B as two more tensor maps.
 template <int kCtaGroup, int kMSub, int BN, int kStages>
-__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
+__global__ void __launch_bounds__(64 + 128 * kMSub + 32, 1)   // + the scale-producer warp
 gemm_mx_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CStoreMaps<1> tm_c, const __grid_constant__ CUtensorMap tm_sfa,
                   const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {

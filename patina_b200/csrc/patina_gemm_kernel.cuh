@@ -224,9 +224,13 @@ struct GemmTraits {
   static constexpr uint32_t kSfAtoms = kMx ? (kMSub + kSfbAtoms) : 0u;
   static constexpr uint32_t kSfStageBytes = kSfAtoms * kSfAtomBytes;
   static constexpr uint32_t kSfCols = 4u * kSfAtoms;
-  static constexpr uint32_t kAccBufs = (2 * kAccCols + kSfCols <= 512) ? 2 : 1;
+  // (Two copies of the scale columns used by alternate k-blocks, so that the next k-block's copy
+  // need not wait for the MMAs still reading this one's, were measured: no gain, 459 vs 457 us at
+  // 8192^3. One copy.)
+  static constexpr uint32_t kSfCopies = 1;
+  static constexpr uint32_t kAccBufs = (2 * kAccCols + kSfCopies * kSfCols <= 512) ? 2 : 1;
   static constexpr uint32_t kSfCol0 = kAccBufs * kAccCols;          // first scale column
-  static constexpr uint32_t kTmemUsed = kAccBufs * kAccCols + kSfCols;
+  static constexpr uint32_t kTmemUsed = kAccBufs * kAccCols + kSfCopies * kSfCols;
   // tcgen05.alloc takes powers of two (32..512): round the request up
   static constexpr uint32_t kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128
                                         : kTmemUsed <= 256 ? 256 : 512;
@@ -514,8 +518,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
         // block scales in TMEM: A's slabs first, then B's atoms; the tile's first row of B may
         // lie 64 rows into its first atom, i.e. 2 columns in (widths are multiples of 64)
-        const uint32_t tsfa0 = tmem_base + T::kSfCol0;
-        const uint32_t tsfb0 = tsfa0 + 4u * (uint32_t)kMSub + ((c.n * BN) % kSfAtomRows) / 32u;
+        const uint32_t tsf_base = tmem_base + T::kSfCol0;
+        const uint32_t sfb_off = 4u * (uint32_t)kMSub + ((c.n * BN) % kSfAtomRows) / 32u;
         ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
         if (!ok) break;
         ptx::tc_fence_after_sync();
@@ -528,6 +532,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
           if (it == 0) PATINA_TRACE_KB(32u, kb);
           const uint32_t sa = ring + s * T::kStageBytes;
           const uint64_t db = smem_desc_sw128_kmajor(sa + T::kABytes);
+          const uint32_t tsfa0 = tsf_base + (kb % T::kSfCopies) * T::kSfCols;   // this k-block's copy of the scale columns
+          const uint32_t tsfb0 = tsfa0 + sfb_off;
           if constexpr (kMx) {
             // this k-block's scales: shared memory -> TMEM, 32 lines of 16 bytes per atom (8-line
             // groups 128 bytes apart, no swizzle)
@@ -580,9 +586,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
   // and the atoms under the tile's rows of B -- all of them in both CTAs of a pair, since every
   // CTA's accumulator has all BN columns) onto the same `full` barrier, whose expected byte
   // count, set by the TMA producer, includes them. Issuing a TMA load costs the issuing lane
-  // over a hundred cycles; with up to four more loads per stage on the operand producer's lane
-  // the ring was issue-bound (tensor pipe 60 % at 8192^3). Atom indices are clamped into the
-  // buffers; an atom past the edge only scales rows or columns that are never stored.
+  // over a hundred cycles, and a stage has up to four scale atoms: they are kept off the operand
+  // producer's lane (measured at 8192^3: 457 us against 463 us with one lane issuing everything).
+  // Atom indices are clamped into the buffers; an atom past the edge only scales rows or columns
+  // that are never stored.
   else if (kMx && warp_idx == 2u + kEpiWarps) {
     if constexpr (kMx) {
       if (lane == 0) {

@@ -394,6 +394,7 @@ struct PatinaGemmContext {
 #ifdef PATINA_TRACE
   unsigned long long* trace = nullptr;  // trace builds only: [grid][32] time stamps of the next launch
   uint32_t l2_hint_a = 0, l2_hint_b = 0;
+  uint32_t box_rows = 0;                // trace builds only: rows per operand TMA box (0 = whole slab)
   PatinaGemmConfig scatter_cfg{};       // trace builds only: tile override for the scatter entry
   bool has_scatter_cfg = false;
 #endif
@@ -791,11 +792,18 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   const uint32_t kelems = kBlockKBytes / ib;
   CUtensorMap tm_a, tm_b;
   CStoreMaps<kMaxDests> tm_c;
+  // Rows per TMA box: the whole slab unless a smaller box divides it (see GemmParams::a_box_rows).
+  const uint32_t b_rows = (uint32_t)(k->block_n / k->cta_group);
+  uint32_t a_box = kCtaRows, b_box = b_rows;
+#ifdef PATINA_TRACE
+  if (ctx->box_rows && kCtaRows % ctx->box_rows == 0) a_box = ctx->box_rows;
+  if (ctx->box_rows && b_rows % ctx->box_rows == 0 && ctx->box_rows < b_rows) b_box = ctx->box_rows;
+#endif
   rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
-                      kCtaRows, kelems, &tm_a);
+                      a_box, kelems, &tm_a);
   if (rc != PATINA_GEMM_OK) return rc;
   rc = get_tensor_map(ctx, B, tmap_in_type(in_type), ib, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
-                      (uint32_t)(k->block_n / k->cta_group), kelems, &tm_b);
+                      b_box, kelems, &tm_b);
   if (rc != PATINA_GEMM_OK) return rc;
   for (int d = 0; d <= n_extra; ++d) {
     rc = get_tensor_map(ctx, d == 0 ? C : extra_dests[d - 1],
@@ -846,6 +854,8 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     p.activation = (uint32_t)epi->activation;
   }
   p.n_dests = (uint32_t)(1 + n_extra);
+  p.a_box_rows = a_box;
+  p.b_box_rows = b_box;
   p.c_dests[0] = C;
   for (int d = 0; d < n_extra; ++d) p.c_dests[d + 1] = extra_dests[d];
   p.ldc = ldc;
@@ -1006,6 +1016,8 @@ int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sf
   p.n_dests = 1;
   p.c_dests[0] = C;
   p.ldc = ldc;
+  p.a_box_rows = kCtaRows;
+  p.b_box_rows = (uint32_t)(k->block_n / k->cta_group);
   p.sf_m_blocks = ceil_div(M, kSfAtomRows);
   p.sf_n_blocks = ceil_div(N, kSfAtomRows);
   p.sf_k_atoms = ceil_div(K, 128);
@@ -1140,6 +1152,8 @@ int launch_grouped(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.group_m = (cfg && cfg->group_m > 0) ? (uint32_t)cfg->group_m : 8u;
   p.alpha = alpha;
   p.n_dests = 1;
+  p.a_box_rows = kCtaRows;
+  p.b_box_rows = (uint32_t)(k->block_n / k->cta_group);
   p.group_rows = group_rows;
   p.group_alpha = group_alpha;
   p.n_groups = (uint32_t)n_groups;
@@ -1197,6 +1211,12 @@ int patina_gemm_debug_set_scatter_config(PatinaGemmContext* ctx, const PatinaGem
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   ctx->has_scatter_cfg = cfg != nullptr;
   if (cfg) ctx->scatter_cfg = *cfg;
+  return PATINA_GEMM_OK;
+}
+// Trace builds only: fetch operand slabs as several TMA boxes of this many rows (0 = one box).
+int patina_gemm_debug_set_box_rows(PatinaGemmContext* ctx, uint32_t rows) {
+  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
+  ctx->box_rows = rows;
   return PATINA_GEMM_OK;
 }
 // Trace builds only: L2 eviction hints on the operand loads of pair kernels (0 none, 1 evict-first,

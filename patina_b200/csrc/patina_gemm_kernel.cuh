@@ -81,6 +81,9 @@ struct GemmParams {
   // block-scaled operands (kernels instantiated with kMXE4M3): extents of the scale buffers in
   // atoms of 128 rows x 128 K elements, so that tiles hanging over the edge read inside them
   uint32_t sf_m_blocks, sf_n_blocks, sf_k_atoms;
+  // rows per TMA box of A and of B (the tensor maps are encoded with these): a 128-row slab of A,
+  // or this CTA's rows of B, may be fetched as several smaller boxes
+  uint32_t a_box_rows, b_box_rows;
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
 #ifdef PATINA_TRACE
@@ -350,9 +353,11 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         ptx::mbar_arrive_expect_tx(full_bar + 8u * kb, T::kStageBytes);
 #pragma unroll
         for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-          ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * kb, k0,
-                           a_row + (int32_t)(ms * kCtaRows));
-        ptx::tma_load_2d(sa + T::kABytes, &tm_b, full_bar + 8u * kb, k0, b_row);
+          for (uint32_t r = 0; r < kCtaRows; r += p.a_box_rows)
+            ptx::tma_load_2d(sa + ms * T::kASubBytes + r * kBlockKBytes, &tm_a, full_bar + 8u * kb, k0,
+                             a_row + (int32_t)(ms * kCtaRows + r));
+        for (uint32_t r = 0; r < T::kBRows; r += p.b_box_rows)
+          ptx::tma_load_2d(sa + T::kABytes + r * kBlockKBytes, &tm_b, full_bar + 8u * kb, k0, b_row + (int32_t)r);
       }
       pre_kb = n_pre;
     }
@@ -484,18 +489,22 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
 #pragma unroll
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
               if (ms < n_sub)
-                ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0,
-                                    a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
-            ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
+                for (uint32_t r = 0; r < kCtaRows; r += p.a_box_rows)
+                  ptx::tma_load_2d_pair(sa + ms * T::kASubBytes + r * kBlockKBytes, &tm_a, leader_full + 8u * s, k0,
+                                        a_row + (int32_t)(ms * kCtaRows * kCtaGroup + r));
+            for (uint32_t r = 0; r < T::kBRows; r += p.b_box_rows)
+              ptx::tma_load_2d_pair(sb + r * kBlockKBytes, &tm_b, leader_full + 8u * s, k0, b_row + (int32_t)r);
             }
           } else {
             ptx::mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
 #pragma unroll
             for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
               if (ms < n_sub)
-                ptx::tma_load_2d(sa + ms * T::kASubBytes, &tm_a, full_bar + 8u * s, k0,
-                               a_row + (int32_t)(ms * kCtaRows * kCtaGroup));
-            ptx::tma_load_2d(sb, &tm_b, full_bar + 8u * s, k0, b_row);
+                for (uint32_t r = 0; r < kCtaRows; r += p.a_box_rows)
+                  ptx::tma_load_2d(sa + ms * T::kASubBytes + r * kBlockKBytes, &tm_a, full_bar + 8u * s, k0,
+                                   a_row + (int32_t)(ms * kCtaRows * kCtaGroup + r));
+            for (uint32_t r = 0; r < T::kBRows; r += p.b_box_rows)
+              ptx::tma_load_2d(sb + r * kBlockKBytes, &tm_b, full_bar + 8u * s, k0, b_row + (int32_t)r);
           }
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
         }

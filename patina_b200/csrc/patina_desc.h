@@ -186,10 +186,12 @@ PATINA_HD constexpr uint32_t staging_buf_bytes(uint32_t m_sub, uint32_t out_byte
 
 PATINA_HD constexpr SmemPlan smem_plan(uint32_t cta_group, uint32_t m_sub, uint32_t block_n,
                                        uint32_t stages, uint32_t out_bytes = 2,
-                                       uint32_t sf_stage_bytes = 0, bool fused = false) {
+                                       uint32_t sf_stage_bytes = 0, bool fused = false,
+                                       uint32_t k_chunks = 1) {
   SmemPlan p{};
-  p.a_bytes = m_sub * kCtaRows * kBlockKBytes;
-  p.b_bytes = (block_n / cta_group) * kBlockKBytes;
+  // (k_chunks: 128-byte spans of K per stage; more than one when a stage is fetched with 3-D boxes)
+  p.a_bytes = m_sub * kCtaRows * kBlockKBytes * k_chunks;
+  p.b_bytes = (block_n / cta_group) * kBlockKBytes * k_chunks;
   p.stage_bytes = p.a_bytes + p.b_bytes;
   p.stages = stages;
   p.staging_bytes = 4 * m_sub * staging_bufs(m_sub, out_bytes, fused) * staging_buf_bytes(m_sub, out_bytes, fused);

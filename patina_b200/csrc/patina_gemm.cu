@@ -51,6 +51,7 @@ struct KernelEntry {
   KernelFn fn_fused;     // same kernel with the bias / residual / activation epilogue, or null
   ScatterFn fn_scatter;  // same kernel storing every tile to up to kMaxDests destinations, or null
   uint32_t smem_bytes;
+  int k_chunks = 1;      // k-blocks per stage; above 1 the operands come in 3-D boxes (K % 128 bytes == 0)
 };
 
 #define PATINA_KERNEL(G, MS, BN, S, IN, OUT)                                    \
@@ -67,6 +68,11 @@ struct KernelEntry {
     gemm_tn_kernel<G, MS, BN, S, IN, OUT, true>,                    \
     gemm_tn_kernel<G, MS, BN, S, IN, OUT, false, false, kMaxDests>, \
     GemmTraits<G, MS, BN, S, IN, OUT>::kSmemBytes }
+
+// single-CTA kernel with KC k-blocks per stage (3-D operand boxes), plain epilogue
+#define PATINA_KERNEL_KC(MS, BN, S, IN, OUT, KC)                                                   \
+  { 1, MS, BN, S, IN, OUT, gemm_tn_chunked_kernel<MS, BN, S, IN, OUT, KC>, nullptr, nullptr,       \
+    GemmTraits<1, MS, BN, S, IN, OUT, false, KC>::kSmemBytes, KC }
 
 // Listed best-first per type pair: an explicit request takes the first match.
 #define PATINA_KERNEL_Q(G, MS, BN, S)                                           \
@@ -89,10 +95,15 @@ const KernelEntry kKernels[] = {
     PATINA_KERNEL_F(2, 2, 160, 4, kBF16, kOutBF16),
     PATINA_KERNEL_F(2, 2, 128, 4, kBF16, kOutBF16),  // 512 x 128 per pair, double-buffered
     PATINA_KERNEL_F(2, 1, 128, 8, kBF16, kOutBF16),
+    // Two k-blocks per stage, one 3-D box per operand and stage (see GemmTraits::kChunkABytes):
+    // listed before their one-k-block twins, so they win ties and take plain launches whose K is
+    // whole k-blocks (1024^3: 7.6 - 7.9 us against 8.9; 2048 x 1024 x 1024: 8.4 against 9.6).
+    PATINA_KERNEL_KC(1, 128, 3, kBF16, kOutBF16, 2),
     PATINA_KERNEL_F(1, 1, 128, 6, kBF16, kOutBF16),
     // narrow tiles for problems with fewer 128-wide tiles than SMs: every SM's share of the
     // operands shrinks with the tile count, and one SM takes in about 64 bytes per clock
     PATINA_KERNEL_F(2, 1, 64, 8, kBF16, kOutBF16),   // 256 x 64 per pair
+    PATINA_KERNEL_KC(1, 64, 4, kBF16, kOutBF16, 2),
     PATINA_KERNEL_F(1, 1, 64, 8, kBF16, kOutBF16),   // 128 x 64
     // e4m3 -> bf16
     PATINA_KERNEL(2, 2, 256, 4, kE4M3, kOutBF16),
@@ -100,6 +111,7 @@ const KernelEntry kKernels[] = {
     PATINA_KERNEL(2, 2, 224, 4, kE4M3, kOutBF16),
     PATINA_KERNEL(2, 1, 256, 6, kE4M3, kOutBF16),
     PATINA_KERNEL(1, 1, 256, 4, kE4M3, kOutBF16),
+    PATINA_KERNEL_KC(1, 128, 3, kE4M3, kOutBF16, 2),
     PATINA_KERNEL(1, 1, 128, 6, kE4M3, kOutBF16),
     // bf16 -> e4m3 (scaled, with amax): fused epilogue only, so both slots hold that kernel
     PATINA_KERNEL_Q(2, 1, 256, 6),
@@ -200,6 +212,10 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int64_t K, int n
   return 1.0e12 / (mainloop + fixed);
 }
 
+// Kernels with several k-blocks per stage view an operand as {128 bytes, rows, K / 128 bytes}:
+// K must be whole k-blocks (a ragged last k-block cannot be a box of that tensor).
+bool chunked_ok(int in_type, int64_t K) { return K % (int64_t)(kBlockKBytes / input_bytes(in_type)) == 0; }
+
 int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
               const PatinaGemmConfig* cfg, int num_sms, PatinaGemmPlan* out,
               const KernelEntry** entry_out, std::string* err, bool need_fused = false,
@@ -224,6 +240,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (c.block_n != 0 && k.block_n != c.block_n) continue;
       if (c.stages != 0 && k.stages != c.stages) continue;
       if (k.m_sub != (c.m_sub != 0 ? c.m_sub : 1)) continue;  // explicit requests default to m_sub = 1
+      if (k.k_chunks > 1 && !chunked_ok(in_type, K)) continue;
       if (need_fused && !k.fn_fused) continue;
       if (need_scatter && !k.fn_scatter) continue;
       best = &k;
@@ -241,6 +258,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (k.in_type != in_type || k.out_type != out_type) continue;
       if (c.stages != 0 && k.stages != c.stages) continue;
       if (k.cta_group == 2 && num_sms < 2) continue;
+      if (k.k_chunks > 1 && !chunked_ok(in_type, K)) continue;
       if (need_fused && !k.fn_fused) continue;
       if (need_scatter && !k.fn_scatter) continue;
       // (Peer destinations: store boxes with 128-byte rows cross NVLink at 0.84 of the plain copy
@@ -281,7 +299,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   p.tmem_cols = (2 * best->m_sub * best->block_n <= 512 ? 2 : 1) * best->m_sub * best->block_n;
   p.tmem_cols = p.tmem_cols <= 256 ? 256 : 512;  // allocation granularity: a power of two
   const SmemPlan sp = smem_plan(best->cta_group, best->m_sub, best->block_n, best->stages,
-                                output_bytes(out_type));
+                                output_bytes(out_type), 0, false, (uint32_t)best->k_chunks);
   p.stage_bytes = sp.stage_bytes;
   p.expect_tx_bytes = sp.stage_bytes * best->cta_group;
   p.idesc = idesc(in_type, 128 * best->cta_group, best->block_n);
@@ -394,7 +412,6 @@ struct PatinaGemmContext {
 #ifdef PATINA_TRACE
   unsigned long long* trace = nullptr;  // trace builds only: [grid][32] time stamps of the next launch
   uint32_t l2_hint_a = 0, l2_hint_b = 0;
-  uint32_t box_rows = 0;                // trace builds only: rows per operand TMA box (0 = whole slab)
   PatinaGemmConfig scatter_cfg{};       // trace builds only: tile override for the scatter entry
   bool has_scatter_cfg = false;
 #endif
@@ -459,6 +476,40 @@ int get_tensor_map(PatinaGemmContext* ctx, const void* ptr, CUtensorMapDataType 
   if (rc != CUDA_SUCCESS)
     return set_error(ctx, PATINA_GEMM_ERR_CUDA,
                      fmt("cuTensorMapEncodeTiled failed (CUresult %d) for %llux%llu ld=%llu", (int)rc,
+                         (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld));
+  if (ctx->tmaps.size() >= 64) ctx->tmaps.pop_back();
+  ctx->tmaps.insert(ctx->tmaps.begin(), std::make_pair(key, tm));
+  *out = tm;
+  return PATINA_GEMM_OK;
+}
+
+// The same matrix as a rank-3 tensor {128 bytes of K, rows, K / 128 bytes} (cols must be whole
+// 128-byte spans): a box {128 bytes, box_rows, chunks} lands in shared memory as `chunks`
+// consecutive [box_rows][128 bytes] slabs, each swizzled like a 2-D box of one k-block.
+int get_tensor_map_chunked(PatinaGemmContext* ctx, const void* ptr, CUtensorMapDataType dtype,
+                           uint32_t elt_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                           uint32_t box_rows, uint32_t chunks, CUtensorMap* out) {
+  const uint32_t span_elems = kBlockKBytes / elt_bytes;
+  TensorMapKey key{ptr, rows, cols, ld, box_rows, span_elems | (chunks << 16), (int)dtype};
+  for (size_t i = 0; i < ctx->tmaps.size(); ++i) {
+    if (ctx->tmaps[i].first == key) {
+      *out = ctx->tmaps[i].second;
+      return PATINA_GEMM_OK;
+    }
+  }
+  if (cols % span_elems != 0 || box_rows == 0 || box_rows > 256 || chunks == 0 || chunks > 8)
+    return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "internal: illegal 3-D TMA box");
+  const cuuint64_t gdim[3] = {span_elems, rows, cols / span_elems};
+  const cuuint64_t gstride[2] = {ld * elt_bytes, kBlockKBytes};
+  const cuuint32_t box[3] = {span_elems, box_rows, chunks};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  CUtensorMap tm;
+  CUresult rc = ctx->encode(&tm, dtype, 3, const_cast<void*>(ptr), gdim, gstride, box, estride,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return set_error(ctx, PATINA_GEMM_ERR_CUDA,
+                     fmt("cuTensorMapEncodeTiled (rank 3) failed (CUresult %d) for %llux%llu ld=%llu", (int)rc,
                          (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld));
   if (ctx->tmaps.size() >= 64) ctx->tmaps.pop_back();
   ctx->tmaps.insert(ctx->tmaps.begin(), std::make_pair(key, tm));
@@ -792,18 +843,21 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   const uint32_t kelems = kBlockKBytes / ib;
   CUtensorMap tm_a, tm_b;
   CStoreMaps<kMaxDests> tm_c;
-  // Rows per TMA box: the whole slab unless a smaller box divides it (see GemmParams::a_box_rows).
-  const uint32_t b_rows = (uint32_t)(k->block_n / k->cta_group);
-  uint32_t a_box = kCtaRows, b_box = b_rows;
-#ifdef PATINA_TRACE
-  if (ctx->box_rows && kCtaRows % ctx->box_rows == 0) a_box = ctx->box_rows;
-  if (ctx->box_rows && b_rows % ctx->box_rows == 0 && ctx->box_rows < b_rows) b_box = ctx->box_rows;
-#endif
-  rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
-                      a_box, kelems, &tm_a);
-  if (rc != PATINA_GEMM_OK) return rc;
-  rc = get_tensor_map(ctx, B, tmap_in_type(in_type), ib, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
-                      b_box, kelems, &tm_b);
+  // One TMA box per operand slab and stage: a 128-row slab of A, this CTA's rows of B.
+  const uint32_t a_box = kCtaRows, b_box = (uint32_t)(k->block_n / k->cta_group);
+  if (k->k_chunks > 1) {
+    rc = get_tensor_map_chunked(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
+                                a_box, (uint32_t)k->k_chunks, &tm_a);
+    if (rc != PATINA_GEMM_OK) return rc;
+    rc = get_tensor_map_chunked(ctx, B, tmap_in_type(in_type), ib, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
+                                b_box, (uint32_t)k->k_chunks, &tm_b);
+  } else {
+    rc = get_tensor_map(ctx, A, tmap_in_type(in_type), ib, (uint64_t)M, (uint64_t)K, (uint64_t)lda,
+                        a_box, kelems, &tm_a);
+    if (rc != PATINA_GEMM_OK) return rc;
+    rc = get_tensor_map(ctx, B, tmap_in_type(in_type), ib, (uint64_t)N, (uint64_t)K, (uint64_t)ldb,
+                        b_box, kelems, &tm_b);
+  }
   if (rc != PATINA_GEMM_OK) return rc;
   for (int d = 0; d <= n_extra; ++d) {
     rc = get_tensor_map(ctx, d == 0 ? C : extra_dests[d - 1],
@@ -854,8 +908,6 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     p.activation = (uint32_t)epi->activation;
   }
   p.n_dests = (uint32_t)(1 + n_extra);
-  p.a_box_rows = a_box;
-  p.b_box_rows = b_box;
   p.c_dests[0] = C;
   for (int d = 0; d < n_extra; ++d) p.c_dests[d + 1] = extra_dests[d];
   p.ldc = ldc;
@@ -1016,8 +1068,6 @@ int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sf
   p.n_dests = 1;
   p.c_dests[0] = C;
   p.ldc = ldc;
-  p.a_box_rows = kCtaRows;
-  p.b_box_rows = (uint32_t)(k->block_n / k->cta_group);
   p.sf_m_blocks = ceil_div(M, kSfAtomRows);
   p.sf_n_blocks = ceil_div(N, kSfAtomRows);
   p.sf_k_atoms = ceil_div(K, 128);
@@ -1152,8 +1202,6 @@ int launch_grouped(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.group_m = (cfg && cfg->group_m > 0) ? (uint32_t)cfg->group_m : 8u;
   p.alpha = alpha;
   p.n_dests = 1;
-  p.a_box_rows = kCtaRows;
-  p.b_box_rows = (uint32_t)(k->block_n / k->cta_group);
   p.group_rows = group_rows;
   p.group_alpha = group_alpha;
   p.n_groups = (uint32_t)n_groups;
@@ -1211,12 +1259,6 @@ int patina_gemm_debug_set_scatter_config(PatinaGemmContext* ctx, const PatinaGem
   if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
   ctx->has_scatter_cfg = cfg != nullptr;
   if (cfg) ctx->scatter_cfg = *cfg;
-  return PATINA_GEMM_OK;
-}
-// Trace builds only: fetch operand slabs as several TMA boxes of this many rows (0 = one box).
-int patina_gemm_debug_set_box_rows(PatinaGemmContext* ctx, uint32_t rows) {
-  if (!ctx) return PATINA_GEMM_ERR_INVALID_ARG;
-  ctx->box_rows = rows;
   return PATINA_GEMM_OK;
 }
 // Trace builds only: L2 eviction hints on the operand loads of pair kernels (0 none, 1 evict-first,

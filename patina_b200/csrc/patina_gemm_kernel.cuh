@@ -81,9 +81,6 @@ struct GemmParams {
   // block-scaled operands (kernels instantiated with kMXE4M3): extents of the scale buffers in
   // atoms of 128 rows x 128 K elements, so that tiles hanging over the edge read inside them
   uint32_t sf_m_blocks, sf_n_blocks, sf_k_atoms;
-  // rows per TMA box of A and of B (the tensor maps are encoded with these): a 128-row slab of A,
-  // or this CTA's rows of B, may be fetched as several smaller boxes
-  uint32_t a_box_rows, b_box_rows;
   uint32_t* status;        // [0] first error code, [1] block, [2] detail; 0 = ok
   uint64_t wait_limit_ns;  // bound for every barrier wait
 #ifdef PATINA_TRACE
@@ -204,7 +201,8 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
   }
 }
 
-template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFusedEpi = false>
+template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFusedEpi = false,
+          int kKChunks = 1>
 struct GemmTraits {
   static constexpr uint32_t kEpiWarps = 4 * kMSub;            // one warp per (sub-tile, lane quarter)
   // producer + MMA + epilogue warps (+ the scale-producer warp of block-scaled kernels)
@@ -214,9 +212,17 @@ struct GemmTraits {
   static constexpr uint32_t kUmmaPerStage = kBlockKElems / kUmmaK;  // 4
   static constexpr uint32_t kTileM = kCtaRows * kCtaGroup * kMSub;  // rows of one cluster tile
   static constexpr uint32_t kBRows = BN / kCtaGroup;                // B rows this CTA loads
-  static constexpr uint32_t kASubBytes = kCtaRows * kBlockKBytes;   // one 128-row slab of A
+  // A stage holds kKChunks consecutive 128-byte spans of K ("k-blocks"). With more than one, each
+  // operand slab of the stage is fetched by ONE 3-D TMA box {128 bytes, rows, kKChunks}, which lands
+  // as [chunk][row][128 bytes]: an issuing lane spends 150 - 400 cycles per box whatever its size
+  // (1024^3 on 128 x 256 tiles with one lane issuing: 9.9 us with one box per slab and k-block,
+  // 12.7 / 20.3 / 26.2 us with the same bytes cut into 2 / 4 / 8 boxes), so narrow tiles, whose
+  // k-block of MMAs is short, want few and large boxes.
+  static constexpr uint32_t kChunkABytes = kCtaRows * kBlockKBytes;  // one 128-row slab of A, one k-block
+  static constexpr uint32_t kChunkBBytes = kBRows * kBlockKBytes;
+  static constexpr uint32_t kASubBytes = kChunkABytes * kKChunks;    // one slab of A, one stage
   static constexpr uint32_t kABytes = kMSub * kASubBytes;
-  static constexpr uint32_t kBBytes = kBRows * kBlockKBytes;
+  static constexpr uint32_t kBBytes = kChunkBBytes * kKChunks;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kAccCols = kMSub * BN;                  // TMEM columns of one tile
   // Block-scaled operands: every stage also carries the scale atoms of its A slabs and of the
@@ -247,7 +253,8 @@ struct GemmTraits {
   static constexpr uint32_t kChunks = (BN + kChunkCols - 1) / kChunkCols;
   static constexpr bool kOverlapLastChunk = (BN % kChunkCols) != 0;
   static constexpr uint32_t kSmemBytes =
-      smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut), kSfStageBytes, kFusedEpi).total_bytes;
+      smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut), kSfStageBytes, kFusedEpi, kKChunks).total_bytes;
+  static_assert(kKChunks == 1 || (kCtaGroup == 1 && !is_block_scaled(kIn)), "multi-chunk stages: single-CTA kernels");
   static_assert(!kMx || BN % 64 == 0, "block-scaled tiles: B's scales must start an even number of TMEM columns into an atom");
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
@@ -261,17 +268,29 @@ struct GemmTraits {
 // The kernel body; the __global__ entries below differ only in their parameter lists (the
 // block-scaled one carries two more tensor maps, for the scales of A and B).
 template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused, bool kGrouped,
-          int kDests>
+          int kDests, int kKChunks = 1>
 __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                                              const CStoreMaps<kDests>& tm_c, const GemmParams& p,
                                              const CUtensorMap* tm_sfa, const CUtensorMap* tm_sfb) {
-  using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut, kFused>;
+  using T = GemmTraits<kCtaGroup, kMSub, BN, kStages, kIn, kOut, kFused, kKChunks>;
   constexpr bool kPair = (kCtaGroup == 2);
   constexpr bool kMx = T::kMx;
+  static_assert(kKChunks == 1 || !kGrouped, "multi-chunk stages: plain launches");
+  // stages of the K loop: kKChunks k-blocks each (the last may be partly past K: zero-filled, not multiplied)
+  const uint32_t k_steps = (p.k_blocks + (uint32_t)kKChunks - 1u) / (uint32_t)kKChunks;
   constexpr int kKind = (kIn == kE4M3) ? 1 : 0;
   static_assert(!kMx || (!kFused && !kGrouped && kDests == 1 && kOut == kOutBF16),
                 "block-scaled operands: plain bf16 epilogue only");
   constexpr uint32_t kEpiWarps = T::kEpiWarps;
+  // A stage is fetched by one TMA load per A slab and one for B, each issued by its own lane of
+  // the producer warp. What bounds a producer is not bytes but rounds: one lane's {wait for the
+  // slot, announce the bytes, issue} takes about 390 cycles and a further issue 150 - 200,
+  // whatever the box holds (8 to 32 KB measured alike), so a lane that issues a stage's two or
+  // three loads alone delivers a stage per 550 - 640 cycles -- slower than the MMAs of every
+  // tile narrower than 256 x 256 per pair. Lanes overlap: two lanes of one warp retire a load per
+  // 231 cycles, four per 148 (separate warps: 199 and 100); one SM takes in 120 bytes per clock
+  // when few SMs load and about 84 when 128 do.
+  constexpr uint32_t kLoadLanes = (uint32_t)kMSub + 1u;
   // The fused epilogue may read C itself as the residual, so no column may be produced twice.
   static_assert(!(kFused && T::kOverlapLastChunk), "fused epilogue needs whole store boxes");
   static_assert(!(kFused && kGrouped), "the grouped kernel has the plain epilogue only");
@@ -334,32 +353,33 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
     *abort_ptr = 0u;
     ptx::fence_mbar_init();
   }
-  // Single-CTA kernels: the producer lane (this same thread 0) issues the first pass through
+  // Single-CTA kernels: the producer lanes issue the first pass through
   // the ring right here, before TMEM allocation and the set-up barrier, so that those hide
   // behind the first loads' latency. Every stage is free, so no wait is needed. (A pair's loads
   // complete on the leader's barriers, which the partner may only use after the cluster-wide
   // barrier below; a grouped launch needs its tables first.)
   uint32_t pre_kb = 0;
   if constexpr (!kPair && !kGrouped && !kMx) {
-    if (threadIdx.x == 0 && cluster_id < p.num_tiles) {
-      ptx::fence_proxy_async_smem();
-      const TileCoord c0 = tile_coord(cluster_id, p.tiles_m, p.tiles_n, p.group_m);
-      const int32_t a_row = (int32_t)(c0.m * T::kTileM);
-      const int32_t b_row = (int32_t)(c0.n * BN);
-      const uint32_t n_pre = p.k_blocks < (uint32_t)kStages ? p.k_blocks : (uint32_t)kStages;
-      for (uint32_t kb = 0; kb < n_pre; ++kb) {
-        const uint32_t sa = ring + kb * T::kStageBytes;
-        const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
-        ptx::mbar_arrive_expect_tx(full_bar + 8u * kb, T::kStageBytes);
-#pragma unroll
-        for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-          for (uint32_t r = 0; r < kCtaRows; r += p.a_box_rows)
-            ptx::tma_load_2d(sa + ms * T::kASubBytes + r * kBlockKBytes, &tm_a, full_bar + 8u * kb, k0,
-                             a_row + (int32_t)(ms * kCtaRows + r));
-        for (uint32_t r = 0; r < T::kBRows; r += p.b_box_rows)
-          ptx::tma_load_2d(sa + T::kABytes + r * kBlockKBytes, &tm_b, full_bar + 8u * kb, k0, b_row + (int32_t)r);
+    if (warp_idx == 0) {
+      __syncwarp();  // the barriers thread 0 has just initialised, seen by the other issuing lanes
+      if (lane < kLoadLanes && cluster_id < p.num_tiles) {
+        ptx::fence_proxy_async_smem();
+        const TileCoord c0 = tile_coord(cluster_id, p.tiles_m, p.tiles_n, p.group_m);
+        const bool is_b = (lane == (uint32_t)kMSub);
+        const CUtensorMap* const tm = is_b ? &tm_b : &tm_a;
+        const int32_t row = is_b ? (int32_t)(c0.n * BN) : (int32_t)(c0.m * T::kTileM + lane * kCtaRows);
+        const uint32_t dst_off = is_b ? T::kABytes : lane * T::kASubBytes;
+        const uint32_t n_pre = k_steps < (uint32_t)kStages ? k_steps : (uint32_t)kStages;
+        for (uint32_t kb = 0; kb < n_pre; ++kb) {
+          const uint32_t dst = ring + kb * T::kStageBytes + dst_off;
+          if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * kb, T::kStageBytes);
+          if constexpr (kKChunks == 1)
+            ptx::tma_load_2d(dst, tm, full_bar + 8u * kb, (int32_t)(kb * T::kBlockKElems), row);
+          else
+            ptx::tma_load_3d(dst, tm, full_bar + 8u * kb, 0, row, (int32_t)(kb * kKChunks));
+        }
+        pre_kb = n_pre;
       }
-      pre_kb = n_pre;
     }
   }
   if constexpr (kGrouped) {
@@ -443,68 +463,54 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
 
   // ------------------------------------------------------------ TMA producer
   if (warp_idx == 0) {
-    if (lane == 0) {
+    if (lane < kLoadLanes) {
       // (pre_kb k-blocks of the first tile are already in flight: see the prologue)
       uint32_t s = pre_kb == (uint32_t)kStages ? 0u : pre_kb, ph = pre_kb == (uint32_t)kStages ? 1u : 0u;
       uint32_t kb_first = pre_kb;
       const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
+      const bool is_b = (lane == (uint32_t)kMSub);
+      const CUtensorMap* const tm = is_b ? &tm_b : &tm_a;
+      const uint32_t dst_off = is_b ? T::kABytes : lane * T::kASubBytes;
+#ifdef PATINA_TRACE
+      const uint32_t hint = is_b ? p.l2_hint_b : p.l2_hint_a;
+      const uint64_t policy = hint == 1 ? ptx::l2_policy_evict_first() : ptx::l2_policy_evict_last();
+#endif
       uint32_t grp = 0;
       for (uint32_t t = cluster_id; t < num_tiles; t += num_clusters) {
         const TileSpot c = locate(t, grp);
         // Sub-tile s of this CTA covers rows a_row + s * (128 * kCtaGroup). In a grouped launch
         // the last row block of a group also loads rows of the next group (or zeros past the
         // end): they only feed accumulator rows that are never stored.
-        const int32_t a_row = (int32_t)(c.row_base + c.m * T::kTileM + cta_rank * kCtaRows);
-        const int32_t b_row = (int32_t)(c.b_row_base + c.n * BN + cta_rank * T::kBRows);
+        const int32_t row = is_b ? (int32_t)(c.b_row_base + c.n * BN + cta_rank * T::kBRows)
+                                 : (int32_t)(c.row_base + c.m * T::kTileM + cta_rank * kCtaRows +
+                                             lane * (kCtaRows * kCtaGroup));
         const uint32_t n_sub = live_subtiles(c);
+        const bool live = is_b || lane < n_sub;
         // bytes this CTA loads per stage
         const uint32_t stage_tx = n_sub * T::kASubBytes + T::kBBytes + T::kSfStageBytes;
         // (block scales of a stage are loaded by the scale-producer warp, onto the same barrier)
         bool ok = true;
-        for (uint32_t kb = kb_first; kb < p.k_blocks; ++kb) {
+        for (uint32_t kb = kb_first; kb < k_steps; ++kb) {
           ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
           if (!ok) break;
-          if (t == cluster_id) PATINA_TRACE_KB(48u, kb);
-          const uint32_t sa = ring + s * T::kStageBytes;
-          const uint32_t sb = sa + T::kABytes;
+          if (lane == 0 && t == cluster_id) PATINA_TRACE_KB(48u, kb);
+          const uint32_t dst = ring + s * T::kStageBytes + dst_off;
           const int32_t k0 = (int32_t)(kb * T::kBlockKElems);
-          if constexpr (kPair) {
-            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, 2u * stage_tx);
+          // One arrival per stage (the leader's lane 0) announces the bytes of all lanes and both
+          // CTAs; a load that lands before it only drives the pending byte count negative.
+          if (lane == 0 && cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar + 8u * s, (uint32_t)kCtaGroup * stage_tx);
+          if (live) {
+            if constexpr (kPair) {
 #ifdef PATINA_TRACE
-            if (p.l2_hint_a | p.l2_hint_b) {
-              const uint64_t pol_first = ptx::l2_policy_evict_first(), pol_last = ptx::l2_policy_evict_last();
-              const uint64_t pa = p.l2_hint_a == 1 ? pol_first : pol_last, pb = p.l2_hint_b == 1 ? pol_first : pol_last;
-#pragma unroll
-              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
-                if (ms >= n_sub) continue;
-                const int32_t r = a_row + (int32_t)(ms * kCtaRows * kCtaGroup);
-                if (p.l2_hint_a) ptx::tma_load_2d_pair_hint(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0, r, pa);
-                else ptx::tma_load_2d_pair(sa + ms * T::kASubBytes, &tm_a, leader_full + 8u * s, k0, r);
-              }
-              if (p.l2_hint_b) ptx::tma_load_2d_pair_hint(sb, &tm_b, leader_full + 8u * s, k0, b_row, pb);
-              else ptx::tma_load_2d_pair(sb, &tm_b, leader_full + 8u * s, k0, b_row);
-            } else
+              if (hint) ptx::tma_load_2d_pair_hint(dst, tm, leader_full + 8u * s, k0, row, policy);
+              else
 #endif
-            {
-#pragma unroll
-            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-              if (ms < n_sub)
-                for (uint32_t r = 0; r < kCtaRows; r += p.a_box_rows)
-                  ptx::tma_load_2d_pair(sa + ms * T::kASubBytes + r * kBlockKBytes, &tm_a, leader_full + 8u * s, k0,
-                                        a_row + (int32_t)(ms * kCtaRows * kCtaGroup + r));
-            for (uint32_t r = 0; r < T::kBRows; r += p.b_box_rows)
-              ptx::tma_load_2d_pair(sb + r * kBlockKBytes, &tm_b, leader_full + 8u * s, k0, b_row + (int32_t)r);
+              ptx::tma_load_2d_pair(dst, tm, leader_full + 8u * s, k0, row);
+            } else if constexpr (kKChunks > 1) {
+              ptx::tma_load_3d(dst, tm, full_bar + 8u * s, 0, row, (int32_t)(kb * kKChunks));
+            } else {
+              ptx::tma_load_2d(dst, tm, full_bar + 8u * s, k0, row);
             }
-          } else {
-            ptx::mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
-#pragma unroll
-            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms)
-              if (ms < n_sub)
-                for (uint32_t r = 0; r < kCtaRows; r += p.a_box_rows)
-                  ptx::tma_load_2d(sa + ms * T::kASubBytes + r * kBlockKBytes, &tm_a, full_bar + 8u * s, k0,
-                                   a_row + (int32_t)(ms * kCtaRows * kCtaGroup + r));
-            for (uint32_t r = 0; r < T::kBRows; r += p.b_box_rows)
-              ptx::tma_load_2d(sb + r * kBlockKBytes, &tm_b, full_bar + 8u * s, k0, b_row + (int32_t)r);
           }
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
         }
@@ -533,7 +539,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * T::kAccCols;
-        for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+        for (uint32_t kb = 0; kb < k_steps; ++kb) {
           ok = bounded_wait<kPair>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
           ptx::tc_fence_after_sync();
@@ -553,20 +559,26 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
                                                      smem_desc(sfs + j * kSfAtomBytes, 0, 128, kSwizzleNone));
           }
 #pragma unroll
-          for (uint32_t k = 0; k < T::kUmmaPerStage; ++k) {
-            const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
+          for (uint32_t ch = 0; ch < (uint32_t)kKChunks; ++ch) {
+            // (a multi-chunk stage's chunks past K hold TMA's zero fill: skipped)
+            if (kKChunks > 1 && kb * (uint32_t)kKChunks + ch >= p.k_blocks) break;
+            const uint64_t db_c = db + (uint64_t)((ch * T::kChunkBBytes) >> 4);
 #pragma unroll
-            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
-              if (ms < n_sub) {
-                const uint64_t da = smem_desc_sw128_kmajor(sa + ms * T::kASubBytes);
-                if constexpr (kMx) {
-                  // the k-th 32-element block of this stage uses byte k of each scale column
-                  ptx::umma_mx<kCtaGroup>(tmem_d + ms * BN, da + adv, db + adv,
-                                          idesc_mx(kCtaRows * kCtaGroup, BN, k, k),
-                                          (tsfa0 + 4u * ms) | (k << 30), tsfb0 | (k << 30), (kb | k) != 0u);
-                } else {
-                  ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db + adv, idesc_v,
-                                              (kb | k) != 0u);
+            for (uint32_t k = 0; k < T::kUmmaPerStage; ++k) {
+              const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
+#pragma unroll
+              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
+                if (ms < n_sub) {
+                  const uint64_t da = smem_desc_sw128_kmajor(sa + ms * T::kASubBytes + ch * T::kChunkABytes);
+                  if constexpr (kMx) {
+                    // the k-th 32-element block of this stage uses byte k of each scale column
+                    ptx::umma_mx<kCtaGroup>(tmem_d + ms * BN, da + adv, db_c + adv,
+                                            idesc_mx(kCtaRows * kCtaGroup, BN, k, k),
+                                            (tsfa0 + 4u * ms) | (k << 30), tsfb0 | (k << 30), (kb | k) != 0u);
+                  } else {
+                    ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db_c + adv, idesc_v,
+                                                (kb | ch | k) != 0u);
+                  }
                 }
               }
             }
@@ -601,41 +613,29 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
   // that are never stored.
   else if (kMx && warp_idx == 2u + kEpiWarps) {
     if constexpr (kMx) {
-      if (lane == 0) {
+      if (lane < T::kSfAtoms) {   // one lane per scale atom of a stage (lanes overlap their issue latency)
         uint32_t s = 0, ph = 0, grp = 0;
         const uint32_t leader_full = kPair ? ptx::mapa(full_bar, 0) : full_bar;
+        const bool is_b = lane >= (uint32_t)kMSub;
+        const CUtensorMap* const tm = is_b ? tm_sfb : tm_sfa;
         for (uint32_t t = cluster_id; t < num_tiles; t += num_clusters) {
           const TileSpot c = locate(t, grp);
-          const uint32_t a_row = c.row_base + c.m * T::kTileM + cta_rank * kCtaRows;
-          uint32_t sfa_atom[kMSub], sfb_atom[T::kSfbAtoms > 0 ? T::kSfbAtoms : 1];
-#pragma unroll
-          for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
-            uint32_t mb = (a_row + ms * kCtaRows * kCtaGroup) / kSfAtomRows;
-            mb = mb < p.sf_m_blocks ? mb : p.sf_m_blocks - 1u;
-            sfa_atom[ms] = mb * p.sf_k_atoms;
+          uint32_t blk, last;
+          if (is_b) {
+            blk = (c.n * BN) / kSfAtomRows + (lane - (uint32_t)kMSub);
+            last = p.sf_n_blocks - 1u;
+          } else {
+            blk = (c.row_base + c.m * T::kTileM + cta_rank * kCtaRows + lane * kCtaRows * kCtaGroup) / kSfAtomRows;
+            last = p.sf_m_blocks - 1u;
           }
-#pragma unroll
-          for (uint32_t a = 0; a < T::kSfbAtoms; ++a) {
-            uint32_t nb = (c.n * BN) / kSfAtomRows + a;
-            nb = nb < p.sf_n_blocks ? nb : p.sf_n_blocks - 1u;
-            sfb_atom[a] = nb * p.sf_k_atoms;
-          }
+          const uint32_t atom0 = (blk < last ? blk : last) * p.sf_k_atoms;
           bool ok = true;
           for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
             ok = bounded_wait<kPair>(empty_bar + 8u * s, ph ^ 1u, w, kTimeoutProducerEmpty, t);
             if (!ok) break;
-            const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
-            const uint32_t bar = (kPair ? leader_full : full_bar) + 8u * s;
-#pragma unroll
-            for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
-              if constexpr (kPair) ptx::tma_load_2d_pair(sfs + ms * kSfAtomBytes, tm_sfa, bar, 0, (int32_t)(sfa_atom[ms] + kb));
-              else ptx::tma_load_2d(sfs + ms * kSfAtomBytes, tm_sfa, bar, 0, (int32_t)(sfa_atom[ms] + kb));
-            }
-#pragma unroll
-            for (uint32_t a = 0; a < T::kSfbAtoms; ++a) {
-              if constexpr (kPair) ptx::tma_load_2d_pair(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, bar, 0, (int32_t)(sfb_atom[a] + kb));
-              else ptx::tma_load_2d(sfs + (kMSub + a) * kSfAtomBytes, tm_sfb, bar, 0, (int32_t)(sfb_atom[a] + kb));
-            }
+            const uint32_t dst = sf_ring + s * T::kSfStageBytes + lane * kSfAtomBytes;
+            if constexpr (kPair) ptx::tma_load_2d_pair(dst, tm, leader_full + 8u * s, 0, (int32_t)(atom0 + kb));
+            else ptx::tma_load_2d(dst, tm, full_bar + 8u * s, 0, (int32_t)(atom0 + kb));
             if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
           }
           if (!ok) break;
@@ -954,6 +954,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                const __grid_constant__ CStoreMaps<kDests> tm_c, const GemmParams p) {
   gemm_tn_body<kCtaGroup, kMSub, BN, kStages, kIn, kOut, kFused, kGrouped, kDests>(tm_a, tm_b, tm_c, p,
                                                                                    nullptr, nullptr);
+}
+
+// Single-CTA kernel whose stages hold kKChunks k-blocks, each operand slab of a stage fetched by
+// one 3-D box (tensor maps of rank 3: {128 bytes of K, rows, K / 128 bytes}); plain epilogue.
+template <int kMSub, int BN, int kStages, int kIn, int kOut, int kKChunks>
+__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
+gemm_tn_chunked_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                       const __grid_constant__ CStoreMaps<1> tm_c, const GemmParams p) {
+  gemm_tn_body<1, kMSub, BN, kStages, kIn, kOut, false, false, 1, kKChunks>(tm_a, tm_b, tm_c, p, nullptr, nullptr);
 }
 
 // Block-scaled operands (e4m3 elements, one E8M0 scale per 32 K elements of a row): the same

@@ -60,11 +60,11 @@ def shape_from_plan(plan, name: str = "patina_b200_gemm") -> KernelShape:
     """From a `PatinaGemmPlan` (see `lib.plan`) of a single-CTA, one-sub-tile configuration."""
     if plan.cta_group != 1 or plan.m_sub != 1:
         raise ValueError("the dialect (version 0.1) describes one CTA with one 128-row accumulator")
-    a_bytes = 128 * 128
-    b_bytes = plan.stage_bytes - a_bytes
-    if b_bytes != plan.block_n * 128:
+    # a stage holds one or more 128-byte spans of K for 128 rows of A and block_n rows of B
+    spans, rest = divmod(plan.stage_bytes, (128 + plan.block_n) * 128)
+    if rest or spans < 1:
         raise ValueError("unexpected stage layout")
-    return KernelShape(name=name, block_n=plan.block_n, block_k=64, stages=plan.stages,
+    return KernelShape(name=name, block_n=plan.block_n, block_k=64 * spans, stages=plan.stages,
                        tmem_cols=plan.tmem_cols)
 
 

@@ -21,7 +21,8 @@ def test_every_single_cta_plan_prints_and_verifies(built_lib):
         # the printed stage bytes are the kernel's own expect_tx count
         assert f"expect_tx_stage %pipe, full, %s, {plan.expect_tx_bytes}" in text
         assert f"stages = {plan.stages}" in text and "block = 192" in text
-        assert text.count("patina.umma.step") == 4          # four K16 steps per 128-byte stage
+        # four K16 steps per 128-byte span of K in a stage
+        assert text.count("patina.umma.step") == 4 * plan.stage_bytes // ((128 + block_n) * 128)
     pair = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192)
     with pytest.raises(ValueError):
         dt.shape_from_plan(pair)                             # CTA pairs cannot be spelled in version 0.1

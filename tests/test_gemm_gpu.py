@@ -58,7 +58,10 @@ def cfgs():
             "pair_2sub_n240": GemmConfig(2, 240, 0, 0, 0, 2), "pair_2sub_n208": GemmConfig(2, 208, 0, 0, 0, 2),
             "pair_2sub_n176": GemmConfig(2, 176, 0, 0, 0, 2),
             # narrow tiles for problems with few tiles
-            "pair_n64": GemmConfig(2, 64, 0, 0, 0), "1cta_n64": GemmConfig(1, 64, 0, 0, 0)}
+            "pair_n64": GemmConfig(2, 64, 0, 0, 0), "1cta_n64": GemmConfig(1, 64, 0, 0, 0),
+            # (1cta_n128 / 1cta_n64 take the kernels with two k-blocks per stage when K is whole
+            # k-blocks; these name the one-k-block kernels by their stage counts)
+            "1cta_n128_6stages": GemmConfig(1, 128, 6, 0, 0), "1cta_n64_8stages": GemmConfig(1, 64, 8, 0, 0)}
 
 
 # ------------------------------------------------------------ reference shape
@@ -129,6 +132,45 @@ def test_bf16_1024_cubed_all_configs(ctx, oracle_mod):
     # configurations agree with each other far inside the tolerance
     for name, out in outs.items():
         check_norm(oracle_mod, out, outs["auto"].float().cpu().numpy(), f"{name} vs auto")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 136, 192), (1024, 1024, 1088), (520, 1000, 4096),
+                                   (2048, 264, 960)])
+def test_two_k_blocks_per_stage_kernels(ctx, oracle_mod, M, N, K):
+    """The single-CTA kernels whose stages hold two k-blocks fetched as one 3-D box per operand
+    (128 x 128 tiles with 3 stages, 128 x 64 with 4): odd and even counts of k-blocks (an odd
+    count leaves the last stage half zero-filled and half multiplied), ragged M and N. They add
+    the same products in the same order as the one-k-block kernels: equal bit for bit."""
+    from patina_b200 import inputs, GemmConfig, lib as L
+    assert K % 64 == 0
+    A, B = inputs.make_operands("llm", M, N, K, seed=M + N + K)
+    want = expect_bf16(oracle_mod, A, B, alpha=0.75)
+    dA, dB = A.cuda(), B.cuda()
+    for block_n, two, one in ((128, 3, 6), (64, 4, 8)):
+        plan = L.plan(L.IN_BF16, L.OUT_BF16, M, N, K, GemmConfig(1, block_n, two, 0, 0))
+        assert plan.stages == two and plan.stage_bytes == 2 * (128 + block_n) * 128
+        assert L.plan(L.IN_BF16, L.OUT_BF16, M, N, K, GemmConfig(1, block_n, 0, 0, 0)).stages == two
+        ldc = (N + 7) // 8 * 8 + 8
+        full = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ctx.gemm_tn(dA, dB, out=full[:, :N], alpha=0.75, config=GemmConfig(1, block_n, two, 0, 0))
+        ctx.status()
+        check_norm(oracle_mod, full[:, :N], want, f"128 x {block_n}, two k-blocks per stage, {M}x{N}x{K}")
+        assert bool(torch.isnan(full[:, N:]).all())
+        ref = ctx.gemm_tn(dA, dB, alpha=0.75, config=GemmConfig(1, block_n, one, 0, 0))
+        ctx.status()
+        assert torch.equal(full[:, :N], ref)
+
+
+def test_two_k_blocks_per_stage_needs_whole_k_blocks(ctx):
+    """K = 72 is not whole 64-element k-blocks: the 3-D operand view does not exist, the library's
+    own choice falls back to the one-k-block kernel and an explicit request is refused."""
+    from patina_b200 import GemmConfig, PatinaGemmError, lib as L
+    assert L.plan(L.IN_BF16, L.OUT_BF16, 256, 256, 72, GemmConfig(1, 128, 0, 0, 0)).stages == 6
+    A = torch.zeros((256, 72), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(PatinaGemmError):
+        ctx.gemm_tn(A, A, config=GemmConfig(1, 128, 3, 0, 0))
+    ctx.gemm_tn(A, A, config=GemmConfig(1, 128, 0, 0, 0))
+    ctx.status()
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 8, 8), (16, 24, 40), (128, 128, 64), (129, 257, 72), (1000, 776, 520),
@@ -216,7 +258,7 @@ def test_fp8_e4m3(ctx, oracle_mod, M, N, K):
     check_norm(oracle_mod, out, want, "fp8 auto")
     for name, cfg in cfgs().items():
         if name in ("pair_n128", "pair_2sub_n128", "pair_2sub_n192", "pair_2sub_n160", "pair_2sub_n208",
-                    "pair_2sub_n176", "pair_n64", "1cta_n64"):
+                    "pair_2sub_n176", "pair_n64", "1cta_n64", "1cta_n64_8stages"):
             continue  # no such fp8 kernels
         out = ctx.gemm_tn(Aq.cuda(), Bq.cuda(), alpha=sa * sb, config=cfg)
         ctx.status()

@@ -212,6 +212,13 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int64_t K, int n
   return 1.0e12 / (mainloop + fixed);
 }
 
+// Threads of a block: producer and MMA warps, four epilogue warps per accumulator sub-tile, a
+// second MMA-issuing warp when there are two sub-tiles, a scale-producer warp when block-scaled
+// (GemmTraits::kThreads).
+uint32_t block_threads(int m_sub, bool block_scaled) {
+  return 64u + 128u * (uint32_t)m_sub + (m_sub == 2 ? 32u : 0u) + (block_scaled ? 32u : 0u);
+}
+
 // Kernels with several k-blocks per stage view an operand as {128 bytes, rows, K / 128 bytes}:
 // K must be whole k-blocks (a ragged last k-block cannot be a box of that tensor).
 bool chunked_ok(int in_type, int64_t K) { return K % (int64_t)(kBlockKBytes / input_bytes(in_type)) == 0; }
@@ -293,7 +300,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   if (slots == 0) slots = 1;
   const uint32_t clusters = p.num_tiles < slots ? p.num_tiles : slots;
   p.grid = clusters * best->cta_group;
-  p.block = 64 + 128 * best->m_sub;
+  p.block = block_threads(best->m_sub, false);
   p.cluster = best->cta_group;
   p.smem_bytes = best->smem_bytes;
   p.tmem_cols = (2 * best->m_sub * best->block_n <= 512 ? 2 : 1) * best->m_sub * best->block_n;
@@ -770,7 +777,7 @@ int resident_clusters(const KernelEntry* k, int num_sms, int* cache) {
   if (*cache != 0) return *cache;
   cudaLaunchConfig_t qc{};
   qc.gridDim = dim3((unsigned)(num_sms / k->cta_group) * k->cta_group, 1, 1);
-  qc.blockDim = dim3(64 + 128 * k->m_sub + (k->in_type == kMXE4M3 ? 32 : 0), 1, 1);
+  qc.blockDim = dim3(block_threads(k->m_sub, k->in_type == kMXE4M3), 1, 1);
   qc.dynamicSmemBytes = k->smem_bytes;
   cudaLaunchAttribute qa[1];
   qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -1091,7 +1098,7 @@ int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sf
 
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3(clusters * k->cta_group, 1, 1);
-  lc.blockDim = dim3(64 + 128 * k->m_sub + 32, 1, 1);   // + the scale-producer warp
+  lc.blockDim = dim3(block_threads(k->m_sub, true), 1, 1);
   lc.dynamicSmemBytes = k->smem_bytes;
   lc.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1212,7 +1219,7 @@ int launch_grouped(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
 
   cudaLaunchConfig_t lc{};
   lc.gridDim = dim3(clusters * k->cta_group, 1, 1);
-  lc.blockDim = dim3(64 + 128 * k->m_sub, 1, 1);
+  lc.blockDim = dim3(block_threads(k->m_sub, false), 1, 1);
   lc.dynamicSmemBytes = k->smem_bytes;
   lc.stream = stream;
   cudaLaunchAttribute attr[1];

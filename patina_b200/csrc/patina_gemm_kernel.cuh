@@ -206,7 +206,10 @@ template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool
 struct GemmTraits {
   static constexpr uint32_t kEpiWarps = 4 * kMSub;            // one warp per (sub-tile, lane quarter)
   // producer + MMA + epilogue warps (+ the scale-producer warp of block-scaled kernels)
-  static constexpr uint32_t kThreads = 64 + 32 * kEpiWarps + (is_block_scaled(kIn) ? 32u : 0u);
+  // (+ a second MMA-issuing warp when there are two accumulator sub-tiles)
+  static constexpr uint32_t kThreads =
+      64 + 32 * kEpiWarps + (is_block_scaled(kIn) ? 32u : 0u) + (kMSub == 2 ? 32u : 0u);
+  static constexpr uint32_t kSecondIssuerWarp = 2 + kEpiWarps + (is_block_scaled(kIn) ? 1u : 0u);
   static constexpr uint32_t kBlockKElems = kBlockKBytes / input_bytes(kIn);
   static constexpr uint32_t kUmmaK = umma_k(kIn);
   static constexpr uint32_t kUmmaPerStage = kBlockKElems / kUmmaK;  // 4
@@ -233,10 +236,10 @@ struct GemmTraits {
   static constexpr uint32_t kSfAtoms = kMx ? (kMSub + kSfbAtoms) : 0u;
   static constexpr uint32_t kSfStageBytes = kSfAtoms * kSfAtomBytes;
   static constexpr uint32_t kSfCols = 4u * kSfAtoms;
-  // (Two copies of the scale columns used by alternate k-blocks, so that the next k-block's copy
-  // need not wait for the MMAs still reading this one's, were measured: no gain, 459 vs 457 us at
-  // 8192^3. One copy.)
-  static constexpr uint32_t kSfCopies = 1;
+  // One set of scale columns per MMA-issuing lane (one lane per sub-tile: each copies what its
+  // own MMAs read). (A second set for alternate k-blocks, so that the next k-block's copy need
+  // not wait for the MMAs still reading this one's, was measured: no gain.)
+  static constexpr uint32_t kSfCopies = kMSub;
   static constexpr uint32_t kAccBufs = (2 * kAccCols + kSfCopies * kSfCols <= 512) ? 2 : 1;
   static constexpr uint32_t kSfCol0 = kAccBufs * kAccCols;          // first scale column
   static constexpr uint32_t kTmemUsed = kAccBufs * kAccCols + kSfCopies * kSfCols;
@@ -291,6 +294,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
   // 231 cycles, four per 148 (separate warps: 199 and 100); one SM takes in 120 bytes per clock
   // when few SMs load and about 84 when 128 do.
   constexpr uint32_t kLoadLanes = (uint32_t)kMSub + 1u;
+  constexpr uint32_t kIssuers = (uint32_t)kMSub;   // MMA-issuing threads: one per accumulator sub-tile
   // The fused epilogue may read C itself as the residual, so no column may be produced twice.
   static_assert(!(kFused && T::kOverlapLastChunk), "fused epilogue needs whole store boxes");
   static_assert(!(kFused && kGrouped), "the grouped kernel has the plain epilogue only");
@@ -344,10 +348,10 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
     }
     for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
       ptx::mbar_init(full_bar + 8u * s, 1);
-      ptx::mbar_init(empty_bar + 8u * s, 1);
+      ptx::mbar_init(empty_bar + 8u * s, kIssuers);
     }
     for (uint32_t b = 0; b < 2; ++b) {
-      ptx::mbar_init(tfull_bar + 8u * b, 1);
+      ptx::mbar_init(tfull_bar + 8u * b, kIssuers);
       ptx::mbar_init(tempty_bar + 8u * b, kEpiWarps * kCtaGroup);
     }
     *abort_ptr = 0u;
@@ -520,77 +524,82 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
     }
   }
   // -------------------------------------------------------------- MMA issuer
-  else if (warp_idx == 1) {
+  // One warp (its lane 0) of the leader CTA per accumulator sub-tile: a thread issues one tcgen05 instruction
+  // (mma, cp, commit) per 71 - 85 cycles, however short the instruction's work -- measured back to
+  // back: 128 x 64 x 16 and 128 x 128 x 16 MMAs both retire one per 85 cycles from one thread, one
+  // per 48 and 64 from two -- so a k-block of a two-sub-tile kernel (8 MMAs, 2 commits, a wait, and
+  // 4 scale copies when block-scaled) is 11 to 16 issue slots against 768 - 1024 cycles of
+  // tensor-pipe work. The sub-tiles' MMAs are independent, so each issuer multiplies its own
+  // sub-tile (every accumulator sees the same MMAs in the same order whoever issues them), copies
+  // the scales it needs into its own TMEM columns (tcgen05.cp is ordered before the MMAs of the
+  // same thread only) and commits for itself: the `empty` and `tmem full` barriers count
+  // kIssuers arrivals. Warp 1 takes sub-tile 0, the last warp of the block sub-tile 1.
+  else if (warp_idx == 1 || (kMSub == 2 && warp_idx == T::kSecondIssuerWarp)) {
     if (lane == 0 && cta_rank == 0) {
+      const uint32_t my = (warp_idx == 1) ? 0u : 1u;  // the accumulator sub-tile this thread multiplies
       const uint32_t idesc_v = idesc(kIn, kCtaRows * kCtaGroup, BN);
-      const uint32_t peer_empty = kPair ? ptx::mapa(empty_bar, 1) : 0u;
-      const uint32_t peer_tfull = kPair ? ptx::mapa(tfull_bar, 1) : 0u;
       uint32_t s = 0, ph = 0, it = 0, grp = 0;
       bool ok = true;
       for (uint32_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
         const TileSpot c = locate(t, grp);
-        const uint32_t n_sub = live_subtiles(c);
+        const bool live = my < live_subtiles(c);
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
-        // block scales in TMEM: A's slabs first, then B's atoms; the tile's first row of B may
-        // lie 64 rows into its first atom, i.e. 2 columns in (widths are multiples of 64)
-        const uint32_t tsf_base = tmem_base + T::kSfCol0;
-        const uint32_t sfb_off = 4u * (uint32_t)kMSub + ((c.n * BN) % kSfAtomRows) / 32u;
+        // block scales in TMEM, one set of columns per issuer: A's slabs first, then B's
+        // atoms; the tile's first row of B may lie 64 rows into its first atom, i.e. 2 columns in
+        // (widths are multiples of 64)
+        const uint32_t tsfa0 = tmem_base + T::kSfCol0 + my * T::kSfCols;
+        const uint32_t tsfb0 = tsfa0 + 4u * (uint32_t)kMSub + ((c.n * BN) % kSfAtomRows) / 32u;
         ok = bounded_wait<kPair>(tempty_bar + 8u * buf, acc_ph ^ 1u, w, kTimeoutMmaTmemEmpty, t);
         if (!ok) break;
         ptx::tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + buf * T::kAccCols;
+        const uint32_t tmem_d = tmem_base + buf * T::kAccCols + my * BN;
         for (uint32_t kb = 0; kb < k_steps; ++kb) {
           ok = bounded_wait<kPair>(full_bar + 8u * s, ph, w, kTimeoutMmaFull, t);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          if (it == 0 && kb == 0) PATINA_TRACE_AT(2);
-          if (it == 0) PATINA_TRACE_KB(32u, kb);
+          if (my == 0 && it == 0 && kb == 0) PATINA_TRACE_AT(2);
+          if (my == 0 && it == 0) PATINA_TRACE_KB(32u, kb);
           const uint32_t sa = ring + s * T::kStageBytes;
           const uint64_t db = smem_desc_sw128_kmajor(sa + T::kABytes);
-          const uint32_t tsfa0 = tsf_base + (kb % T::kSfCopies) * T::kSfCols;   // this k-block's copy of the scale columns
-          const uint32_t tsfb0 = tsfa0 + sfb_off;
           if constexpr (kMx) {
             // this k-block's scales: shared memory -> TMEM, 32 lines of 16 bytes per atom (8-line
-            // groups 128 bytes apart, no swizzle)
+            // groups 128 bytes apart, no swizzle): this lane's slab of A and all atoms of B
             const uint32_t sfs = sf_ring + s * T::kSfStageBytes;
 #pragma unroll
             for (uint32_t j = 0; j < T::kSfAtoms; ++j)
-              ptx::tmem_cp_32x128b_warpx4<kCtaGroup>(tsfa0 + 4u * j,
-                                                     smem_desc(sfs + j * kSfAtomBytes, 0, 128, kSwizzleNone));
+              if (live && (j == my || j >= (uint32_t)kMSub))
+                ptx::tmem_cp_32x128b_warpx4<kCtaGroup>(tsfa0 + 4u * j,
+                                                       smem_desc(sfs + j * kSfAtomBytes, 0, 128, kSwizzleNone));
           }
 #pragma unroll
           for (uint32_t ch = 0; ch < (uint32_t)kKChunks; ++ch) {
             // (a multi-chunk stage's chunks past K hold TMA's zero fill: skipped)
             if (kKChunks > 1 && kb * (uint32_t)kKChunks + ch >= p.k_blocks) break;
             const uint64_t db_c = db + (uint64_t)((ch * T::kChunkBBytes) >> 4);
+            const uint64_t da = smem_desc_sw128_kmajor(sa + my * T::kASubBytes + ch * T::kChunkABytes);
 #pragma unroll
             for (uint32_t k = 0; k < T::kUmmaPerStage; ++k) {
               const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
-#pragma unroll
-              for (uint32_t ms = 0; ms < (uint32_t)kMSub; ++ms) {
-                if (ms < n_sub) {
-                  const uint64_t da = smem_desc_sw128_kmajor(sa + ms * T::kASubBytes + ch * T::kChunkABytes);
-                  if constexpr (kMx) {
-                    // the k-th 32-element block of this stage uses byte k of each scale column
-                    ptx::umma_mx<kCtaGroup>(tmem_d + ms * BN, da + adv, db_c + adv,
-                                            idesc_mx(kCtaRows * kCtaGroup, BN, k, k),
-                                            (tsfa0 + 4u * ms) | (k << 30), tsfb0 | (k << 30), (kb | k) != 0u);
-                  } else {
-                    ptx::umma<kCtaGroup, kKind>(tmem_d + ms * BN, da + adv, db_c + adv, idesc_v,
-                                                (kb | ch | k) != 0u);
-                  }
+              if (live) {
+                if constexpr (kMx) {
+                  // the k-th 32-element block of this stage uses byte k of each scale column
+                  ptx::umma_mx<kCtaGroup>(tmem_d, da + adv, db_c + adv, idesc_mx(kCtaRows * kCtaGroup, BN, k, k),
+                                          (tsfa0 + 4u * my) | (k << 30), tsfb0 | (k << 30), (kb | k) != 0u);
+                } else {
+                  ptx::umma<kCtaGroup, kKind>(tmem_d, da + adv, db_c + adv, idesc_v, (kb | ch | k) != 0u);
                 }
               }
             }
           }
-          ptx::umma_commit<kCtaGroup>(empty_bar + 8u * s);
-          if constexpr (kPair) ptx::umma_commit<kCtaGroup>(peer_empty + 8u * s);
+          // (a lane without MMAs in this stage arrives at once)
+          if constexpr (kPair) ptx::umma_commit_pair(empty_bar + 8u * s);   // both CTAs' slots
+          else ptx::umma_commit<kCtaGroup>(empty_bar + 8u * s);
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
-        ptx::umma_commit<kCtaGroup>(tfull_bar + 8u * buf);
-        if constexpr (kPair) ptx::umma_commit<kCtaGroup>(peer_tfull + 8u * buf);
-        PATINA_TRACE_AT(3);  // (overwritten per tile: the last tile's stamp stays)
+        if constexpr (kPair) ptx::umma_commit_pair(tfull_bar + 8u * buf);
+        else ptx::umma_commit<kCtaGroup>(tfull_bar + 8u * buf);
+        if (my == 0) PATINA_TRACE_AT(3);  // (overwritten per tile: the last tile's stamp stays)
       }
       // Every MMA must have retired before shared memory or TMEM is released:
       // wait for the last accumulator's completion here as well.
@@ -949,7 +958,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
 
 template <int kCtaGroup, int kMSub, int BN, int kStages, int kIn, int kOut, bool kFused = false,
           bool kGrouped = false, int kDests = 1>
-__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
+__global__ void __launch_bounds__(64 + 128 * kMSub + (kMSub == 2 ? 32 : 0), 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CStoreMaps<kDests> tm_c, const GemmParams p) {
   gemm_tn_body<kCtaGroup, kMSub, BN, kStages, kIn, kOut, kFused, kGrouped, kDests>(tm_a, tm_b, tm_c, p,
@@ -968,7 +977,7 @@ gemm_tn_chunked_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
 // Block-scaled operands (e4m3 elements, one E8M0 scale per 32 K elements of a row): the same
 // kernel with the scale buffers of A and B as two more tensor maps.
 template <int kCtaGroup, int kMSub, int BN, int kStages>
-__global__ void __launch_bounds__(64 + 128 * kMSub + 32, 1)   // + the scale-producer warp
+__global__ void __launch_bounds__(64 + 128 * kMSub + 32 + (kMSub == 2 ? 32 : 0), 1)   // + the scale-producer warp
 gemm_mx_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CStoreMaps<1> tm_c, const __grid_constant__ CUtensorMap tm_sfa,
                   const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {

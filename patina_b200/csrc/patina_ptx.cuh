@@ -328,7 +328,7 @@ __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t 
 
 // One arrival on `cluster_bar` (a shared::cluster address: this CTA's or its
 // pair partner's) once every tcgen05 operation this thread issued so far has
-// completed. Plain (non-multicast) form; a pair is signalled with two calls.
+// completed. Plain form: one barrier.
 template <int kCtaGroup>
 __device__ __forceinline__ void umma_commit(uint32_t cluster_bar) {
   if constexpr (kCtaGroup == 1)
@@ -341,6 +341,14 @@ __device__ __forceinline__ void umma_commit(uint32_t cluster_bar) {
         "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
             cluster_bar)
         : "memory");
+}
+
+// The same arrival on the barrier at this offset in BOTH CTAs of a pair, with one instruction
+// (a commit is one of the issuing thread's tcgen05 issue slots, like an MMA). `bar` is the
+// executing CTA's own barrier address.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(both) : "memory");
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives row

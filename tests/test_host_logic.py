@@ -67,7 +67,7 @@ def test_plan_headline_shape():
     p = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192)
     assert (p.cta_group, p.m_sub, p.block_n, p.cluster, p.tile_m) == (2, 2, 256, 2, 512)
     assert (p.tiles_m, p.tiles_n, p.num_tiles, p.k_blocks) == (16, 32, 512, 128)
-    assert p.grid == 148 and p.block == 320 and p.tmem_cols == 512
+    assert p.grid == 148 and p.block == 352 and p.tmem_cols == 512
     assert p.smem_bytes <= 232448
     # bytes the full barrier expects == bytes of the TMA boxes that land on it
     # (the invariant the reference's verifier enforces, mlir/lib/PatinaOps.cpp:587-614):
@@ -96,7 +96,7 @@ def test_plan_variants():
     with pytest.raises(ValueError):
         L.plan(L.IN_F16, L.OUT_F32, 128, 128, 128, L.GemmConfig(2, 256, 0, 0, 0, 2))  # no such f16 kernel
     p = L.plan(L.IN_BF16, L.OUT_BF16, 4096, 4096, 4096, L.GemmConfig(2, 128, 0, 0, 0, 2))
-    assert (p.tile_m, p.tmem_cols, p.block) == (512, 512, 320)
+    assert (p.tile_m, p.tmem_cols, p.block) == (512, 512, 352)
 
 
 def test_planner_picks_match_what_was_measured_fastest():

@@ -71,6 +71,7 @@ pub struct PatinaGemmPlan {
     pub stage_bytes: u32,
     pub expect_tx_bytes: u32,
     pub idesc: u32,
+    pub half_tiles: u32,
 }
 
 #[repr(C)]

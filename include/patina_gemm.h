@@ -76,6 +76,9 @@ typedef struct PatinaGemmPlan {
   uint32_t grid, block, cluster, smem_bytes, tmem_cols;
   uint32_t stage_bytes, expect_tx_bytes;
   uint32_t idesc;
+  uint32_t half_tiles; /* tiles of the last wave run as two half tiles each (m_sub = 2 kernels, when
+                          that wave fills at most half of the clusters): the persistent CTAs walk
+                          num_tiles + half_tiles scheduler indices */
 } PatinaGemmPlan;
 
 /* ---- context (replaces run.rs `Cuda::init` / `Drop`, run.rs:256-394) ----- */

@@ -172,6 +172,15 @@ bool type_pair_supported(int in_type, int out_type) {
 // ------------------------------------------------------------------ planning
 uint32_t ceil_div(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
 
+// Tiles of the last wave that a two-sub-tile kernel runs as two half tiles each (see
+// GemmParams::split_from): all of them when they fill at most half of the clusters -- the wave
+// then takes half as long -- none otherwise (two half waves cost what one wave costs).
+uint32_t half_tile_tail(uint32_t num_tiles, uint32_t clusters, int m_sub) {
+  if (m_sub != 2 || clusters == 0) return 0;
+  const uint32_t tail = num_tiles % clusters;
+  return (tail > 0 && 2u * tail <= clusters) ? tail : 0u;
+}
+
 // Useful work per unit of modelled time, as a fraction of what the 512 x 256 pair tile does on
 // exactly filled waves. Two measured facts go in:
 //  * the throughput of each tile shape on filled waves (M = 8192, K = 4096, 37 tile columns):
@@ -202,7 +211,15 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int64_t K, int n
   // 0.45 us on a lone CTA, a 256 x 256 tile's 0.41 us on a pair).
   const double k_blocks = (double)ceil_div(K, kBlockKBytes / input_bytes(k.in_type));
   const double per_sm_tile = (double)tile_m * (double)k.block_n / (speed * (double)k.cta_group);
-  const double mainloop = per_sm_tile * k_blocks * ((double)(waves - 1) + 0.55 + 0.45 * last_fill);
+  // (a last wave that is run as half tiles -- half_tile_tail() -- takes half as long, and is
+  // filled twice as well)
+  const bool halves = half_tile_tail((uint32_t)tiles, (uint32_t)slots, k.m_sub) != 0;
+  // (A launch that is nothing but half tiles runs them 15 % slower than the one-sub-tile pair
+  // kernel runs the same 256-row tiles -- 8192 x 512 x 4096: 33.5 against 29.3 us -- its ring
+  // holds four stages with an idle slab each, its accumulators are not double-buffered.)
+  const double last_wave = halves ? (waves == 1 ? 0.6 : 0.5) * (0.55 + 0.45 * 2.0 * last_fill)
+                                  : 0.55 + 0.45 * last_fill;
+  const double mainloop = per_sm_tile * k_blocks * ((double)(waves - 1) + last_wave);
   // What a launch costs besides: set-up, the first loads' latency, the last epilogue, teardown.
   // A pair pays about 2 us more (cluster launch, barriers across the two CTAs): at
   // 8192 x 512 x 4096 128 lone CTAs take 25.6 us and 64 pairs 27.9 us, at 2048^3 15.3 vs 17.4 us,
@@ -298,7 +315,9 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   if (c.max_ctas > 0 && (uint32_t)(c.max_ctas / best->cta_group) < slots)
     slots = (uint32_t)(c.max_ctas / best->cta_group);
   if (slots == 0) slots = 1;
-  const uint32_t clusters = p.num_tiles < slots ? p.num_tiles : slots;
+  p.half_tiles = half_tile_tail(p.num_tiles, slots, best->m_sub);
+  const uint32_t work = p.num_tiles + p.half_tiles;
+  const uint32_t clusters = work < slots ? work : slots;
   p.grid = clusters * best->cta_group;
   p.block = block_threads(best->m_sub, false);
   p.cluster = best->cta_group;
@@ -890,8 +909,18 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   }
 
   if (k->cta_group > 1) {
-    const uint32_t cap = (uint32_t)resident_clusters(k, ctx->num_sms, &ctx->max_clusters[ki]) * k->cta_group;
-    if (plan.grid > cap) plan.grid = cap;
+    const uint32_t cap = (uint32_t)resident_clusters(k, ctx->num_sms, &ctx->max_clusters[ki]);
+    const uint32_t slots = (uint32_t)(ctx->num_sms / k->cta_group);
+    if (cap < slots) {
+      // fewer clusters fit than the plan assumed: the waves, and with them the tail, change
+      uint32_t clusters = cap;
+      if (cfg && cfg->max_ctas > 0 && (uint32_t)(cfg->max_ctas / k->cta_group) < clusters)
+        clusters = (uint32_t)(cfg->max_ctas / k->cta_group);
+      if (clusters == 0) clusters = 1;
+      plan.half_tiles = half_tile_tail(plan.num_tiles, clusters, k->m_sub);
+      const uint32_t work = plan.num_tiles + plan.half_tiles;
+      plan.grid = (work < clusters ? work : clusters) * k->cta_group;
+    }
   }
 
   GemmParams p{};
@@ -900,7 +929,8 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   p.K = (uint32_t)K;
   p.tiles_m = plan.tiles_m;
   p.tiles_n = plan.tiles_n;
-  p.num_tiles = plan.num_tiles;
+  p.num_tiles = plan.num_tiles + plan.half_tiles;   // scheduler indices
+  p.split_from = plan.num_tiles - plan.half_tiles;
   p.k_blocks = plan.k_blocks;
   p.group_m = (uint32_t)plan.group_m;
   p.alpha = alpha;
@@ -1094,6 +1124,9 @@ int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sf
   if (cfg && cfg->max_ctas > 0 && (uint32_t)(cfg->max_ctas / k->cta_group) < slots)
     slots = (uint32_t)(cfg->max_ctas / k->cta_group);
   if (slots == 0) slots = 1;
+  const uint32_t halves = half_tile_tail(p.num_tiles, slots, k->m_sub);
+  p.split_from = p.num_tiles - halves;
+  p.num_tiles += halves;   // scheduler indices
   const uint32_t clusters = p.num_tiles < slots ? p.num_tiles : slots;
 
   cudaLaunchConfig_t lc{};
@@ -1205,6 +1238,7 @@ int launch_grouped(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.tiles_m = 0;
   p.tiles_n = tiles_n;
   p.num_tiles = 0;  // the kernel derives it from the group sizes
+  p.split_from = 0xffffffffu;
   p.k_blocks = ceil_div(K, kelems);
   p.group_m = (cfg && cfg->group_m > 0) ? (uint32_t)cfg->group_m : 8u;
   p.alpha = alpha;

@@ -66,6 +66,12 @@ struct GemmParams {
   float out_scale;
   float* amax;
   uint32_t n_dests;        // destinations of C (1..kMaxDests)
+  // Two-sub-tile kernels, plain launch: scheduler indices from split_from on are HALF tiles
+  // (index split_from + 2 i + h is sub-tile h of tile split_from + i); num_tiles counts
+  // scheduler indices. The host splits the tiles of a last wave that fills at most half of the
+  // clusters: the wave then takes half as long. Every accumulator still sees the same MMAs in the
+  // same order, so results do not change. No split: split_from >= num_tiles.
+  uint32_t split_from;
   // grouped launch (kernels instantiated with kGrouped): A and C hold the groups' rows one
   // after another, B holds one [N, K] block per group; M above is the total row count
   const int32_t* group_rows;  // device array, rows of A and C per group
@@ -431,6 +437,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
     uint32_t row_base;    // first row of the problem in A and C
     uint32_t row_end;     // one past its last row
     uint32_t b_row_base;  // first row of the problem in B
+    uint32_t sub_mask;    // accumulator sub-tiles of the tile that this scheduler index covers
   };
   auto locate = [&](uint32_t t, uint32_t& g) -> TileSpot {
     TileSpot sp;
@@ -444,7 +451,18 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
       sp.row_base = grp_row_begin[g];
       sp.row_end = grp_row_begin[g + 1u];
       sp.b_row_base = g * p.N;
+      // the last row block of a group often needs only the first of its two 128-row (256 per
+      // pair) sub-tiles: the second is then neither loaded nor multiplied
+      sp.sub_mask = (kMSub == 2 && sp.row_base + c.m * T::kTileM + kCtaRows * kCtaGroup < sp.row_end) ? 3u : 1u;
     } else {
+      sp.sub_mask = (1u << kMSub) - 1u;
+      if constexpr (kMSub == 2) {
+        if (t >= p.split_from) {   // a half tile of the last wave
+          const uint32_t v = t - p.split_from;
+          t = p.split_from + (v >> 1);
+          sp.sub_mask = 1u << (v & 1u);
+        }
+      }
       const TileCoord c = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
       sp.m = c.m;
       sp.n = c.n;
@@ -454,17 +472,6 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
     }
     return sp;
   };
-  // Sub-tiles of a tile that hold rows of the problem. In a grouped launch the last row block
-  // of a group often needs only the first of its two 128-row (256 per pair) sub-tiles: the
-  // second is then neither loaded nor multiplied.
-  auto live_subtiles = [&](const TileSpot& c) -> uint32_t {
-    if constexpr (kGrouped && kMSub == 2) {
-      return (c.row_base + c.m * T::kTileM + kCtaRows * kCtaGroup >= c.row_end) ? 1u : 2u;
-    } else {
-      return (uint32_t)kMSub;
-    }
-  };
-
   // ------------------------------------------------------------ TMA producer
   if (warp_idx == 0) {
     if (lane < kLoadLanes) {
@@ -488,10 +495,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
         const int32_t row = is_b ? (int32_t)(c.b_row_base + c.n * BN + cta_rank * T::kBRows)
                                  : (int32_t)(c.row_base + c.m * T::kTileM + cta_rank * kCtaRows +
                                              lane * (kCtaRows * kCtaGroup));
-        const uint32_t n_sub = live_subtiles(c);
-        const bool live = is_b || lane < n_sub;
+        const bool live = is_b || ((c.sub_mask >> lane) & 1u) != 0u;
         // bytes this CTA loads per stage
-        const uint32_t stage_tx = n_sub * T::kASubBytes + T::kBBytes + T::kSfStageBytes;
+        const uint32_t stage_tx = (uint32_t)__popc(c.sub_mask) * T::kASubBytes + T::kBBytes + T::kSfStageBytes;
         // (block scales of a stage are loaded by the scale-producer warp, onto the same barrier)
         bool ok = true;
         for (uint32_t kb = kb_first; kb < k_steps; ++kb) {
@@ -542,7 +548,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
       bool ok = true;
       for (uint32_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
         const TileSpot c = locate(t, grp);
-        const bool live = my < live_subtiles(c);
+        const bool live = ((c.sub_mask >> my) & 1u) != 0u;
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
         // block scales in TMEM, one set of columns per issuer: A's slabs first, then B's
         // atoms; the tile's first row of B may lie 64 rows into its first atom, i.e. 2 columns in
@@ -681,7 +687,8 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
       if constexpr (kGrouped) {
         if (p.group_alpha != nullptr) tile_alpha *= __ldg(p.group_alpha + grp);
       }
-      const bool box_outside = row0 >= c.row_end;
+      const bool live_sub = ((c.sub_mask >> ms) & 1u) != 0u;   // else: another index's half, or past the group
+      const bool box_outside = !live_sub || row0 >= c.row_end;
       const bool box_straddles = kGrouped && !box_outside && row0 + kStoreBoxRows > c.row_end;
       const uint32_t col0 = c.n * BN;
       const uint32_t taddr = tmem_base + tmem_lane_offset(q) + buf * T::kAccCols + ms * BN;
@@ -776,7 +783,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
           }
           if constexpr (kOut == kOutE4M3) {
             // rows past M carry act(bias) and must not count; columns past N are exactly zero
-            if (r < p.M) {
+            if (r < p.M && live_sub) {
 #pragma unroll
               for (uint32_t i = 0; i < kFp32PerChunk; ++i)
                 if (cc + i < p.N) tile_amax = fmaxf(tile_amax, fabsf(__uint_as_float(v[i])));

@@ -58,7 +58,7 @@ class GemmPlan(C.Structure):
                 ("num_tiles", C.c_uint32), ("k_blocks", C.c_uint32), ("grid", C.c_uint32),
                 ("block", C.c_uint32), ("cluster", C.c_uint32), ("smem_bytes", C.c_uint32),
                 ("tmem_cols", C.c_uint32), ("stage_bytes", C.c_uint32),
-                ("expect_tx_bytes", C.c_uint32), ("idesc", C.c_uint32)]
+                ("expect_tx_bytes", C.c_uint32), ("idesc", C.c_uint32), ("half_tiles", C.c_uint32)]
 
 
 _lib = None

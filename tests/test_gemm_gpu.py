@@ -161,6 +161,59 @@ def test_two_k_blocks_per_stage_kernels(ctx, oracle_mod, M, N, K):
         assert torch.equal(full[:, :N], ref)
 
 
+@pytest.mark.parametrize("M,N,K", [(1536, 512, 320), (1400, 520, 136), (4096, 1024, 1024)])
+def test_half_tile_tail_wave(ctx, oracle_mod, M, N, K):
+    """Tiles of a last wave that fills at most half of the clusters are run as two half tiles
+    (one accumulator sub-tile each, on different clusters). Every accumulator sees the same MMAs
+    in the same order, so the result equals the unsplit launch bit for bit -- also with rows past
+    M in the split tile and with the fused epilogue."""
+    from patina_b200 import inputs, GemmConfig, lib as L
+    A, B = inputs.make_operands("llm", M, N, K, seed=M + K)
+    want = expect_bf16(oracle_mod, A, B, alpha=0.5)
+    dA, dB = A.cuda(), B.cuda()
+    split_cfg = GemmConfig(2, 256, 0, 0, 8 if M < 4096 else 0, 2)
+    whole_cfg = GemmConfig(2, 256, 0, 0, 2, 2)       # one cluster: no tail wave
+    assert L.plan(L.IN_BF16, L.OUT_BF16, M, N, K, split_cfg).half_tiles > 0
+    assert L.plan(L.IN_BF16, L.OUT_BF16, M, N, K, whole_cfg).half_tiles == 0
+    ldc = (N + 7) // 8 * 8 + 8
+    full = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm_tn(dA, dB, out=full[:, :N], alpha=0.5, config=split_cfg)
+    ctx.status()
+    check_norm(oracle_mod, full[:, :N], want, f"half-tile tail {M}x{N}x{K}")
+    assert bool(torch.isnan(full[:, N:]).all())
+    whole = ctx.gemm_tn(dA, dB, alpha=0.5, config=whole_cfg)
+    ctx.status()
+    assert torch.equal(full[:, :N], whole)
+
+
+def test_half_tile_tail_wave_fused_epilogue(ctx, oracle_mod):
+    """8192 x 4096 has 34 tiles in its last wave: the fused epilogue over half tiles (bias,
+    residual and activation applied by the sub-tile's own epilogue warps only) against the plain
+    kernel's result put through the same arithmetic in fp32."""
+    from patina_b200 import inputs, lib as L
+    M, N, K = 8192, 4096, 2048
+    assert L.plan(L.IN_BF16, L.OUT_BF16, M, N, K).half_tiles == 34
+    A, B = inputs.make_operands("llm", M, N, K, seed=9)
+    dA, dB = A.cuda(), B.cuda()
+    g = torch.Generator().manual_seed(3)
+    bias = torch.randn(N, generator=g).cuda()
+    resid = torch.randn((M, N), generator=g).to(torch.bfloat16).cuda()
+    fused = ctx.gemm_bf16_tn_fused(dA, dB, alpha=0.5, bias=bias, residual=resid, beta=0.25, activation="relu")
+    ctx.status()
+    plain = ctx.gemm_tn(dA, dB, out_dtype=None)          # bf16 of the fp32 accumulators (alpha = 1)
+    ctx.status()
+    # the fused kernel rounds once, from fp32; redo it from the bf16 result: 1 bf16 ulp of slack
+    ref = torch.relu(plain.float() * 0.5 + bias[None, :] + 0.25 * resid.float())
+    err = (fused.float() - ref).abs().max().item()
+    assert err <= 2.0 ** -7 * max(1.0, ref.abs().max().item()), err
+    # and the plain kernel itself, split, equals the oracle on sampled rows
+    rows = np.array([0, 255, 256, 511, 512, 4095, 7936, 8191])
+    want = oracle_mod.scale_round_bf16(oracle_mod.ref_gemm_tn(
+        oracle_mod.bf16_bits_to_f32(A.view(torch.int16).numpy().view(np.uint16)),
+        oracle_mod.bf16_bits_to_f32(B.view(torch.int16).numpy().view(np.uint16)), rows=rows), 1.0)
+    check_norm(oracle_mod, plain[torch.from_numpy(rows).cuda()], want, "split tail rows")
+
+
 def test_two_k_blocks_per_stage_needs_whole_k_blocks(ctx):
     """K = 72 is not whole 64-element k-blocks: the 3-D operand view does not exist, the library's
     own choice falls back to the one-k-block kernel and an explicit request is refused."""

@@ -63,6 +63,23 @@ def test_tile_scheduler_is_a_bijection(built_lib, tiles_m, tiles_n, group):
         assert (m.value, n.value) == (1, 0)
 
 
+def test_plan_half_tile_tail():
+    """A last wave that fills at most half of the clusters is run as half tiles."""
+    # 8192 x 4096: 16 x 16 = 256 tiles of 512 x 256 on 74 clusters: 3 waves and 34 tiles
+    p = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 4096, 14336)
+    assert (p.m_sub, p.num_tiles, p.half_tiles, p.grid) == (2, 256, 34, 148)
+    # 8192^3: 512 tiles = 6 waves and 68 tiles: more than half a wave, left whole
+    assert L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192).half_tiles == 0
+    # fewer tiles than half the clusters: all of them are split, and more CTAs run
+    q = L.plan(L.IN_BF16, L.OUT_BF16, 4096, 1024, 4096, L.GemmConfig(2, 256, 0, 0, 0, 2))
+    assert (q.num_tiles, q.half_tiles, q.grid) == (32, 32, 128)
+    # one accumulator sub-tile per CTA: nothing to split
+    assert L.plan(L.IN_BF16, L.OUT_BF16, 8192, 4096, 14336, L.GemmConfig(2, 256, 0, 0, 0, 1)).half_tiles == 0
+    # a capped grid changes the waves: 6 tiles on 4 clusters leave 2, on 2 clusters none
+    assert L.plan(L.IN_BF16, L.OUT_BF16, 1536, 512, 320, L.GemmConfig(2, 256, 0, 0, 8, 2)).half_tiles == 2
+    assert L.plan(L.IN_BF16, L.OUT_BF16, 1536, 512, 320, L.GemmConfig(2, 256, 0, 0, 4, 2)).half_tiles == 0
+
+
 def test_plan_headline_shape():
     p = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192)
     assert (p.cta_group, p.m_sub, p.block_n, p.cluster, p.tile_m) == (2, 2, 256, 2, 512)
@@ -107,10 +124,12 @@ def test_planner_picks_match_what_was_measured_fastest():
     picks = {
         (8192, 8192, 8192): (2, 2, 256),      # 6.92 waves of 512 x 256
         (4096, 4096, 4096): (2, 2, 240),      # 144 tiles = two waves of 74 pairs instead of 128 + idle
-        (8192, 3584, 8192): (2, 2, 208),      # 1/8 of a 28672-wide projection: 322 vs 331 (224) vs 359 us (256)
+        (8192, 3584, 8192): (2, 2, 224),      # 1/8 of a 28672-wide projection: 3 waves and 34 tiles, those as
+                                              # half tiles: 318 vs 324 (208, no tail) vs 326 us (256)
         (8192, 1792, 4096): (2, 2, 208),
         (8192, 14336, 4096): (2, 2, 240),
-        (8192, 4096, 4096): (2, 1, 256),      # 256 x 256 pair tiles fill 6.92 waves; 512 x 256 only 3.46
+        (8192, 4096, 4096): (2, 2, 256),      # 3 waves and 34 tiles of 512 x 256, those as half tiles: 181.0 us;
+                                              # 256 x 256 pair tiles (6.92 waves) 180.1
         (8192, 512, 4096): (1, 1, 256),       # one wave, short K: 128 lone CTAs 25.6 us, 64 pairs 27.9 us
         (8192, 512, 6144): (2, 1, 256),       # longer K: the pair is ahead again (41.8 vs 44.0 us)
         (2048, 2048, 2048): (1, 1, 256),      # 15.3 vs 17.4 us

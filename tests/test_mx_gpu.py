@@ -77,6 +77,19 @@ def test_mxfp8_every_tile(ctx, oracle_mod, name):
         check(oracle_mod, got, expect(oracle_mod, Aq, ea, Bq, eb), f"{name} {M}x{N}x{K}")
 
 
+def test_mxfp8_half_tile_tail_wave(ctx, oracle_mod):
+    """The two-sub-tile kernel splits the tiles of a short last wave into half tiles (6 tiles on
+    4 clusters: the last 2 become 4 halves): equal, bit for bit, to the launch on one cluster,
+    which splits nothing, and within tolerance of the oracle."""
+    from patina_b200 import GemmConfig
+    M, N, K = 1500, 384, 1152
+    Aq, ea, Bq, eb = make(M, N, K, seed=11)
+    split = run(ctx, Aq, ea, Bq, eb, alpha=0.5, config=GemmConfig(2, 192, 0, 0, 8, 2))
+    whole = run(ctx, Aq, ea, Bq, eb, alpha=0.5, config=GemmConfig(2, 192, 0, 0, 2, 2))
+    check(oracle_mod, split, expect(oracle_mod, Aq, ea, Bq, eb, alpha=0.5), "half-tile tail")
+    assert torch.equal(split, whole)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 8, 32), (200, 392, 352), (129, 257, 96), (520, 1000, 4128)])
 def test_mxfp8_ragged_shapes(ctx, oracle_mod, M, N, K):
     """Ragged M, N and K (K a multiple of 32 but not of 128: the last scale atom is partly

@@ -1111,7 +1111,7 @@ int launch_mx(PatinaGemmContext* ctx, const void* A, int64_t lda, const void* sf
   p.status = ctx->d_status;
   p.wait_limit_ns = ctx->wait_limit_ns;
 #ifdef PATINA_TRACE
-  p.trace = nullptr;
+  p.trace = ctx->trace;
   p.l2_hint_a = p.l2_hint_b = 0;
 #endif
   uint32_t slots = (uint32_t)(ctx->num_sms / k->cta_group);

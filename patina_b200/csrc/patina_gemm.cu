@@ -676,10 +676,11 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.ldc = ldc;
   p.partials = ctx->d_sk_partials;
   p.counters = ctx->d_sk_counters;
-  // Wide X (more than 16 rows): a shared tile's partials are 16 KB and more per contributor; one
-  // finishing CTA per tile pulling them through its own SM was measured at 15 us for M = 128, so
-  // the sum moves to a second small kernel that every SM takes part in.
-  p.split_reduce = (sp.m_pad > 16u && sp.grid > 1u) ? 1u : 0u;
+  // Shared tiles are summed by a second small kernel that every SM takes part in: one finishing
+  // CTA per tile pulling every contributor's partial tile through its own SM was measured at 15 us
+  // for M = 128 (16 KB and more per contributor), and for 16 rows of X it is still behind
+  // (16 x 3584 x 8192: 17.5 against 16.8 us; 16 x 28672 x 8192: 79.0 against 78.7).
+  p.split_reduce = sp.grid > 1u ? 1u : 0u;
   if (reduce_mode == 2) p.split_reduce = 1u;  // explicit request (PatinaGemmConfig::stream_k = 2 / 3)
   if (reduce_mode == 3) p.split_reduce = 0u;
   // No tile is shared (every CTA boundary is a tile boundary): nothing to sum, no second kernel.

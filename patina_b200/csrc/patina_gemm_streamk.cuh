@@ -142,8 +142,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   w.limit_ns = p.wait_limit_ns;
   w.has_peer = false;
 
-  // Producer state lives outside the role branch: thread 0 starts the first ring pass before
-  // the CTA-wide set-up barrier, so that TMEM allocation and the barrier hide behind DRAM latency.
+  // Producer state lives outside the role branch: the producer lanes start the first ring pass
+  // before the CTA-wide set-up barrier, so that TMEM allocation and the barrier hide behind DRAM
+  // latency.
   uint32_t prod_s = 0, prod_ph = 0;
   uint64_t prod_u = u_begin;
   uint32_t prod_t = (uint32_t)(u_begin / p.k_blocks);
@@ -166,18 +167,31 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     *last_ptr = 0u;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
-    stream_once = ptx::l2_policy_evict_first();
-    keep = ptx::l2_policy_evict_last();
-    // First pass through the ring: every stage is free, no wait needed.
-    while (prod_u < u_end && prod_ph == 0u) {
-      const uint32_t sw = ring + prod_s * kSkStageStride;
-      const int32_t k0 = (int32_t)(prod_kb * kBlockKElems);
-      ptx::mbar_arrive_expect_tx(full_bar + 8u * prod_s, kWBytes + x_bytes);
-      ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * prod_s, k0, (int32_t)(prod_t * kSkTileRows), stream_once);
-      ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * prod_s, k0, 0, keep);
-      ++prod_u;
-      if (++prod_s == kStages) { prod_s = 0; prod_ph = 1u; }
-      if (++prod_kb == p.k_blocks) { prod_kb = 0; ++prod_t; }
+  }
+  // Two producer lanes: lane 0 announces the stage's bytes and loads the slab of W, lane 1 loads
+  // the slab of X (an issuing lane spends 150 - 200 cycles per TMA load and 390 per {wait,
+  // announce, issue} round; two lanes overlap theirs).
+  const bool is_producer = (warp_idx == 0 && lane < 2u);
+  if (warp_idx == 0) {
+    __syncwarp();   // thread 0's barriers, seen by lane 1
+    if (is_producer) {
+      ptx::fence_proxy_async_smem();
+      stream_once = ptx::l2_policy_evict_first();
+      keep = ptx::l2_policy_evict_last();
+      // First pass through the ring: every stage is free, no wait needed.
+      while (prod_u < u_end && prod_ph == 0u) {
+        const uint32_t sw = ring + prod_s * kSkStageStride;
+        const int32_t k0 = (int32_t)(prod_kb * kBlockKElems);
+        if (lane == 0) {
+          ptx::mbar_arrive_expect_tx(full_bar + 8u * prod_s, kWBytes + x_bytes);
+          ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * prod_s, k0, (int32_t)(prod_t * kSkTileRows), stream_once);
+        } else {
+          ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * prod_s, k0, 0, keep);
+        }
+        ++prod_u;
+        if (++prod_s == kStages) { prod_s = 0; prod_ph = 1u; }
+        if (++prod_kb == p.k_blocks) { prod_kb = 0; ++prod_t; }
+      }
     }
   }
   if (warp_idx == 1) {
@@ -195,7 +209,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   // ------------------------------------------------------------ TMA producer
   if (warp_idx == 0) {
-    if (lane == 0) {
+    if (is_producer) {
       uint32_t s = prod_s, ph = prod_ph;
       bool ok = true;
       uint64_t u = prod_u;
@@ -214,9 +228,12 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (uint32_t g = 0; g < group; ++g, ++u) {
           const uint32_t sw = ring + s * kSkStageStride;
           const int32_t k0 = (int32_t)(kb * kBlockKElems);
-          ptx::mbar_arrive_expect_tx(full_bar + 8u * s, kWBytes + x_bytes);
-          ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * s, k0, (int32_t)(t * kSkTileRows), stream_once);
-          ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * s, k0, 0, keep);
+          if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(full_bar + 8u * s, kWBytes + x_bytes);
+            ptx::tma_load_2d_hint(sw, &tm_w, full_bar + 8u * s, k0, (int32_t)(t * kSkTileRows), stream_once);
+          } else {
+            ptx::tma_load_2d_hint(sw + kWBytes, &tm_x, full_bar + 8u * s, k0, 0, keep);
+          }
           if (++s == kStages) { s = 0; ph ^= 1u; }
           if (++kb == p.k_blocks) { kb = 0; ++t; }
         }

@@ -9,7 +9,10 @@ import pytest
 from patina_b200 import dialect_text as dt
 from patina_b200 import lib as L
 
-GOLDEN = "/root/reference/crates/patina/tests/golden/v2_gemm_pipelined.mlir"
+# the reference checkout, where there is one: PATINA_REFERENCE_ROOT, else a sibling of this repository
+_REF_ROOT = os.environ.get("PATINA_REFERENCE_ROOT") or os.path.abspath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
+GOLDEN = os.path.join(_REF_ROOT, "crates", "patina", "tests", "golden", "v2_gemm_pipelined.mlir")
 
 
 def test_every_single_cta_plan_prints_and_verifies(built_lib):

@@ -113,13 +113,15 @@ WORKLOADS["moe_grouped_64x2048x4096"] = _wl(
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture;
 # see profiles/. None until a capture of that workload exists.
 NCU_DRAM_TRAFFIC_BYTES = {
-    # profiles/gemm_tn_kernel_bf16_8192_pair512x256.md: 821.4 MB read + 121.4 MB written
-    "bf16_tn_8192": 942_766_080,
+    # profiles/gemm_tn_kernel_bf16_8192_pair512x256.md: 822.4 MB read + 121.7 MB written
+    "bf16_tn_8192": 944_138_240,
     # profiles/gemm_streamk_kernel_bf16_m16_n28672_k8192.md
     "skinny_m16": 476_803_840,
     "skinny_m64": 476_598_016,
     # profiles/gemm_tn_kernel_fp8_8192_pair512x256.md
     "fp8_tn_8192": 434_516_224,
+    # profiles/gemm_mx_tn_kernel_mxfp8_8192_pair512x192.md: 323.4 MB read + 118.7 MB written
+    "mxfp8_tn_8192": 442_086_144,
     # profiles/gemm_tn_kernel_grouped_bf16_moe.md
     "moe_grouped_64x2048x4096": 1_176_533_696,
     "moe_grouped_8x14336x4096": 2_069_426_128,

@@ -194,6 +194,21 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int64_t K, int n
   const uint64_t slots = (uint64_t)(num_sms / k.cta_group);
   if (slots == 0 || tiles == 0) return 0.0;
   const uint64_t waves = (tiles + slots - 1) / slots;
+  if (k.k_chunks == 2) {
+    // Two k-blocks per stage, two accumulators: a k-block takes a CTA 0.16 us at either width
+    // (issue and operand intake, not the tensor pipe), 0.20 us for the 128-wide tile once more
+    // than about 96 CTAs pull 32 KB per k-block each; the 128-wide tile's epilogue is 0.5 us
+    // longer. Measured: 1024^3 6.7 us on 128 x 64 tiles and 7.2 on 128 x 128, 2048 x 1024 x 1024
+    // 10.3 and 7.7, 1024 x 1024 x 4096 15.6 and 15.7, 2048^3 28.2 and 18.4.
+    // For problems of at most one wave of 128 x 128 tiles; beyond, the wide tiles' lower operand
+    // traffic per flop wins (2048^3: 15.7 us on 128 x 256 tiles against 18.4).
+    if ((uint64_t)ceil_div(M, 128) * ceil_div(N, 128) > slots) return 0.0;
+    const uint64_t ctas = tiles < slots ? tiles : slots;
+    const double kb = (double)ceil_div(K, kBlockKBytes / input_bytes(k.in_type));
+    const double t_kb = (k.block_n >= 128 && ctas > 96) ? 0.20 : 0.16;
+    const double time_us = t_kb * kb * (double)waves + (k.block_n >= 128 ? 4.6 : 4.1);
+    return 1.0e12 / (time_us * 82000.0);
+  }
   const double last_fill = (double)(tiles - (waves - 1) * slots) / (double)slots;
   double speed = 0.6;
   if (k.cta_group == 2 && k.m_sub == 2) {
@@ -230,10 +245,10 @@ double config_score(const KernelEntry& k, int64_t M, int64_t N, int64_t K, int n
 }
 
 // Threads of a block: producer and MMA warps, four epilogue warps per accumulator sub-tile, a
-// second MMA-issuing warp when there are two sub-tiles, a scale-producer warp when block-scaled
-// (GemmTraits::kThreads).
-uint32_t block_threads(int m_sub, bool block_scaled) {
-  return 64u + 128u * (uint32_t)m_sub + (m_sub == 2 ? 32u : 0u) + (block_scaled ? 32u : 0u);
+// second MMA-issuing warp when there are two sub-tiles or two k-blocks per stage, a scale-producer
+// warp when block-scaled (GemmTraits::kThreads).
+uint32_t block_threads(int m_sub, bool block_scaled, int k_chunks = 1) {
+  return 64u + 128u * (uint32_t)m_sub + ((m_sub == 2 || k_chunks == 2) ? 32u : 0u) + (block_scaled ? 32u : 0u);
 }
 
 // Kernels with several k-blocks per stage view an operand as {128 bytes, rows, K / 128 bytes}:
@@ -319,10 +334,11 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
   const uint32_t work = p.num_tiles + p.half_tiles;
   const uint32_t clusters = work < slots ? work : slots;
   p.grid = clusters * best->cta_group;
-  p.block = block_threads(best->m_sub, false);
+  p.block = block_threads(best->m_sub, false, best->k_chunks);
   p.cluster = best->cta_group;
   p.smem_bytes = best->smem_bytes;
-  p.tmem_cols = (2 * best->m_sub * best->block_n <= 512 ? 2 : 1) * best->m_sub * best->block_n;
+  const uint32_t acc_cols = (uint32_t)(best->m_sub * best->block_n * (best->k_chunks == 2 ? 2 : 1));
+  p.tmem_cols = (2 * acc_cols <= 512 ? 2 : 1) * acc_cols;
   p.tmem_cols = p.tmem_cols <= 256 ? 256 : 512;  // allocation granularity: a power of two
   const SmemPlan sp = smem_plan(best->cta_group, best->m_sub, best->block_n, best->stages,
                                 output_bytes(out_type), 0, false, (uint32_t)best->k_chunks);
@@ -719,6 +735,12 @@ bool cluster_k_supported(int in_type, int out_type, int64_t M, int64_t N, int64_
 // 0: do not split; else the cluster size.
 int cluster_k_choice(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
   if (M <= 128) return 0;                                          // the skinny paths cover these
+  // Only where even 128 x 64 tiles leave a third of the SMs without one: the two-accumulator
+  // single-CTA kernels run a k-block in 0.16 us whatever their width, and from 1024 x 1024 x 4096
+  // on (128 such tiles) they are ahead of the split (15.4 against 16.0 us; 1024 x 2048 x 2048:
+  // 10.7 against 12.8), while 512 x 512 x 4096 (32 tiles) is 13.1 us split and 14.3 whole, and
+  // 512 x 1024 x 8192 (64 tiles) 18.4 and 25.0.
+  if ((uint64_t)ceil_div(M, kCtaRows) * ceil_div(N, 64) * 3 > (uint64_t)num_sms * 2) return 0;
   const uint64_t tiles = (uint64_t)ceil_div(M, kCtaRows) * ceil_div(N, kSplitBN);
   const uint32_t kb = ceil_div(K, kBlockKBytes / 2);
   for (int split = 4; split >= 2; split /= 2) {

@@ -213,8 +213,16 @@ struct GemmTraits {
   static constexpr uint32_t kEpiWarps = 4 * kMSub;            // one warp per (sub-tile, lane quarter)
   // producer + MMA + epilogue warps (+ the scale-producer warp of block-scaled kernels)
   // (+ a second MMA-issuing warp when there are two accumulator sub-tiles)
+  // Two k-blocks per stage also means two accumulators per tile: the stage's first k-block is
+  // multiplied into the first by one issuing thread, its second into the second by another, and
+  // the epilogue adds the two (C = sum over even k-blocks + sum over odd k-blocks, in fp32: a
+  // fixed order, but not the order of the one-accumulator kernels). One thread cannot issue the
+  // MMAs of a narrow tile as fast as the tensor pipe retires them (85 cycles of issue against
+  // 48 / 64 of pipe at 64 / 128 columns), and two threads may not share an accumulator.
+  static constexpr bool kDualAcc = (kKChunks == 2);
+  static constexpr uint32_t kIssuers = kDualAcc ? 2u : (uint32_t)kMSub;   // MMA-issuing threads
   static constexpr uint32_t kThreads =
-      64 + 32 * kEpiWarps + (is_block_scaled(kIn) ? 32u : 0u) + (kMSub == 2 ? 32u : 0u);
+      64 + 32 * kEpiWarps + (is_block_scaled(kIn) ? 32u : 0u) + (kIssuers == 2 ? 32u : 0u);
   static constexpr uint32_t kSecondIssuerWarp = 2 + kEpiWarps + (is_block_scaled(kIn) ? 1u : 0u);
   static constexpr uint32_t kBlockKElems = kBlockKBytes / input_bytes(kIn);
   static constexpr uint32_t kUmmaK = umma_k(kIn);
@@ -233,7 +241,7 @@ struct GemmTraits {
   static constexpr uint32_t kABytes = kMSub * kASubBytes;
   static constexpr uint32_t kBBytes = kChunkBBytes * kKChunks;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr uint32_t kAccCols = kMSub * BN;                  // TMEM columns of one tile
+  static constexpr uint32_t kAccCols = kMSub * BN * (kKChunks == 2 ? 2 : 1);   // TMEM columns of one tile
   // Block-scaled operands: every stage also carries the scale atoms of its A slabs and of the
   // rows of B under the tile (512 bytes each), and TMEM holds one 4-column copy of each behind
   // the accumulators, rewritten for every k-block (tcgen05.cp and tcgen05.mma run in issue order).
@@ -263,7 +271,8 @@ struct GemmTraits {
   static constexpr bool kOverlapLastChunk = (BN % kChunkCols) != 0;
   static constexpr uint32_t kSmemBytes =
       smem_plan(kCtaGroup, kMSub, BN, kStages, output_bytes(kOut), kSfStageBytes, kFusedEpi, kKChunks).total_bytes;
-  static_assert(kKChunks == 1 || (kCtaGroup == 1 && !is_block_scaled(kIn)), "multi-chunk stages: single-CTA kernels");
+  static_assert(kKChunks == 1 || (kKChunks == 2 && kCtaGroup == 1 && kMSub == 1 && !is_block_scaled(kIn) && !kFusedEpi),
+                "two k-blocks per stage: single-CTA kernels with one sub-tile, plain epilogue");
   static_assert(!kMx || BN % 64 == 0, "block-scaled tiles: B's scales must start an even number of TMEM columns into an atom");
   static_assert(kMSub == 1 || kMSub == 2, "one or two accumulator sub-tiles per CTA");
   static_assert(umma_shape_ok(128 * kCtaGroup, BN), "illegal tcgen05.mma shape");
@@ -300,7 +309,7 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
   // 231 cycles, four per 148 (separate warps: 199 and 100); one SM takes in 120 bytes per clock
   // when few SMs load and about 84 when 128 do.
   constexpr uint32_t kLoadLanes = (uint32_t)kMSub + 1u;
-  constexpr uint32_t kIssuers = (uint32_t)kMSub;   // MMA-issuing threads: one per accumulator sub-tile
+  constexpr uint32_t kIssuers = T::kIssuers;   // MMA-issuing threads: one per accumulator (sub-tile, or k-block parity)
   // The fused epilogue may read C itself as the residual, so no column may be produced twice.
   static_assert(!(kFused && T::kOverlapLastChunk), "fused epilogue needs whole store boxes");
   static_assert(!(kFused && kGrouped), "the grouped kernel has the plain epilogue only");
@@ -540,15 +549,16 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
   // the scales it needs into its own TMEM columns (tcgen05.cp is ordered before the MMAs of the
   // same thread only) and commits for itself: the `empty` and `tmem full` barriers count
   // kIssuers arrivals. Warp 1 takes sub-tile 0, the last warp of the block sub-tile 1.
-  else if (warp_idx == 1 || (kMSub == 2 && warp_idx == T::kSecondIssuerWarp)) {
+  else if (warp_idx == 1 || (kIssuers == 2 && warp_idx == T::kSecondIssuerWarp)) {
     if (lane == 0 && cta_rank == 0) {
-      const uint32_t my = (warp_idx == 1) ? 0u : 1u;  // the accumulator sub-tile this thread multiplies
+      const uint32_t my = (warp_idx == 1) ? 0u : 1u;  // the accumulator this thread multiplies into: sub-tile
+                                                      // `my`, or (kDualAcc) the stages' k-block `my`
       const uint32_t idesc_v = idesc(kIn, kCtaRows * kCtaGroup, BN);
       uint32_t s = 0, ph = 0, it = 0, grp = 0;
       bool ok = true;
       for (uint32_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
         const TileSpot c = locate(t, grp);
-        const bool live = ((c.sub_mask >> my) & 1u) != 0u;
+        const bool live = T::kDualAcc || ((c.sub_mask >> my) & 1u) != 0u;
         const uint32_t buf = it % T::kAccBufs, acc_ph = (it / T::kAccBufs) & 1u;
         // block scales in TMEM, one set of columns per issuer: A's slabs first, then B's
         // atoms; the tile's first row of B may lie 64 rows into its first atom, i.e. 2 columns in
@@ -579,10 +589,11 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
           }
 #pragma unroll
           for (uint32_t ch = 0; ch < (uint32_t)kKChunks; ++ch) {
-            // (a multi-chunk stage's chunks past K hold TMA's zero fill: skipped)
+            if (T::kDualAcc && ch != my) continue;      // the other issuer's k-block
+            // (a stage's k-block past K holds TMA's zero fill: not multiplied)
             if (kKChunks > 1 && kb * (uint32_t)kKChunks + ch >= p.k_blocks) break;
             const uint64_t db_c = db + (uint64_t)((ch * T::kChunkBBytes) >> 4);
-            const uint64_t da = smem_desc_sw128_kmajor(sa + my * T::kASubBytes + ch * T::kChunkABytes);
+            const uint64_t da = smem_desc_sw128_kmajor(sa + (T::kDualAcc ? 0u : my) * T::kASubBytes + ch * T::kChunkABytes);
 #pragma unroll
             for (uint32_t k = 0; k < T::kUmmaPerStage; ++k) {
               const uint32_t adv = k_advance_units_sw128(k * T::kUmmaK, kIn);
@@ -592,7 +603,9 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
                   ptx::umma_mx<kCtaGroup>(tmem_d, da + adv, db_c + adv, idesc_mx(kCtaRows * kCtaGroup, BN, k, k),
                                           (tsfa0 + 4u * my) | (k << 30), tsfb0 | (k << 30), (kb | k) != 0u);
                 } else {
-                  ptx::umma<kCtaGroup, kKind>(tmem_d, da + adv, db_c + adv, idesc_v, (kb | ch | k) != 0u);
+                  // (an accumulator's first MMA overwrites it: k-block 0, or 1 for the second of two)
+                  ptx::umma<kCtaGroup, kKind>(tmem_d, da + adv, db_c + adv, idesc_v,
+                                              (T::kDualAcc ? (kb | k) : (kb | ch | k)) != 0u);
                 }
               }
             }
@@ -924,6 +937,18 @@ __device__ __forceinline__ void gemm_tn_body(const CUtensorMap& tm_a, const CUte
 #pragma unroll 1
       for (uint32_t ch = 0; ch < T::kChunks; ++ch) {
         request(ch, v);
+        if constexpr (T::kDualAcc) {
+          // the odd k-blocks' accumulator, BN columns further on (never written when K is one k-block)
+          if (p.k_blocks > 1u) {
+            uint32_t v2[kFp32PerChunk];
+            const uint32_t c0 = chunk_col(ch);
+#pragma unroll
+            for (uint32_t h = 0; h < kFp32PerChunk; h += 32u) ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)BN + c0 + h, &v2[h]);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (uint32_t i = 0; i < kFp32PerChunk; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v2[i]));
+          }
+        }
         ptx::tmem_ld_wait();
         finish(ch, v);
       }
@@ -972,10 +997,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                                                                    nullptr, nullptr);
 }
 
-// Single-CTA kernel whose stages hold kKChunks k-blocks, each operand slab of a stage fetched by
-// one 3-D box (tensor maps of rank 3: {128 bytes of K, rows, K / 128 bytes}); plain epilogue.
+// Single-CTA kernel whose stages hold two k-blocks, each operand slab of a stage fetched by one
+// 3-D box (tensor maps of rank 3: {128 bytes of K, rows, K / 128 bytes}), the two k-blocks
+// multiplied into two accumulators by two issuing threads; plain epilogue.
 template <int kMSub, int BN, int kStages, int kIn, int kOut, int kKChunks>
-__global__ void __launch_bounds__(64 + 128 * kMSub, 1)
+__global__ void __launch_bounds__(64 + 128 * kMSub + 32, 1)   // + the second MMA-issuing warp
 gemm_tn_chunked_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                        const __grid_constant__ CStoreMaps<1> tm_c, const GemmParams p) {
   gemm_tn_body<1, kMSub, BN, kStages, kIn, kOut, false, false, 1, kKChunks>(tm_a, tm_b, tm_c, p, nullptr, nullptr);

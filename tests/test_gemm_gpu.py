@@ -138,9 +138,12 @@ def test_bf16_1024_cubed_all_configs(ctx, oracle_mod):
                                    (2048, 264, 960)])
 def test_two_k_blocks_per_stage_kernels(ctx, oracle_mod, M, N, K):
     """The single-CTA kernels whose stages hold two k-blocks fetched as one 3-D box per operand
-    (128 x 128 tiles with 3 stages, 128 x 64 with 4): odd and even counts of k-blocks (an odd
-    count leaves the last stage half zero-filled and half multiplied), ragged M and N. They add
-    the same products in the same order as the one-k-block kernels: equal bit for bit."""
+    (128 x 128 tiles with 3 stages, 128 x 64 with 4), the even k-blocks multiplied into one
+    accumulator and the odd ones into a second by two issuing threads, the two added in the
+    epilogue: odd and even counts of k-blocks (an odd count leaves the last stage half zero-filled;
+    a single k-block leaves the second accumulator unused), ragged M and N. Against the oracle,
+    and against the one-accumulator kernel of the same tile (another summation order: within
+    the tolerance, and equal bit for bit when K is a single k-block)."""
     from patina_b200 import inputs, GemmConfig, lib as L
     assert K % 64 == 0
     A, B = inputs.make_operands("llm", M, N, K, seed=M + N + K)
@@ -149,16 +152,20 @@ def test_two_k_blocks_per_stage_kernels(ctx, oracle_mod, M, N, K):
     for block_n, two, one in ((128, 3, 6), (64, 4, 8)):
         plan = L.plan(L.IN_BF16, L.OUT_BF16, M, N, K, GemmConfig(1, block_n, two, 0, 0))
         assert plan.stages == two and plan.stage_bytes == 2 * (128 + block_n) * 128
+        assert plan.block == 224 and plan.tmem_cols == 4 * block_n
         assert L.plan(L.IN_BF16, L.OUT_BF16, M, N, K, GemmConfig(1, block_n, 0, 0, 0)).stages == two
         ldc = (N + 7) // 8 * 8 + 8
         full = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")
-        ctx.gemm_tn(dA, dB, out=full[:, :N], alpha=0.75, config=GemmConfig(1, block_n, two, 0, 0))
-        ctx.status()
-        check_norm(oracle_mod, full[:, :N], want, f"128 x {block_n}, two k-blocks per stage, {M}x{N}x{K}")
-        assert bool(torch.isnan(full[:, N:]).all())
+        for _ in range(2):   # twice: the second accumulator is reused
+            ctx.gemm_tn(dA, dB, out=full[:, :N], alpha=0.75, config=GemmConfig(1, block_n, two, 0, 0))
+            ctx.status()
+            check_norm(oracle_mod, full[:, :N], want, f"128 x {block_n}, two k-blocks per stage, {M}x{N}x{K}")
+            assert bool(torch.isnan(full[:, N:]).all())
         ref = ctx.gemm_tn(dA, dB, alpha=0.75, config=GemmConfig(1, block_n, one, 0, 0))
         ctx.status()
-        assert torch.equal(full[:, :N], ref)
+        check_norm(oracle_mod, full[:, :N], ref.float().cpu().numpy(), "two accumulators vs one")
+        if K == 64:
+            assert torch.equal(full[:, :N], ref)
 
 
 @pytest.mark.parametrize("M,N,K", [(1536, 512, 320), (1400, 520, 136), (4096, 1024, 1024)])

@@ -132,7 +132,13 @@ def test_planner_picks_match_what_was_measured_fastest():
                                               # 256 x 256 pair tiles (6.92 waves) 180.1
         (8192, 512, 4096): (1, 1, 256),       # one wave, short K: 128 lone CTAs 25.6 us, 64 pairs 27.9 us
         (8192, 512, 6144): (2, 1, 256),       # longer K: the pair is ahead again (41.8 vs 44.0 us)
-        (2048, 2048, 2048): (1, 1, 256),      # 15.3 vs 17.4 us
+        (2048, 2048, 2048): (1, 1, 256),      # 15.3 vs 17.4 us (128 x 128 tiles with two accumulators: 18.4)
+        # at most one wave of 128 x 128 tiles: two k-blocks per stage, two accumulators
+        (1024, 1024, 1024): (1, 1, 64),       # 6.7 us; 128 x 128 tiles 7.2; one accumulator 9.2
+        (512, 512, 512): (1, 1, 64),          # 5.1 vs 5.5
+        (2048, 1024, 1024): (1, 1, 128),      # 7.7 vs 10.3 on 128 x 64 tiles (two waves) vs 9.9 on 128 x 256
+        (1024, 2048, 2048): (1, 1, 128),      # 10.7 vs 15.7
+        (1536, 1536, 4096): (1, 1, 128),      # 17.7 vs 27.3
     }
     for shape, want in picks.items():
         p = L.plan(L.IN_BF16, L.OUT_BF16, *shape)
@@ -306,16 +312,19 @@ def test_mx_quantiser_round_trip(oracle_mod):
 
 
 def test_cluster_split_k_choice(built_lib):
-    """Which problems get K cut across a cluster: more than 128 rows, few 128 x 256 tiles (one
-    wave of clusters), enough k-blocks saved per CTA to pay for the exchange; never the skinny
-    shapes (stream-K), never shapes that fill the machine."""
+    """Which problems get K cut across a cluster: more than 128 rows, so few tiles that even
+    128 x 64 ones would leave a third of the SMs without one (above that the two-accumulator
+    single-CTA kernels are ahead: timed on a B200, microseconds split / whole), enough k-blocks
+    saved per CTA to pay for the exchange; never the skinny shapes (stream-K)."""
     from patina_b200 import lib as Lm
     c = lambda M, N, K: built_lib.patina_gemm_cluster_k_chosen(Lm.IN_BF16, Lm.OUT_BF16, M, N, K, 148)
     assert c(1024, 1024, 1024) == 0          # 16 k-blocks: the exchange costs more than it saves
-    assert c(1024, 2048, 2048) == 2          # 64 tiles, 32 k-blocks: two CTAs per tile
-    assert c(256, 4096, 4096) == 4
-    assert c(1024, 1024, 4096) == 4
-    assert c(512, 512, 4096) == 4            # 8 tiles: the largest cluster
+    assert c(512, 512, 4096) == 4            # 32 tiles of 128 x 64: 13.1 / 14.3
+    assert c(512, 1024, 8192) == 4           # 64 tiles: 18.4 / 25.0
+    assert c(256, 256, 8192) == 4            # 17.4 / 24.6
+    assert c(1024, 1024, 4096) == 0          # 128 tiles: 16.0 / 15.4
+    assert c(256, 4096, 4096) == 0           # 16.1 / 15.5
+    assert c(1024, 2048, 2048) == 0          # 12.8 / 10.7
     assert c(2048, 2048, 2048) == 0          # 128 tiles: no room for a second CTA per tile
     assert c(8192, 8192, 8192) == 0
     assert c(1024, 1024, 256) == 0           # 4 k-blocks: nothing to save

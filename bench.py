@@ -58,9 +58,9 @@ WORKLOADS = {
                         "bf16 TN GEMM M=N=K=8192, N(0,1)*0.1, fp32 accumulate, bf16 out"),
     "bf16_tn_1024": _wl(1024, 1024, 1024, "uniform",
                         "bf16 TN GEMM M=N=K=1024, U(-1,1), fp32 accumulate, bf16 out (the CPU-checkable case)"),
-    "bf16_tn_1024x1024x4096": _wl(1024, 1024, 4096, "normal_0p1",
-                                  "bf16 TN GEMM M=N=1024, K=4096 (few tiles, deep K: K is cut across a 4-CTA cluster), "
-                                  "N(0,1)*0.1, fp32 accumulate, bf16 out"),
+    "bf16_tn_512x1024x8192": _wl(512, 1024, 8192, "normal_0p1",
+                                 "bf16 TN GEMM M=512, N=1024, K=8192 (few tiles, deep K: K is cut across a 4-CTA cluster), "
+                                 "N(0,1)*0.1, fp32 accumulate, bf16 out"),
     "bf16_tn_4096": _wl(4096, 4096, 4096, "normal_0p1",
                         "bf16 TN GEMM M=N=K=4096, N(0,1)*0.1, fp32 accumulate, bf16 out"),
     "fp8_tn_8192": _wl(8192, 8192, 8192, "unit_normal", "fp8 e4m3 TN GEMM M=N=K=8192, per-tensor scales "

@@ -120,6 +120,7 @@ const KernelEntry kKernels[] = {
     // f16 -> f32 (the reference kernel's types)
     PATINA_KERNEL(2, 1, 256, 6, kF16, kOutF32),
     PATINA_KERNEL(1, 1, 256, 4, kF16, kOutF32),
+    PATINA_KERNEL_KC(1, 128, 3, kF16, kOutF32, 2),
     PATINA_KERNEL(1, 1, 128, 6, kF16, kOutF32),
 };
 constexpr int kNumKernels = sizeof(kKernels) / sizeof(kKernels[0]);

@@ -48,6 +48,7 @@ pub struct PatinaGemmConfig {
     pub m_sub: i32,
     pub stream_k: i32,
     pub cluster_k: i32,
+    pub k_order: i32,
 }
 
 #[repr(C)]
@@ -182,7 +183,7 @@ impl Default for PatinaGemmConfig {
     /// All zero: "choose for me" in every field.
     fn default() -> Self {
         PatinaGemmConfig { cta_group: 0, block_n: 0, stages: 0, group_m: 0, max_ctas: 0, m_sub: 0, stream_k: 0,
-                           cluster_k: 0 }
+                           cluster_k: 0, k_order: 0 }
     }
 }
 

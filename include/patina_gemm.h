@@ -66,6 +66,12 @@ typedef struct PatinaGemmConfig {
   int32_t cluster_k; /* few tiles, deep K, M > 128 (bf16): K cut across a thread-block cluster of
                         this many CTAs (2 or 4) per 128 x 256 tile, partial tiles summed through
                         distributed shared memory; 0 = library decides, -1 = never */
+  int32_t k_order;   /* 0 = library decides: problems of at most one wave of 128 x 128 tiles take
+                        kernels with two accumulators (C = sum over even k-blocks + sum over odd
+                        k-blocks), a few take cluster_k; 1 = every output is summed over k in
+                        ascending order in one accumulator, so the result does not depend on how
+                        a problem is cut into column shards or row blocks (the sharded and
+                        host-buffer entry points ask for this themselves) */
 } PatinaGemmConfig;
 
 /* What a call would launch; computed on the host without touching a device. */

@@ -280,7 +280,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (c.block_n != 0 && k.block_n != c.block_n) continue;
       if (c.stages != 0 && k.stages != c.stages) continue;
       if (k.m_sub != (c.m_sub != 0 ? c.m_sub : 1)) continue;  // explicit requests default to m_sub = 1
-      if (k.k_chunks > 1 && !chunked_ok(in_type, K)) continue;
+      if (k.k_chunks > 1 && (!chunked_ok(in_type, K) || c.k_order == 1)) continue;
       if (need_fused && !k.fn_fused) continue;
       if (need_scatter && !k.fn_scatter) continue;
       best = &k;
@@ -298,7 +298,7 @@ int make_plan(int in_type, int out_type, int64_t M, int64_t N, int64_t K,
       if (k.in_type != in_type || k.out_type != out_type) continue;
       if (c.stages != 0 && k.stages != c.stages) continue;
       if (k.cta_group == 2 && num_sms < 2) continue;
-      if (k.k_chunks > 1 && !chunked_ok(in_type, K)) continue;
+      if (k.k_chunks > 1 && (!chunked_ok(in_type, K) || c.k_order == 1)) continue;
       if (need_fused && !k.fn_fused) continue;
       if (need_scatter && !k.fn_scatter) continue;
       // (Peer destinations: store boxes with 128-byte rows cross NVLink at 0.84 of the plain copy
@@ -878,7 +878,8 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
                      "cluster_k needs bf16 in and out, 2 or 4 CTAs, at least that many 128-byte k-blocks, "
                      "N a multiple of 8, the plain epilogue and no explicit tile");
-  if (n_extra == 0 && epi == nullptr && !explicit_tile && want_ck >= 0 && want_sk <= 0) {
+  if (n_extra == 0 && epi == nullptr && !explicit_tile && want_ck >= 0 && want_sk <= 0 &&
+      !(cfg && cfg->k_order == 1 && want_ck == 0)) {
     const int split = want_ck > 0 ? want_ck : cluster_k_choice(in_type, out_type, M, N, K, ctx->num_sms);
     if (split >= 2)
       return launch_cluster_k(ctx, A, lda, B, ldb, C, ldc, M, N, K, alpha, split, cfg ? cfg->group_m : 0, stream);
@@ -1574,8 +1575,11 @@ int patina_gemm_sharded_bf16_tn(PatinaGemmContext* const* ctxs, int n_shards, co
     int64_t n0, n1;
     patina_gemm_column_shard(N, n_shards, g, &n0, &n1);
     if (n1 == n0) continue;
+    // (ascending k in one accumulator: every shard's columns equal the unsharded result's)
+    PatinaGemmConfig cfg{};
+    cfg.k_order = 1;
     const int rc = launch_gemm(ctxs[g], kBF16, kOutBF16, A[g], lda, B_shards[g], ldb, C_shards[g], ldc, M, n1 - n0,
-                               K, alpha, nullptr, static_cast<cudaStream_t>(streams ? streams[g] : nullptr));
+                               K, alpha, &cfg, static_cast<cudaStream_t>(streams ? streams[g] : nullptr));
     if (rc != PATINA_GEMM_OK) return rc;
   }
   return PATINA_GEMM_OK;
@@ -1663,6 +1667,12 @@ int patina_gemm_host(PatinaGemmContext* ctx, int in_type, int out_type, const vo
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG, "null host pointer");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   DeviceGuard guard(ctx->device);
+  // Ascending k in one accumulator, whether the call runs one GEMM or one per row block: the
+  // result does not depend on how (or whether) the rows are cut.
+  PatinaGemmConfig host_cfg{};
+  if (cfg) host_cfg = *cfg;
+  if (host_cfg.k_order == 0) host_cfg.k_order = 1;
+  cfg = &host_cfg;
   const size_t ib = input_bytes(in_type), ob = output_bytes(out_type);
   // Device copies are dense with the pitch rounded up to 16 bytes.
   const int64_t dk = (int64_t)((((size_t)K * ib + 15) / 16) * 16 / ib);

@@ -40,7 +40,7 @@ class StreamKPlan(C.Structure):
 class GemmConfig(C.Structure):
     _fields_ = [("cta_group", C.c_int32), ("block_n", C.c_int32), ("stages", C.c_int32),
                 ("group_m", C.c_int32), ("max_ctas", C.c_int32), ("m_sub", C.c_int32), ("stream_k", C.c_int32),
-                ("cluster_k", C.c_int32)]
+                ("cluster_k", C.c_int32), ("k_order", C.c_int32)]
 
 
 class GemmEpilogue(C.Structure):

@@ -13,6 +13,12 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from .lib import GemmConfig
+
+# every output summed over k in ascending order in one accumulator: what makes a shard's or a row
+# block's result equal, bit for bit, to the same part of an uncut launch with this setting
+ASCENDING_K = GemmConfig(k_order=1)
+
 
 def column_shard(n: int, world: int, rank: int, align: int = 256) -> tuple[int, int]:
     """[start, stop) of rank's columns. Shards are contiguous, sized in multiples of
@@ -34,8 +40,10 @@ def shard_sizes(n: int, world: int, align: int = 256) -> list[int]:
 def gemm_column_shard(ctx, A: torch.Tensor, B_shard: torch.Tensor, out: torch.Tensor | None = None,
                       alpha: float = 1.0) -> torch.Tensor:
     """This rank's C[:, n0:n1] = alpha * A @ B_shard^T on its own GPU. `out` may be a
-    column slice of a full-width C (row stride N): the kernel takes the leading dimension."""
-    return ctx.gemm_tn(A, B_shard, out=out, alpha=alpha)
+    column slice of a full-width C (row stride N): the kernel takes the leading dimension.
+    Summed over k in ascending order in one accumulator (`k_order = 1`), so the shard holds the
+    bits an unsharded launch with the same setting produces for these columns."""
+    return ctx.gemm_tn(A, B_shard, out=out, alpha=alpha, config=ASCENDING_K)
 
 
 def all_gather_columns(c_shard: torch.Tensor, n_total: int, group=None, align: int = 256) -> torch.Tensor:
@@ -169,7 +177,9 @@ class HostShardedGemm:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.m, self.n, self.k = m, n_shard, k
         self.device = torch.device("cuda", ctx.device) if device is None else torch.device(device)
-        self.gemm = gemm if gemm is not None else ctx.gemm_tn
+        # (row blocks: ascending k, so that the result does not depend on the cut)
+        self.gemm = gemm if gemm is not None else (
+            lambda a, b, out=None, alpha=1.0: ctx.gemm_tn(a, b, out=out, alpha=alpha, config=ASCENDING_K))
         self.blocks = row_blocks(m, self.world, max_blocks)
         padded = (self.blocks[-1][0] + self.blocks[-1][2] * self.world) if self.blocks else 0
         self.dA = torch.empty((max(padded, m), k), dtype=dtype, device=self.device)

@@ -657,20 +657,24 @@ def test_cluster_split_k_refusals(ctx):
     ctx.status()
 
 
-def test_sharded_entry_point_on_one_gpu(oracle_mod):
+@pytest.mark.parametrize("K", [520, 512])
+def test_sharded_entry_point_on_one_gpu(oracle_mod, K):
     """patina_gemm_sharded_bf16_tn with several shards that all live on this GPU (one context and
     one stream per shard, as on a multi-GPU node one per GPU): each shard writes its column block
     of one full-width C through the leading dimension, and the result equals the unsharded call
-    bit for bit, for shard counts that split the width evenly and unevenly."""
+    that sums in the same ascending k order (`k_order = 1`, which the sharded entry point asks
+    for itself) bit for bit, for shard counts that split the width evenly and unevenly. K = 512
+    is whole k-blocks: without that setting the unsharded call and the narrower shards would take
+    the two-accumulator kernels, whose sums round differently."""
     import ctypes as C
     import patina_b200
     from patina_b200 import inputs, sharded, lib as L
     lib = L.load()
-    M, N, K = 1000, 1800, 520
+    M, N = 1000, 1800
     A, B = inputs.make_operands("llm", M, N, K, seed=12)
     dA, dB = A.cuda(), B.cuda()
     ctxs = [patina_b200.GemmContext(0) for _ in range(4)]
-    single = ctxs[0].gemm_tn(dA, dB)
+    single = ctxs[0].gemm_tn(dA, dB, config=sharded.ASCENDING_K)
     ctxs[0].status()
     for world in (1, 2, 3, 4):
         full = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")

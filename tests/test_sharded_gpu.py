@@ -36,7 +36,8 @@ def _worker(rank, world, port, q):
         shard = sharded.gemm_column_shard(ctx, dA, dB[n0:n1])
         ctx.status()
         full = sharded.all_gather_columns(shard, N)
-        single = ctx.gemm_tn(dA, dB)                                      # the whole problem on this GPU
+        single = ctx.gemm_tn(dA, dB, config=sharded.ASCENDING_K)        # the whole problem on this GPU, summed in
+                                                                          # ascending k like the shards
         ctx.status()
         # also: write the shard straight into a full-width C through the leading dimension
         wide = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
@@ -68,7 +69,7 @@ def _worker(rank, world, port, q):
         for _ in range(2):
             run(mine, hB, hC)
             ctx.status()
-        host_ok = bool(torch.equal(hC.cuda(), ctx.gemm_tn(A2.cuda(), dB[n0:n1])))
+        host_ok = bool(torch.equal(hC.cuda(), ctx.gemm_tn(A2.cuda(), dB[n0:n1], config=sharded.ASCENDING_K)))
         ctx.status()
         ok = (bool(torch.equal(full, single)) and bool(torch.equal(wide[:, n0:n1], single[:, n0:n1]))
               and fused_ok and host_ok)

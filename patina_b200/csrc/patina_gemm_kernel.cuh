@@ -2,12 +2,15 @@
 //
 //   C[M,N] = alpha * A[M,K] * B[N,K]^T      (both operands K-major, "TN")
 //
-// One CTA = 6 warps with fixed roles, the same split the reference's generated
-// kernel uses (crates/patina/tests/golden/v2_gemm_pipelined.ptx:89-94):
-//   warp 0      TMA producer   (one elected lane)
+// One CTA = 6 and more warps with fixed roles, the split the reference's generated
+// kernel uses (crates/patina/tests/golden/v2_gemm_pipelined.ptx:89-94) and a few more:
+//   warp 0      TMA producer   (one lane per load of a stage: each A slab, B)
 //   warp 1      MMA issuer     (one elected lane; the whole warp owns TMEM alloc/dealloc)
 //   warps 2..   epilogue       (TMEM -> registers -> swizzled SMEM -> TMA store),
 //               four warps per accumulator sub-tile, one per TMEM lane quarter
+//   then, where they exist: the scale producer of block-scaled kernels, and a second
+//               MMA issuer in kernels with two accumulators to multiply into at once
+//               (two sub-tiles, or the even and odd k-blocks of a narrow tile)
 //
 // What is different from that kernel (which runs one 128x128 tile in one CTA):
 //   * persistent: each CTA (or CTA pair) walks a list of output tiles
@@ -22,9 +25,9 @@
 //     operand prefetch;
 //   * optional CTA pair (kCtaGroup == 2): tcgen05.mma.cta_group::2 computes a
 //     256 x BN tile; each CTA loads its own 128 rows of A and its own BN/2 rows
-//     of B; the pair leader issues the MMAs. No TMA multicast is used: each
+//     of B; the pair leader issues the MMAs. No TMA load is multicast: each
 //     CTA's loads land in its own shared memory and count on the leader's
-//     barrier;
+//     barrier (the one multicast in the file is the commit that signals both CTAs);
 //   * every wait is bounded (WaitCtx): on expiry the CTA records a status code,
 //     raises an abort flag that all roles poll, drains and returns.
 #pragma once

@@ -63,6 +63,21 @@ def test_tile_scheduler_is_a_bijection(built_lib, tiles_m, tiles_n, group):
         assert (m.value, n.value) == (1, 0)
 
 
+def test_plan_ascending_k_order():
+    """k_order = 1 keeps a small problem off the two-accumulator kernels (whose stages hold two
+    k-blocks: 7 warps, 3 or 4 stages) and off the cluster split."""
+    free = L.plan(L.IN_BF16, L.OUT_BF16, 1024, 1024, 1024)
+    assert (free.cta_group, free.block_n, free.stages, free.block) == (1, 64, 4, 224)
+    assert free.stage_bytes == 2 * (128 + 64) * 128 and free.tmem_cols == 256
+    kept = L.plan(L.IN_BF16, L.OUT_BF16, 1024, 1024, 1024, L.GemmConfig(k_order=1))
+    assert kept.block == 192 and kept.stage_bytes == (128 + kept.block_n) * 128
+    with pytest.raises(ValueError):   # the two-k-block kernel by its stage count, and ascending k: no such kernel
+        L.plan(L.IN_BF16, L.OUT_BF16, 1024, 1024, 1024, L.GemmConfig(1, 128, 3, k_order=1))
+    # large problems are summed in ascending k anyway: the setting changes nothing there
+    a, b = L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192), L.plan(L.IN_BF16, L.OUT_BF16, 8192, 8192, 8192, L.GemmConfig(k_order=1))
+    assert (a.cta_group, a.m_sub, a.block_n, a.stages) == (b.cta_group, b.m_sub, b.block_n, b.stages)
+
+
 def test_plan_half_tile_tail():
     """A last wave that fills at most half of the clusters is run as half tiles."""
     # 8192 x 4096: 16 x 16 = 256 tiles of 512 x 256 on 74 clusters: 3 waves and 34 tiles

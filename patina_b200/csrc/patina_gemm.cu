@@ -590,6 +590,13 @@ SkPlan make_sk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms) {
   // every CTA gets at least kSkMinUnits units, so that its set-up is paid for by some streaming
   const uint64_t want = (s.units + kSkMinUnits - 1) / kSkMinUnits;
   s.grid = (uint32_t)((uint64_t)num_sms < want ? (uint64_t)num_sms : want);
+  // Fewer tiles than SMs: cut every tile into the same number of ranges, so that each CTA has one
+  // segment of one tile (one accumulator to drain, one partial tile to publish) -- as long as that
+  // keeps nine SMs in ten busy.
+  if (s.tiles < s.grid) {
+    const uint32_t aligned = s.tiles * (s.grid / s.tiles);
+    if (aligned * 10u >= s.grid * 9u) s.grid = aligned;
+  }
   s.max_contrib = streamk_max_contrib(s.units, s.grid, s.k_blocks);
   s.partial_bytes = (uint64_t)s.tiles * s.max_contrib * s.m_pad * 128ull * sizeof(float);
   s.counter_bytes = (uint64_t)s.tiles * sizeof(uint32_t);

@@ -234,7 +234,14 @@ def test_streamk_partition(built_lib, M, N, K, sms):
     p = L.streamk_plan(L.IN_BF16, M, N, K, sms)
     assert p.m_pad % 16 == 0 and M <= p.m_pad < M + 16
     assert p.tiles == -(-N // 128) and p.k_blocks == -(-K // 64) and p.units == p.tiles * p.k_blocks
-    assert p.grid == min(sms, -(-p.units // 8)) and p.smem_bytes <= 232448   # at least 8 units per CTA
+    # at least 8 units per CTA; with fewer tiles than CTAs every tile is cut into the same number
+    # of ranges (one segment per CTA) when that keeps nine SMs in ten busy
+    want = min(sms, -(-p.units // 8))
+    if p.tiles < want and p.tiles * (want // p.tiles) * 10 >= want * 9:
+        want = p.tiles * (want // p.tiles)
+    assert p.grid == want and p.smem_bytes <= 232448
+    if (M, N, K, sms) == (64, 3584, 8192, 148):
+        assert p.grid == 140                  # 28 tiles x 5 ranges
     assert p.partial_bytes == p.tiles * p.max_contrib * p.m_pad * 128 * 4 and p.counter_bytes == p.tiles * 4
     b, e = C.c_uint64(), C.c_uint64()
     prev_end, lens = 0, []

@@ -604,9 +604,10 @@ SkPlan make_sk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms) {
 }
 
 // The automatic choice between the two kernels for M <= 128.
-//  * Many weight tiles (N = 28672, K = 8192): stream-K leads for M <= 32 (75.3 vs 77 us at
-//    M = 16); from M = 64 on the X slab is as large as the W slab and the large-tile kernel,
-//    which loads one X slab per 256 rows of W, is ahead -- as long as it has a tile for most SMs.
+//  * Many weight tiles (N = 28672, K = 8192): stream-K leads at M <= 16 (75.3 vs 77 us); with
+//    32 rows of X it is already behind (80.4 vs 78.3 us) and from M = 64 on the X slab is as large
+//    as the W slab and the large-tile kernel, which loads one X slab per 256 rows of W, is well
+//    ahead (80.1 vs 89.4 us) -- as long as it has a tile for most SMs.
 //  * Few weight tiles (a narrow shard, or the reference's own 128 x 128 x K shape) leave the
 //    large-tile kernel on a handful of SMs, each pulling its whole K through one SM's L2 port:
 //    128 x 128 x 8192 takes 45 us there and 10 us when K is cut across CTAs (128 x 1024 x 4096:
@@ -615,7 +616,7 @@ SkPlan make_sk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms) {
 bool streamk_preferred(int in_type, int out_type, int64_t M, int64_t N, int64_t K, int num_sms) {
   if (!streamk_supported(in_type, out_type, M)) return false;
   const SkPlan s = make_sk_plan(in_type, M, N, K, num_sms);
-  if (M <= 32 && s.units >= 4ull * (uint64_t)num_sms) return true;
+  if (M <= 16 && s.units >= 4ull * (uint64_t)num_sms) return true;
   const uint64_t large_tiles = (uint64_t)ceil_div(N, 256);  // one 128-row tile covers all of M
   const bool starved = large_tiles * 10 < (uint64_t)num_sms * 7;
   return starved && s.k_blocks >= 24;

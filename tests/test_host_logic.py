@@ -273,6 +273,7 @@ def test_automatic_choice_between_the_two_kernels(built_lib):
     timed on a B200 (microseconds: stream-K / large-tile)."""
     chosen = lambda M, N, K, t=L.IN_BF16, o=L.OUT_BF16: built_lib.patina_gemm_streamk_chosen(t, o, M, N, K, 148)
     assert chosen(16, 28672, 8192) == 1        # 75.3 / 77
+    assert chosen(32, 28672, 8192) == 0        # 80.4 / 78.3
     assert chosen(64, 28672, 8192) == 0        # 88 / 78: enough 256-wide tiles for most SMs
     assert chosen(128, 28672, 8192) == 0       # 98 / 79
     assert chosen(64, 3584, 8192) == 1         # 16.8 / 23 (an 8-way shard: 14 tiles of 256)

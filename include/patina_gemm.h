@@ -60,7 +60,7 @@ typedef struct PatinaGemmConfig {
   int32_t max_ctas;  /* cap on persistent CTAs (0 = number of SMs) */
   int32_t m_sub;     /* 128-row accumulator sub-tiles per CTA: 1 or 2;
                         tile height = 128 * cta_group * m_sub */
-  int32_t stream_k;  /* skinny path (M <= 128, bf16 out): 0 = library decides, 1 = force,
+  int32_t stream_k;  /* skinny path (M <= 128; bf16 out, or f16 in / f32 out): 0 = library decides, 1 = force,
                         -1 = never; 2 = force, and sum shared tiles in the follow-up kernel;
                         3 = force, and let the last CTA to reach a tile sum it */
   int32_t cluster_k; /* few tiles, deep K, M > 128 (bf16): K cut across a thread-block cluster of

@@ -439,7 +439,7 @@ struct PatinaGemmContext {
   float* d_sk_partials = nullptr;
   uint32_t* d_sk_counters = nullptr;
   size_t cap_sk_partials = 0, cap_sk_counters = 0;
-  bool sk_attr_set[2] = {false, false};
+  bool sk_attr_set[3] = {false, false, false};
   bool ck_attr_set[3] = {false, false, false};   // cluster split-K kernels (2, 4, 8 CTAs)
   bool mx_attr_set[kNumMxKernels] = {};
   int mx_max_clusters[kNumMxKernels] = {};
@@ -576,7 +576,9 @@ struct SkPlan {
 };
 
 bool streamk_supported(int in_type, int out_type, int64_t M) {
-  return out_type == kOutBF16 && (in_type == kBF16 || in_type == kE4M3) && M >= 1 && M <= 128;
+  const bool types = (out_type == kOutBF16 && (in_type == kBF16 || in_type == kE4M3)) ||
+                     (out_type == kOutF32 && in_type == kF16);   // the reference's own types
+  return types && M >= 1 && M <= 128;
 }
 
 constexpr uint64_t kSkMinUnits = 8;
@@ -654,7 +656,7 @@ cudaError_t launch_sk_kernel(const SkPlan& sp, cudaStream_t stream, const CUtens
 
 int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t lda, const void* B,
                    int64_t ldb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha,
-                   cudaStream_t stream, int reduce_mode = 0) {
+                   cudaStream_t stream, int reduce_mode = 0, bool out_f32 = false) {
   const SkPlan sp = make_sk_plan(in_type, M, N, K, ctx->num_sms);
   // scratch: grow-only; counters start (and are left) at zero
   if (ctx->cap_sk_partials < sp.partial_bytes) {
@@ -697,7 +699,8 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
   p.stage_stride = streamk_stage_stride(sp.m_pad);
   p.burst = ctx->sk_burst < p.stages / 2 ? ctx->sk_burst : p.stages / 2;
   p.alpha = alpha;
-  p.C = static_cast<__nv_bfloat16*>(C);
+  p.C = C;
+  p.out_f32 = out_f32 ? 1u : 0u;
   p.ldc = ldc;
   p.partials = ctx->d_sk_partials;
   p.counters = ctx->d_sk_counters;
@@ -715,9 +718,9 @@ int launch_streamk(PatinaGemmContext* ctx, int in_type, const void* A, int64_t l
 #ifdef PATINA_TRACE
   p.trace = ctx->trace;
 #endif
-  cudaError_t e = (in_type == kBF16)
-                      ? launch_sk_kernel<kBF16>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[0])
-                      : launch_sk_kernel<kE4M3>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[1]);
+  cudaError_t e = (in_type == kBF16)   ? launch_sk_kernel<kBF16>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[0])
+                  : (in_type == kE4M3) ? launch_sk_kernel<kE4M3>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[1])
+                                       : launch_sk_kernel<kF16>(sp, stream, tm_w, tm_x, p, &ctx->sk_attr_set[2]);
   if (e != cudaSuccess) return cuda_fail(ctx, e, "stream-K launch");
   ctx->launches += p.split_reduce ? 2 : 1;
   return PATINA_GEMM_OK;
@@ -874,12 +877,12 @@ int launch_gemm(PatinaGemmContext* ctx, int in_type, int out_type, const void* A
   const int want_sk = cfg ? cfg->stream_k : 0;
   if (want_sk > 0 && !streamk_supported(in_type, out_type, M))
     return set_error(ctx, PATINA_GEMM_ERR_INVALID_ARG,
-                     "stream_k needs M <= 128, bf16 or e4m3 inputs and bf16 output");
+                     "stream_k needs M <= 128 and bf16 or e4m3 inputs with bf16 output, or f16 inputs with f32 output");
   const bool explicit_tile = cfg && (cfg->cta_group != 0 || cfg->block_n != 0 || cfg->m_sub != 0);
   if (n_extra == 0 && epi == nullptr &&
       (want_sk > 0 || (want_sk == 0 && !explicit_tile &&
                        streamk_preferred(in_type, out_type, M, N, K, ctx->num_sms))))
-    return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream, want_sk);
+    return launch_streamk(ctx, in_type, A, lda, B, ldb, C, ldc, M, N, K, alpha, stream, want_sk, out_type == kOutF32);
   const int want_ck = cfg ? cfg->cluster_k : 0;
   if (want_ck > 0 && (n_extra > 0 || epi != nullptr || explicit_tile ||
                       !cluster_k_supported(in_type, out_type, M, N, K, want_ck)))
@@ -1817,7 +1820,8 @@ int patina_gemm_cluster_k_chosen(int in_type, int out_type, int64_t M, int64_t N
 
 int patina_gemm_streamk_plan(int in_type, int64_t M, int64_t N, int64_t K, int num_sms,
                              PatinaStreamKPlan* out) {
-  if (!out || N <= 0 || K <= 0 || num_sms <= 0 || !streamk_supported(in_type, kOutBF16, M))
+  if (!out || N <= 0 || K <= 0 || num_sms <= 0 ||
+      !streamk_supported(in_type, in_type == kF16 ? kOutF32 : kOutBF16, M))
     return PATINA_GEMM_ERR_INVALID_ARG;
   const SkPlan s = make_sk_plan(in_type, M, N, K, num_sms);
   out->grid = s.grid;
@@ -2015,7 +2019,7 @@ extern "C" int patina_gemm_bf16_tn_skinny_noalloc(const void* A, int64_t lda, co
   p.stage_stride = streamk_stage_stride(sp.m_pad);
   p.burst = 4 < p.stages / 2 ? 4 : p.stages / 2;
   p.alpha = alpha;
-  p.C = static_cast<__nv_bfloat16*>(C);
+  p.C = C;
   p.ldc = ldc;
   p.status = reinterpret_cast<uint32_t*>(d.scratch);
   p.counters = reinterpret_cast<uint32_t*>(d.scratch + kNoAllocStatusBytes);

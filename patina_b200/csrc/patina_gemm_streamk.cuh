@@ -42,7 +42,8 @@ struct StreamKParams {
                            // of the same rows of W reach DRAM together (measured: 1 -> 4 stages
                            // lifts a 470 MB stream from 4.8 to 5.8 TB/s)
   float alpha;
-  __nv_bfloat16* C;
+  void* C;                 // bf16 [M, ldc], or fp32 when out_f32
+  uint32_t out_f32;        // 1: C is fp32 (the reference's f16 -> f32 types), 0: bf16
   int64_t ldc;
   float* partials;         // [tiles][max_contrib][m_pad / 4][128 rows][4] fp32
   uint32_t* counters;      // [tiles], zero between launches
@@ -95,6 +96,12 @@ PATINA_HD bool streamk_any_shared_tile(uint64_t units, uint64_t parts, uint32_t 
   for (uint64_t c = 1; c < parts; ++c)
     if (streamk_range_start(c, units, parts) % k_blocks != 0) return true;
   return false;
+}
+
+// One element of C, rounded to the output type.
+__device__ __forceinline__ void streamk_store(const StreamKParams& p, size_t index, float v) {
+  if (p.out_f32) static_cast<float*>(p.C)[index] = v;
+  else static_cast<__nv_bfloat16*>(p.C)[index] = __float2bfloat16_rn(v);
 }
 
 template <int kIn>
@@ -407,7 +414,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           if (n < p.N) {
 #pragma unroll
             for (uint32_t i = 0; i < 16; ++i)
-              if (m0 + i < p.M) p.C[(size_t)(m0 + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
+              if (m0 + i < p.M) streamk_store(p, (size_t)(m0 + i) * p.ldc + n, acc[i] * p.alpha);
           }
         }
       }
@@ -488,7 +495,7 @@ streamk_reduce_kernel(const StreamKParams p, const uint32_t parts) {
   if (n < p.N) {
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i)
-      if (m0 + i < p.M) p.C[(size_t)(m0 + i) * p.ldc + n] = __float2bfloat16_rn(acc[i] * p.alpha);
+      if (m0 + i < p.M) streamk_store(p, (size_t)(m0 + i) * p.ldc + n, acc[i] * p.alpha);
   }
 }
 

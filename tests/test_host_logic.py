@@ -264,8 +264,7 @@ def test_streamk_partition(built_lib, M, N, K, sms):
 def test_streamk_plan_rejects_wide_m():
     with pytest.raises(ValueError):
         L.streamk_plan(L.IN_BF16, 129, 4096, 4096)
-    with pytest.raises(ValueError):
-        L.streamk_plan(L.IN_F16, 16, 4096, 4096)
+    assert L.streamk_plan(L.IN_F16, 16, 4096, 4096).tiles == 32    # f16 (-> f32): the reference's types
 
 
 def test_automatic_choice_between_the_two_kernels(built_lib):
@@ -284,7 +283,9 @@ def test_automatic_choice_between_the_two_kernels(built_lib):
     assert chosen(16, 24, 40) == 0
     assert chosen(129, 3584, 8192) == 0        # the stream-K kernel holds at most 128 rows of X
     assert chosen(16, 28672, 8192, L.IN_E4M3) == 1
-    assert chosen(128, 128, 4096, L.IN_F16, L.OUT_F32) == 0   # f32 output: large-tile kernel only
+    assert chosen(128, 128, 4096, L.IN_F16, L.OUT_F32) == 1   # the reference's own types and shape: 9.6 / 15.1
+    assert chosen(128, 128, 128, L.IN_F16, L.OUT_F32) == 0    # its test cases (K = 32, 128): one or two k-blocks
+    assert chosen(128, 128, 4096, L.IN_F16, L.OUT_BF16) == 0  # no such type pair
 
 
 def test_block_scaled_encodings(built_lib):
